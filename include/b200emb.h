@@ -1,0 +1,213 @@
+/*
+ * b200emb.h -- C ABI of the B200-native model-forward path for embedding,
+ * reranking and classification.
+ *
+ * The library replaces the model-forward step that the infinity_emb engine
+ * reaches through its backend interface
+ *   infinity_emb/transformer/abstract.py:44-69      (BaseTransformer: encode_pre / encode_core / encode_post)
+ * and that the reference implements with third-party torch code in
+ *   infinity_emb/transformer/embedder/sentence_transformer.py:117-157   (embed: forward, pooling, fp32 + L2 normalise)
+ *   infinity_emb/transformer/crossencoder/torch.py:100-111              (rerank: forward + classification head logits)
+ *   infinity_emb/transformer/classifier/torch.py:74-76                  (classify: forward + head)
+ * The reference has no FFI of its own (it is pure Python); a maintainer binds
+ * this header with ctypes (see INTEGRATION.md for the stub).
+ *
+ * Conventions
+ *   - plain C types only; no exceptions cross the boundary;
+ *   - every function returns a status: 0 = ok, < 0 = invalid argument,
+ *     > 0 = CUDA / runtime failure (including a device-side bounded wait that
+ *     gave up). b200emb_last_error() returns the message of the calling
+ *     thread's last failure;
+ *   - the caller owns every input / output buffer and keeps it alive until
+ *     the call returns; calls are synchronous (internal streams are joined
+ *     before returning) unless a function says otherwise;
+ *   - a handle is not re-entrant (the reference's batcher calls encode_core
+ *     from one thread per replica, infinity_emb/inference/batch_handler.py:562-588);
+ *     distinct handles are independent;
+ *   - there is no CPU fallback: without a usable CUDA device every compute
+ *     entry point fails with B200EMB_ERR_CUDA.
+ */
+#ifndef B200EMB_H_
+#define B200EMB_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200EMB_ABI_VERSION 1
+
+/* status codes */
+#define B200EMB_OK 0
+#define B200EMB_ERR_INVALID (-1)     /* bad argument (null pointer, shape, cu_seqlens not monotone, id out of range ...) */
+#define B200EMB_ERR_UNSUPPORTED (-2) /* a shape / option the kernels do not cover */
+#define B200EMB_ERR_IO (-3)          /* weight file missing, truncated or lacking a tensor */
+#define B200EMB_ERR_CUDA 1           /* a CUDA call failed */
+#define B200EMB_ERR_DEVICE_WAIT 2    /* a bounded device-side wait ran out; the context stays usable */
+
+/* b200emb_model_desc.arch */
+#define B200EMB_ARCH_BERT 0    /* post-LayerNorm encoder, learned absolute positions, token types (BertModel) */
+#define B200EMB_ARCH_XLMR 1    /* same block; positions start at pos_offset (XLM-RoBERTa: padding_idx + 1 = 2) */
+#define B200EMB_ARCH_MOE 2     /* post-LN encoder whose odd layers route the FFN over n_experts with top_k softmax gating */
+#define B200EMB_ARCH_DECODER 3 /* pre-RMSNorm, RoPE, causal grouped-query attention, SwiGLU (Qwen2Model) */
+
+/* b200emb_model_desc.pooling  (reference: PoolingMethod, infinity_emb/primitives.py:161-168;
+ * math: infinity_emb/transformer/utils_optimum.py:29-47) */
+#define B200EMB_POOL_CLS 0  /* row cu_seqlens[i] */
+#define B200EMB_POOL_MEAN 1 /* mean of rows cu_seqlens[i] .. cu_seqlens[i+1]-1, fp32 accumulation */
+#define B200EMB_POOL_LAST 2 /* row cu_seqlens[i+1]-1 */
+
+/* b200emb_model_desc.head */
+#define B200EMB_HEAD_NONE 0       /* output = pooled (optionally L2-normalised) hidden state, [n_seqs, hidden] */
+#define B200EMB_HEAD_CLASSIFIER 1 /* output = out_proj(tanh(dense(h_cls))), [n_seqs, n_labels] raw logits */
+
+/* b200emb_model_desc.weight_format */
+#define B200EMB_WFMT_BF16 0
+#define B200EMB_WFMT_MXFP8 1 /* e4m3 elements, 32-element K blocks, e8m0 scales */
+#define B200EMB_WFMT_NVFP4 2 /* e2m1 elements, 16-element K blocks, e4m3 scales */
+
+/* epilogues of b200emb_op_gemm_bf16 */
+#define B200EMB_EPI_BIAS 0
+#define B200EMB_EPI_BIAS_GELU 1 /* exact (erf) GELU */
+#define B200EMB_EPI_BIAS_TANH 2
+
+typedef struct b200emb_model_desc {
+  int32_t abi_version; /* B200EMB_ABI_VERSION */
+  int32_t arch;
+  int32_t n_layers;
+  int32_t hidden;
+  int32_t n_heads;
+  int32_t n_kv_heads; /* == n_heads unless grouped-query attention */
+  int32_t head_dim;   /* 32, 64 or 128 */
+  int32_t ffn;
+  int32_t vocab;
+  int32_t max_pos;    /* rows of the position table (or longest sequence for RoPE models) */
+  int32_t type_vocab; /* 0 = no token-type table */
+  int32_t pos_offset; /* position id of the first token of a sequence */
+  float norm_eps;
+  float rope_theta;
+  int32_t n_experts;
+  int32_t top_k;
+  int32_t moe_every; /* layer l routes its FFN iff moe_every > 0 and l % moe_every == moe_every - 1 */
+  int32_t pooling;
+  int32_t normalize; /* 1: x / max(||x||_2, 1e-12) after pooling (sentence_transformer.py:142-145) */
+  int32_t head;
+  int32_t n_labels;
+  int32_t weight_format;
+  int32_t max_tokens; /* workspace sizing hint (tokens per device per call); workspaces grow when exceeded */
+  int32_t reserved[8];
+} b200emb_model_desc;
+
+/* Wall and device times of one b200emb_forward call. Device times come from
+ * CUDA events recorded on the stream the kernels are launched on. */
+#define B200EMB_KCLASS_EMBED 0
+#define B200EMB_KCLASS_GEMM 1
+#define B200EMB_KCLASS_ATTN 2
+#define B200EMB_KCLASS_NORM 3
+#define B200EMB_KCLASS_POOL 4
+#define B200EMB_KCLASS_OTHER 5
+#define B200EMB_N_KCLASS 8
+typedef struct b200emb_timing {
+  int32_t per_kernel;  /* in: 1 = bracket every launch with events (slower; fills kclass_*) */
+  int32_t n_devices;   /* out */
+  float h2d_ms;        /* out: max over devices */
+  float kernels_ms;    /* out: first launch to last launch, max over devices */
+  float d2h_ms;        /* out */
+  float total_ms;      /* out: host clock around the whole call */
+  int32_t launches;    /* out: kernels launched by this call, all devices */
+  float kclass_ms[B200EMB_N_KCLASS];       /* out (per_kernel): summed duration per kernel class, device 0 */
+  int32_t kclass_launches[B200EMB_N_KCLASS]; /* out (per_kernel) */
+  double gemm_flops;   /* out: algorithmic GEMM flops issued by device 0 (2*M*N*K per launch) */
+} b200emb_timing;
+
+typedef struct b200emb_handle b200emb_handle;
+
+/* ---- model lifetime -------------------------------------------------------
+ * Replaces the backend constructors that load one replica per device
+ * (infinity_emb/inference/select_model.py:80-83,
+ *  infinity_emb/transformer/embedder/sentence_transformer.py:57-111).
+ * Weights are read from a b200emb weight file (written by
+ * infinity_b200.weights.save_weights) and replicated on every listed device. */
+int b200emb_create(const b200emb_model_desc* desc, const char* weight_path, const int32_t* device_ids,
+                   int32_t n_devices, b200emb_handle** out);
+int b200emb_destroy(b200emb_handle* h);
+
+/* ---- the hot path -----------------------------------------------------------
+ * Replaces encode_core (+ the pooling / normalise part of encode_post):
+ *   sentence_transformer.py:117-133 + :142-145, crossencoder/torch.py:100-108,
+ *   classifier/torch.py:74-76.
+ * Input is the ragged token stream of one batch in the batcher's order
+ * (infinity_emb/inference/queue.py:35-76): input_ids[n_tokens],
+ * token_type_ids[n_tokens] (nullable = all zero), cu_seqlens[n_seqs + 1] with
+ * cu_seqlens[0] == 0, strictly increasing, cu_seqlens[n_seqs] == n_tokens.
+ * All are HOST pointers. Output row i belongs to sequence i:
+ * out[i * out_row_stride + j], j < hidden (HEAD_NONE) or j < n_labels, fp32.
+ * With several devices the sequences are split token-balanced (longest
+ * processing time first on cost a*L + b*L^2) and rows are scattered back to
+ * batch order on the host; no collective runs. */
+int b200emb_forward(b200emb_handle* h, const int32_t* input_ids, const int32_t* token_type_ids,
+                    const int32_t* cu_seqlens, int32_t n_seqs, int32_t n_tokens, float* out,
+                    int64_t out_row_stride, b200emb_timing* timing /* nullable */);
+
+/* Same computation with every buffer already resident on device 0 of the
+ * handle (device pointers; out is device fp32). Used to measure the kernels
+ * without host<->device copies. Single-device handles only. */
+int b200emb_forward_device(b200emb_handle* h, const int32_t* d_input_ids, const int32_t* d_token_type_ids,
+                           const int32_t* d_cu_seqlens, const int32_t* h_cu_seqlens, int32_t n_seqs,
+                           int32_t n_tokens, float* d_out, int64_t out_row_stride, b200emb_timing* timing);
+
+/* Token-balanced partition used by b200emb_forward, exposed for tests and for
+ * callers that run one process per GPU: assigns sequence i (length lens[i]) to
+ * shard_of[i] in [0, n_shards). Deterministic; ties go to the lower index. */
+int b200emb_partition(const int32_t* lens, int32_t n_seqs, int32_t n_shards, double cost_linear,
+                      double cost_quadratic, int32_t* shard_of);
+
+/* Thread-local message of the last failure on the calling thread ("" if none). */
+const char* b200emb_last_error(void);
+
+/* Number of CUDA devices visible, or a negative status. */
+int b200emb_device_count(void);
+
+/* ---- single kernels on device buffers (used by the parity tests) -------------
+ * Pointers are DEVICE pointers on the current device; `stream` is a
+ * cudaStream_t (NULL = default stream). The calls are asynchronous on that
+ * stream except where noted. None has a counterpart function in the reference:
+ * each is one step of the third-party torch forward the reference calls at
+ * sentence_transformer.py:124. */
+
+/* C[M,N] (bf16) = epilogue(A[M,K] (bf16, row-major) * W[N,K]^T (bf16, row-major) + bias[N] (fp32, nullable)).
+ * K % 8 == 0, N % 8 == 0. tcgen05 / TMEM kernel fed by TMA. Synchronises the
+ * stream before returning and reports a device-side wait that gave up. */
+int b200emb_op_gemm_bf16(const void* A, const void* W, const float* bias, void* C, int32_t M, int32_t N,
+                         int32_t K, int32_t epilogue, void* stream);
+
+/* Variable-length attention over a packed qkv buffer [n_tokens, (n_heads + 2*n_kv_heads) * head_dim]
+ * (all query heads, then all key heads, then all value heads), bf16.
+ * out [n_tokens, n_heads * head_dim] bf16. h_cu_seqlens is the host copy used
+ * to build the tile list. causal: 0 = bidirectional, 1 = causal. */
+int b200emb_op_attention(const void* qkv, void* out, const int32_t* d_cu_seqlens, const int32_t* h_cu_seqlens,
+                         int32_t n_seqs, int32_t n_tokens, int32_t n_heads, int32_t n_kv_heads,
+                         int32_t head_dim, int32_t causal, void* stream);
+
+/* x[t,:] = LayerNorm(word[ids[t]] + pos[pos_offset + t - cu_seqlens[seq(t)]] + type[types[t]]) -> bf16.
+ * Tables are bf16, gamma/beta fp32. type_table / types nullable. With
+ * gamma == NULL the sum is written without normalisation (decoder gather). */
+int b200emb_op_embed_ln(const int32_t* ids, const int32_t* types, const int32_t* d_cu_seqlens, int32_t n_seqs,
+                        int32_t n_tokens, const void* word, const void* pos, const void* type_table,
+                        const float* gamma, const float* beta, int32_t hidden, int32_t pos_offset, float eps,
+                        void* out, void* stream);
+
+/* out = LayerNorm(x + y) * gamma + beta, rows of `hidden` bf16, fp32 statistics. y nullable. */
+int b200emb_op_add_ln(const void* x, const void* y, const float* gamma, const float* beta, int32_t n_rows,
+                      int32_t hidden, float eps, void* out, void* stream);
+
+/* Pooling + optional L2 normalisation over the ragged stream:
+ * out[i,:] fp32 (out_bf16 == 0) or bf16 (out_bf16 == 1). */
+int b200emb_op_pool(const void* x, const int32_t* d_cu_seqlens, int32_t n_seqs, int32_t hidden, int32_t pooling,
+                    int32_t normalize, void* out, int64_t out_row_stride, int32_t out_bf16, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200EMB_H_ */

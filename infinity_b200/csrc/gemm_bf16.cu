@@ -1,0 +1,361 @@
+// bf16 GEMM for sm_100a: C[M,N] = epilogue(A[M,K] * W[N,K]^T + bias).
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0        TMA producer: streams 128x64 A tiles and BNx64 W tiles (128-byte swizzle)
+//                 through a STAGES-deep shared-memory ring, one mbarrier pair per slot
+//   warp 1        allocates TMEM and issues tcgen05.mma (128 x BN x 16 per instruction,
+//                 fp32 accumulators in TMEM); two accumulator buffers so the epilogue of
+//                 tile i overlaps the MMAs of tile i+1
+//   warps 2..9    epilogue: tcgen05.ld the accumulator (one TMEM lane = one output row per
+//                 thread), add bias, apply GELU / tanh, round to bf16, store 16-byte vectors
+// M is ragged (token count): TMA zero-fills rows past M, stores are predicated.
+// No cluster launch, no multicast: each CTA issues its own loads; W tiles are re-used
+// out of L2.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace b2 {
+
+static constexpr int BM = 128;
+static constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle span
+static constexpr int UMMA_K = 16;
+static constexpr int N_EPI_WARPS = 8;
+static constexpr int GEMM_THREADS = 32 * (2 + N_EPI_WARPS);
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // two accumulator buffers
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+
+template <int EPI>
+__device__ __forceinline__ float apply_epilogue(float v) {
+  if (EPI == EPI_BIAS_GELU) return gelu_erf(v);
+  if (EPI == EPI_BIAS_TANH) return tanhf(v);
+  return v;
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                         const float* __restrict__ bias, __nv_bfloat16* __restrict__ C, int M, int N, int K,
+                         int* __restrict__ err_flag) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte-swizzled tiles must start on a 1024-byte boundary.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full_bar = empty_bar + STAGES;  // [2]
+  uint64_t* acc_empty_bar = acc_full_bar + 2;   // [2]
+  uint64_t* drain_bar = acc_empty_bar + 2;  // error path only: MMAs in flight before TMEM is freed
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tiles = (M + BM - 1) / BM;
+  const int n_tiles = (N + BN - 1) / BN;
+  const int total_tiles = m_tiles * n_tiles;
+  const int k_blocks = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full_bar[a], 1);
+      mbar_init(&acc_empty_bar[a], N_EPI_WARPS);
+    }
+    mbar_init(drain_bar, 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_w);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      uint32_t issued = 0;  // slots filled so far (for draining on the error path)
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / n_tiles) * BM;
+        const int n0 = (tile % n_tiles) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u)) {
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + Cfg::A_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+          tma_load_2d(a_dst, &tmap_a, &full_bar[stage], kb * BK, m0);
+          tma_load_2d(b_dst, &tmap_w, &full_bar[stage], kb * BK, n0);
+          ++issued;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        atomicExch(err_flag, 1);
+        // Let the copies already in flight land before this CTA's shared memory is released:
+        // wait (bounded) on the full barrier of every slot filled in the last lap.
+        const uint32_t pending = issued < (uint32_t)STAGES ? issued : (uint32_t)STAGES;
+        for (uint32_t i = 0; i < pending; ++i) {
+          const uint32_t idx = issued - 1 - i;  // i-th most recent fill
+          mbar_wait(&full_bar[idx % STAGES], (idx / STAGES) & 1u);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16_f32(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local_tile = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
+        const int acc = local_tile & 1;
+        const uint32_t acc_phase = (local_tile >> 1) & 1u;
+        if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1u)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+          const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
+          const uint64_t b_desc = make_kmajor_sw128_desc(b_addr);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing 16 elements along K inside the 128-byte swizzle span = +32 bytes = +2 encoded
+            tc_mma_f16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);  // slot is free once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) tc_commit(&acc_full_bar[acc]);  // accumulator complete
+      }
+      if (!ok) {
+        atomicExch(err_flag, 2);
+        tc_commit(drain_bar);  // MMAs already issued must finish before the accumulators are freed
+        mbar_wait(drain_bar, 0);
+      }
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    const int ew = warp - 2;                 // 0..7
+    const int quarter = warp & 3;            // TMEM lane quarter this warp may read
+    const int half = ew >> 2;                // which half of the tile's columns
+    constexpr int COLS_PER_WARP = BN / (N_EPI_WARPS / 4);
+    bool ok = true;
+    int local_tile = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
+      const int m0 = (tile / n_tiles) * BM;
+      const int n0 = (tile % n_tiles) * BN;
+      const int acc = local_tile & 1;
+      const uint32_t acc_phase = (local_tile >> 1) & 1u;
+      if (!mbar_wait(&acc_full_bar[acc], acc_phase)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + half * COLS_PER_WARP;
+#pragma unroll 1
+      for (int c = 0; c < COLS_PER_WARP; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c, r);
+        tmem_ld_wait();
+        const int col0 = n0 + half * COLS_PER_WARP + c;
+        if (row < M && col0 < N) {
+          __nv_bfloat16* dst = C + static_cast<size_t>(row) * N + col0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (col0 + j < N) {  // N % 8 == 0, so a group of 8 is all in or all out
+              float v[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+              if (bias != nullptr) {
+                const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + col0 + j));
+                const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias + col0 + j + 4));
+                v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+              }
+              uint4 packed;
+              __nv_bfloat162 p0 = __floats2bfloat162_rn(apply_epilogue<EPI>(v[0]), apply_epilogue<EPI>(v[1]));
+              __nv_bfloat162 p1 = __floats2bfloat162_rn(apply_epilogue<EPI>(v[2]), apply_epilogue<EPI>(v[3]));
+              __nv_bfloat162 p2 = __floats2bfloat162_rn(apply_epilogue<EPI>(v[4]), apply_epilogue<EPI>(v[5]));
+              __nv_bfloat162 p3 = __floats2bfloat162_rn(apply_epilogue<EPI>(v[6]), apply_epilogue<EPI>(v[7]));
+              packed.x = *reinterpret_cast<uint32_t*>(&p0);
+              packed.y = *reinterpret_cast<uint32_t*>(&p1);
+              packed.z = *reinterpret_cast<uint32_t*>(&p2);
+              packed.w = *reinterpret_cast<uint32_t*>(&p3);
+              *reinterpret_cast<uint4*>(dst + j) = packed;
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+    }
+    if (!ok && lane == 0) atomicExch(err_flag, 3);
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---- host side ------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  }
+  return fn;
+}
+
+// bf16 row-major [rows, cols] matrix, box = [box_rows, 64 columns], 128-byte swizzle, zero fill.
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return set_error(B200EMB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(B200EMB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return B200EMB_OK;
+}
+
+template <int BN, int EPI>
+static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tw, const float* bias, void* C, int M, int N, int K,
+                      int sm_count, int* err_flag, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, EPI>;
+  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+  const int tiles = m_tiles * n_tiles;
+  const int grid = tiles < sm_count ? tiles : sm_count;
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tw, bias, reinterpret_cast<__nv_bfloat16*>(C), M, N, K,
+                                                        err_flag);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "gemm launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
+template <int BN>
+static int launch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tw, const float* bias, void* C, int M, int N,
+                      int K, int sm_count, int* err_flag, cudaStream_t stream) {
+  switch (epi) {
+    case EPI_BIAS: return launch_cfg<BN, EPI_BIAS>(ta, tw, bias, C, M, N, K, sm_count, err_flag, stream);
+    case EPI_BIAS_GELU: return launch_cfg<BN, EPI_BIAS_GELU>(ta, tw, bias, C, M, N, K, sm_count, err_flag, stream);
+    case EPI_BIAS_TANH: return launch_cfg<BN, EPI_BIAS_TANH>(ta, tw, bias, C, M, N, K, sm_count, err_flag, stream);
+  }
+  return set_error(B200EMB_ERR_INVALID, "unknown epilogue %d", epi);
+}
+
+template <int BN, int EPI>
+static int init_one() {
+  B2_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     GemmCfg<BN>::SMEM_BYTES));
+  return B200EMB_OK;
+}
+template <int BN>
+static int init_bn() {
+  int rc = init_one<BN, EPI_BIAS>();
+  if (!rc) rc = init_one<BN, EPI_BIAS_GELU>();
+  if (!rc) rc = init_one<BN, EPI_BIAS_TANH>();
+  return rc;
+}
+int gemm_init_device() {
+  int rc = init_bn<256>();
+  if (!rc) rc = init_bn<128>();
+  if (!rc) rc = init_bn<64>();
+  return rc;
+}
+
+int gemm_pick_bn(int M, int N, int sm_count) {
+  // Widest tile whose grid still fills the machine at least once; small problems take narrower tiles.
+  const int m_tiles = (M + BM - 1) / BM;
+  if (m_tiles * ((N + 255) / 256) >= sm_count) return 256;
+  if (m_tiles * ((N + 127) / 128) >= sm_count) return 128;
+  return 64;
+}
+
+int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int epi,
+                     int sm_count, int* err_flag, cudaStream_t stream, int force_bn) {
+  if (M <= 0) return B200EMB_OK;
+  if (N <= 0 || K <= 0 || (K % 8) != 0 || (N % 8) != 0)
+    return set_error(B200EMB_ERR_INVALID, "gemm: need N, K > 0 and multiples of 8 (N=%d K=%d)", N, K);
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) ||
+      (reinterpret_cast<uintptr_t>(C) & 15) || (bias && (reinterpret_cast<uintptr_t>(bias) & 15)))
+    return set_error(B200EMB_ERR_INVALID, "gemm: pointers must be 16-byte aligned");
+  const int bn = force_bn > 0 ? force_bn : gemm_pick_bn(M, N, sm_count);
+  CUtensorMap ta, tw;
+  int rc = make_tmap_bf16_2d(&ta, A, (uint64_t)M, (uint64_t)K, BM);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tw, W, (uint64_t)N, (uint64_t)K, (uint32_t)bn);
+  if (rc) return rc;
+  switch (bn) {
+    case 256: return launch_epi<256>(epi, ta, tw, bias, C, M, N, K, sm_count, err_flag, stream);
+    case 128: return launch_epi<128>(epi, ta, tw, bias, C, M, N, K, sm_count, err_flag, stream);
+    case 64: return launch_epi<64>(epi, ta, tw, bias, C, M, N, K, sm_count, err_flag, stream);
+  }
+  return set_error(B200EMB_ERR_INVALID, "gemm: unsupported tile width %d", bn);
+}
+
+}  // namespace b2

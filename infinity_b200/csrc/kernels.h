@@ -1,0 +1,57 @@
+// Internal launcher declarations shared by the runtime and the single-kernel C entry points.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200emb.h"
+
+namespace b2 {
+
+enum { EPI_BIAS = B200EMB_EPI_BIAS, EPI_BIAS_GELU = B200EMB_EPI_BIAS_GELU, EPI_BIAS_TANH = B200EMB_EPI_BIAS_TANH };
+
+// Records a thread-local error message and returns `code`.
+int set_error(int code, const char* fmt, ...);
+#define B2_CUDA_CHECK(expr)                                                                  \
+  do {                                                                                       \
+    cudaError_t e__ = (expr);                                                                \
+    if (e__ != cudaSuccess)                                                                  \
+      return ::b2::set_error(B200EMB_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e__));    \
+  } while (0)
+
+// Opt-in shared-memory attributes of every kernel, for the current device. Idempotent.
+int kernels_init_device();
+
+// ---- GEMM (gemm_bf16.cu) ----
+// err_flag: device int the kernel sets non-zero when a bounded wait gave up.
+// force_bn: 0 = choose the tile width from the problem size, else 64 / 128 / 256.
+int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int epi,
+                     int sm_count, int* err_flag, cudaStream_t stream, int force_bn);
+int gemm_init_device();
+
+// ---- attention (attention.cu) ----
+struct AttnTile {
+  int32_t seq_start;  // first token of the sequence
+  int32_t seq_len;
+  int32_t q_start;    // first query row of this tile, relative to the sequence
+  int32_t pad;
+};
+// Builds the tile list on the host: one entry per 64-row query tile, longest sequences first.
+// Returns the number of tiles; `tiles` may be null to only count.
+int attention_build_tiles(const int32_t* h_cu_seqlens, int n_seqs, AttnTile* tiles);
+int launch_attention(const void* qkv, void* out, const AttnTile* d_tiles, int n_tiles, int n_heads, int n_kv_heads,
+                     int head_dim, int causal, cudaStream_t stream);
+int attention_init_device();
+
+// ---- row kernels (rowops.cu) ----
+int launch_embed_ln(const int32_t* ids, const int32_t* types, const int32_t* d_cu, int n_seqs, int n_tokens,
+                    const void* word, const void* pos, const void* type_table, const float* gamma, const float* beta,
+                    int hidden, int pos_offset, float eps, void* out, cudaStream_t stream);
+int launch_add_ln(const void* x, const void* y, const float* gamma, const float* beta, int n_rows, int hidden,
+                  float eps, void* out, cudaStream_t stream);
+int launch_pool(const void* x, const int32_t* d_cu, int n_seqs, int hidden, int pooling, int normalize, void* out,
+                int64_t out_row_stride, int out_bf16, cudaStream_t stream);
+// logits[i, l] = dot(x[i, :], W[l, :]) + b[l]; x bf16 [n, hidden], W bf16 [n_labels, hidden], out fp32.
+int launch_small_proj(const void* x, const void* W, const float* bias, int n_rows, int hidden, int n_labels,
+                      float* out, int64_t out_row_stride, cudaStream_t stream);
+
+}  // namespace b2

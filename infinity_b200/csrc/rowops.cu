@@ -1,0 +1,361 @@
+// Memory-bound row kernels over the ragged token stream [n_tokens, hidden] (bf16):
+//   embed_ln   : word + position + token-type gather, then LayerNorm
+//   add_ln     : LayerNorm(x + y)   (post-LN residual step of BERT-style blocks)
+//   pool       : CLS / mean / last-token pooling per sequence + L2 normalisation
+//   small_proj : [n, hidden] x [n_labels, hidden]^T for classifier heads with few labels
+// One warp owns one row; a lane holds hidden/256 (rounded up) 16-byte chunks in registers,
+// statistics are fp32 with warp-shuffle reductions (two-pass: mean, then centred variance).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "kernels.h"
+
+namespace b2 {
+
+static constexpr int ROW_WARPS = 8;  // rows per CTA
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(p[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+
+// Normalises the row held in v[NCH][8] (chunk c = lane + 32*i valid iff c < n_chunks) and stores bf16.
+template <int NCH>
+__device__ __forceinline__ void layernorm_store(float (&v)[NCH][8], int lane, int n_chunks, int hidden,
+                                                const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                float eps, __nv_bfloat16* __restrict__ dst) {
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < NCH; ++i)
+    if (lane + 32 * i < n_chunks) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sum += v[i][e];
+    }
+  const float mean = warp_sum(sum) / hidden;
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < NCH; ++i)
+    if (lane + 32 * i < n_chunks) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float d = v[i][e] - mean;
+        sq += d * d;
+      }
+    }
+  const float rstd = rsqrtf(warp_sum(sq) / hidden + eps);
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    const int c = lane + 32 * i;
+    if (c < n_chunks) {
+      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + c * 8));
+      const float4 g1 = __ldg(reinterpret_cast<const float4*>(gamma + c * 8 + 4));
+      const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta + c * 8));
+      const float4 b1 = __ldg(reinterpret_cast<const float4*>(beta + c * 8 + 4));
+      float o[8];
+      o[0] = (v[i][0] - mean) * rstd * g0.x + b0.x;
+      o[1] = (v[i][1] - mean) * rstd * g0.y + b0.y;
+      o[2] = (v[i][2] - mean) * rstd * g0.z + b0.z;
+      o[3] = (v[i][3] - mean) * rstd * g0.w + b0.w;
+      o[4] = (v[i][4] - mean) * rstd * g1.x + b1.x;
+      o[5] = (v[i][5] - mean) * rstd * g1.y + b1.y;
+      o[6] = (v[i][6] - mean) * rstd * g1.z + b1.z;
+      o[7] = (v[i][7] - mean) * rstd * g1.w + b1.w;
+      *reinterpret_cast<uint4*>(dst + c * 8) = pack8(o);
+    }
+  }
+}
+
+template <int NCH>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+embed_ln_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ types, const int32_t* __restrict__ cu,
+                int n_seqs, int n_tokens, const __nv_bfloat16* __restrict__ word,
+                const __nv_bfloat16* __restrict__ pos, const __nv_bfloat16* __restrict__ type_table,
+                const float* __restrict__ gamma, const float* __restrict__ beta, int hidden, int pos_offset,
+                float eps, __nv_bfloat16* __restrict__ out) {
+  const int t = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  if (t >= n_tokens) return;
+  const int lane = threadIdx.x & 31;
+  const int n_chunks = hidden >> 3;
+  // sequence of token t: largest i with cu[i] <= t
+  int lo = 0, hi = n_seqs;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(cu + mid) <= t) lo = mid; else hi = mid;
+  }
+  const int p = pos_offset + t - __ldg(cu + lo);
+  const int id = __ldg(ids + t);
+  const __nv_bfloat16* wrow = word + static_cast<size_t>(id) * hidden;
+  const __nv_bfloat16* prow = pos != nullptr ? pos + static_cast<size_t>(p) * hidden : nullptr;
+  const __nv_bfloat16* trow = nullptr;
+  if (type_table != nullptr) trow = type_table + static_cast<size_t>(types != nullptr ? __ldg(types + t) : 0) * hidden;
+
+  float v[NCH][8];
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    const int c = lane + 32 * i;
+    if (c < n_chunks) {
+      unpack8(__ldg(reinterpret_cast<const uint4*>(wrow + c * 8)), v[i]);
+      if (trow != nullptr) {
+        float a[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(trow + c * 8)), a);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] += a[e];
+      }
+      if (prow != nullptr) {
+        float a[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(prow + c * 8)), a);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] += a[e];
+      }
+    }
+  }
+  __nv_bfloat16* dst = out + static_cast<size_t>(t) * hidden;
+  if (gamma == nullptr) {
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const int c = lane + 32 * i;
+      if (c < n_chunks) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(v[i]);
+    }
+    return;
+  }
+  layernorm_store<NCH>(v, lane, n_chunks, hidden, gamma, beta, eps, dst);
+}
+
+template <int NCH>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+add_ln_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ y,
+              const float* __restrict__ gamma, const float* __restrict__ beta, int n_rows, int hidden, float eps,
+              __nv_bfloat16* __restrict__ out) {
+  const int row = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const int lane = threadIdx.x & 31;
+  const int n_chunks = hidden >> 3;
+  const __nv_bfloat16* xr = x + static_cast<size_t>(row) * hidden;
+  const __nv_bfloat16* yr = y != nullptr ? y + static_cast<size_t>(row) * hidden : nullptr;
+  float v[NCH][8];
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    const int c = lane + 32 * i;
+    if (c < n_chunks) {
+      unpack8(*reinterpret_cast<const uint4*>(xr + c * 8), v[i]);
+      if (yr != nullptr) {
+        float a[8];
+        unpack8(*reinterpret_cast<const uint4*>(yr + c * 8), a);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] += a[e];
+      }
+    }
+  }
+  layernorm_store<NCH>(v, lane, n_chunks, hidden, gamma, beta, eps, out + static_cast<size_t>(row) * hidden);
+}
+
+// One CTA per sequence. Threads tile the hidden dimension in 16-byte chunks; when the block
+// has more threads than chunks the spare threads split the rows (mean pooling) and the
+// partial sums meet in shared memory.
+static constexpr int POOL_THREADS = 256;
+static constexpr int POOL_MAXC = 4;  // chunks per thread: hidden <= 256 * 8 * 4 = 8192
+
+__global__ void __launch_bounds__(POOL_THREADS)
+pool_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ cu, int hidden, int pooling,
+            int normalize, void* __restrict__ out, int64_t out_row_stride, int out_bf16) {
+  extern __shared__ float pool_smem[];  // [row_groups][hidden] partial sums + 32 reduction slots
+  const int seq = blockIdx.x;
+  const int start = __ldg(cu + seq), end = __ldg(cu + seq + 1);
+  const int n_chunks = hidden >> 3;
+  const int cols = n_chunks < POOL_THREADS ? n_chunks : POOL_THREADS;  // threads across the hidden dim
+  const int row_groups = POOL_THREADS / cols;
+  const int cg = threadIdx.x % cols;
+  const int rg = threadIdx.x / cols;
+  int r_begin = start, r_end = end;
+  if (pooling == B200EMB_POOL_CLS) r_end = start + 1;
+  if (pooling == B200EMB_POOL_LAST) r_begin = end - 1;
+  const float inv_count = 1.0f / fmaxf(static_cast<float>(r_end - r_begin), 1e-9f);
+
+  float acc[POOL_MAXC][8];
+#pragma unroll
+  for (int i = 0; i < POOL_MAXC; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+  if (rg < row_groups) {
+    for (int r = r_begin + rg; r < r_end; r += row_groups) {
+      const __nv_bfloat16* xr = x + static_cast<size_t>(r) * hidden;
+#pragma unroll
+      for (int i = 0; i < POOL_MAXC; ++i) {
+        const int c = cg + cols * i;
+        if (c < n_chunks) {
+          float a[8];
+          unpack8(__ldg(reinterpret_cast<const uint4*>(xr + c * 8)), a);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[i][e] += a[e];
+        }
+      }
+    }
+    // partial sums of this row group; combined below in a fixed order (deterministic)
+    float* part = pool_smem + static_cast<size_t>(rg) * hidden;
+#pragma unroll
+    for (int i = 0; i < POOL_MAXC; ++i) {
+      const int c = cg + cols * i;
+      if (c < n_chunks) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) part[c * 8 + e] = acc[i][e];
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < hidden; i += POOL_THREADS) {
+    float tot = pool_smem[i];
+    for (int g2 = 1; g2 < row_groups; ++g2) tot += pool_smem[static_cast<size_t>(g2) * hidden + i];
+    pool_smem[i] = tot;  // only this thread touches column i of group 0 from here on
+  }
+
+  float* red = pool_smem + static_cast<size_t>(row_groups) * hidden;
+  float sq = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += POOL_THREADS) {
+    const float m = pool_smem[i] * inv_count;
+    pool_smem[i] = m;
+    sq += m * m;
+  }
+  float scale = 1.f;
+  if (normalize) {
+    sq = warp_sum(sq);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+    __syncthreads();
+    float tot = 0.f;
+    for (int w = 0; w < POOL_THREADS / 32; ++w) tot += red[w];
+    scale = 1.f / fmaxf(sqrtf(tot), 1e-12f);
+  }
+  if (out_bf16) {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + static_cast<size_t>(seq) * out_row_stride;
+    for (int i = threadIdx.x; i < hidden; i += POOL_THREADS) o[i] = __float2bfloat16(pool_smem[i] * scale);
+  } else {
+    float* o = reinterpret_cast<float*>(out) + static_cast<size_t>(seq) * out_row_stride;
+    for (int i = threadIdx.x; i < hidden; i += POOL_THREADS) o[i] = pool_smem[i] * scale;
+  }
+}
+
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+small_proj_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W,
+                  const float* __restrict__ bias, int n_rows, int hidden, int n_labels, float* __restrict__ out,
+                  int64_t out_row_stride) {
+  const int idx = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  if (idx >= n_rows * n_labels) return;
+  const int row = idx / n_labels, label = idx % n_labels;
+  const int lane = threadIdx.x & 31;
+  const __nv_bfloat16* xr = x + static_cast<size_t>(row) * hidden;
+  const __nv_bfloat16* wr = W + static_cast<size_t>(label) * hidden;
+  float acc = 0.f;
+  for (int c = lane; c < (hidden >> 3); c += 32) {
+    float a[8], b[8];
+    unpack8(*reinterpret_cast<const uint4*>(xr + c * 8), a);
+    unpack8(__ldg(reinterpret_cast<const uint4*>(wr + c * 8)), b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc += a[e] * b[e];
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) out[static_cast<size_t>(row) * out_row_stride + label] = acc + (bias != nullptr ? bias[label] : 0.f);
+}
+
+// ---- launchers ------------------------------------------------------------------
+
+static int check_hidden(int hidden, int max_chunks_per_lane) {
+  if (hidden <= 0 || (hidden % 8) != 0)
+    return set_error(B200EMB_ERR_UNSUPPORTED, "hidden size %d must be a positive multiple of 8", hidden);
+  if ((hidden >> 3) > 32 * max_chunks_per_lane)
+    return set_error(B200EMB_ERR_UNSUPPORTED, "hidden size %d too large for the row kernels", hidden);
+  return B200EMB_OK;
+}
+
+#define B2_DISPATCH_NCH(nch, CALL)                    \
+  switch (nch) {                                      \
+    case 1: { constexpr int NCH = 1; CALL; } break;   \
+    case 2: { constexpr int NCH = 2; CALL; } break;   \
+    case 3: { constexpr int NCH = 3; CALL; } break;   \
+    case 4: { constexpr int NCH = 4; CALL; } break;   \
+    case 5: case 6: case 7: case 8: { constexpr int NCH = 8; CALL; } break; \
+    default: { constexpr int NCH = 16; CALL; } break; \
+  }
+
+int launch_embed_ln(const int32_t* ids, const int32_t* types, const int32_t* d_cu, int n_seqs, int n_tokens,
+                    const void* word, const void* pos, const void* type_table, const float* gamma, const float* beta,
+                    int hidden, int pos_offset, float eps, void* out, cudaStream_t stream) {
+  if (n_tokens <= 0) return B200EMB_OK;
+  int rc = check_hidden(hidden, 16);
+  if (rc) return rc;
+  const int nch = ((hidden >> 3) + 31) / 32;
+  const int grid = (n_tokens + ROW_WARPS - 1) / ROW_WARPS;
+  B2_DISPATCH_NCH(nch, (embed_ln_kernel<NCH><<<grid, ROW_WARPS * 32, 0, stream>>>(
+                           ids, types, d_cu, n_seqs, n_tokens, reinterpret_cast<const __nv_bfloat16*>(word),
+                           reinterpret_cast<const __nv_bfloat16*>(pos),
+                           reinterpret_cast<const __nv_bfloat16*>(type_table), gamma, beta, hidden, pos_offset, eps,
+                           reinterpret_cast<__nv_bfloat16*>(out))));
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "embed_ln launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
+int launch_add_ln(const void* x, const void* y, const float* gamma, const float* beta, int n_rows, int hidden,
+                  float eps, void* out, cudaStream_t stream) {
+  if (n_rows <= 0) return B200EMB_OK;
+  int rc = check_hidden(hidden, 16);
+  if (rc) return rc;
+  const int nch = ((hidden >> 3) + 31) / 32;
+  const int grid = (n_rows + ROW_WARPS - 1) / ROW_WARPS;
+  B2_DISPATCH_NCH(nch, (add_ln_kernel<NCH><<<grid, ROW_WARPS * 32, 0, stream>>>(
+                           reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(y),
+                           gamma, beta, n_rows, hidden, eps, reinterpret_cast<__nv_bfloat16*>(out))));
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "add_ln launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
+int launch_pool(const void* x, const int32_t* d_cu, int n_seqs, int hidden, int pooling, int normalize, void* out,
+                int64_t out_row_stride, int out_bf16, cudaStream_t stream) {
+  if (n_seqs <= 0) return B200EMB_OK;
+  if (hidden <= 0 || (hidden % 8) != 0 || (hidden >> 3) > POOL_THREADS * POOL_MAXC)
+    return set_error(B200EMB_ERR_UNSUPPORTED, "pool: hidden size %d unsupported", hidden);
+  if (pooling < B200EMB_POOL_CLS || pooling > B200EMB_POOL_LAST)
+    return set_error(B200EMB_ERR_INVALID, "pool: unknown pooling %d", pooling);
+  const int n_chunks = hidden >> 3;
+  const int cols = n_chunks < POOL_THREADS ? n_chunks : POOL_THREADS;
+  const size_t smem = (static_cast<size_t>(POOL_THREADS / cols) * hidden + 32) * sizeof(float);
+  pool_kernel<<<n_seqs, POOL_THREADS, smem, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), d_cu, hidden,
+                                                      pooling, normalize, out, out_row_stride, out_bf16);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "pool launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
+int launch_small_proj(const void* x, const void* W, const float* bias, int n_rows, int hidden, int n_labels,
+                      float* out, int64_t out_row_stride, cudaStream_t stream) {
+  if (n_rows <= 0 || n_labels <= 0) return B200EMB_OK;
+  if ((hidden % 8) != 0) return set_error(B200EMB_ERR_UNSUPPORTED, "small_proj: hidden %d not a multiple of 8", hidden);
+  const long long total = static_cast<long long>(n_rows) * n_labels;
+  const int grid = static_cast<int>((total + ROW_WARPS - 1) / ROW_WARPS);
+  small_proj_kernel<<<grid, ROW_WARPS * 32, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x),
+                                                         reinterpret_cast<const __nv_bfloat16*>(W), bias, n_rows,
+                                                         hidden, n_labels, out, out_row_stride);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "small_proj launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
+}  // namespace b2

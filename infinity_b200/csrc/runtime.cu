@@ -1,0 +1,859 @@
+// Host runtime behind the C ABI: weight loading, per-device workspaces, the layer
+// sequence of one forward pass, token-balanced sharding over several devices, and the
+// single-kernel entry points used by the parity tests.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <chrono>
+#include <map>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "kernels.h"
+
+namespace b2 {
+
+// ---- errors -----------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+static std::mutex g_init_mu;
+static bool g_dev_inited[64] = {};
+
+int kernels_init_device() {
+  int dev = 0;
+  B2_CUDA_CHECK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lk(g_init_mu);
+  if (dev >= 0 && dev < 64 && g_dev_inited[dev]) return B200EMB_OK;
+  int rc = gemm_init_device();
+  if (!rc) rc = attention_init_device();
+  if (rc) return rc;
+  if (dev >= 0 && dev < 64) g_dev_inited[dev] = true;
+  return B200EMB_OK;
+}
+
+// ---- weight file --------------------------------------------------------------------
+// Layout (little endian): magic "B2EW0001", u32 n_tensors, u32 reserved, u64 data_offset,
+// then n_tensors entries {char name[64]; u32 dtype; u32 ndim; u64 dims[4]; u64 offset; u64 nbytes},
+// then the data region (offsets relative to data_offset, 256-byte aligned).
+struct TensorEntry {
+  char name[64];
+  uint32_t dtype;  // 0 = fp32, 1 = bf16, 2 = u8, 3 = i32
+  uint32_t ndim;
+  uint64_t dims[4];
+  uint64_t offset;
+  uint64_t nbytes;
+};
+static_assert(sizeof(TensorEntry) == 64 + 8 + 32 + 16, "weight-file entry layout");
+
+struct WeightFile {
+  std::vector<TensorEntry> entries;
+  std::vector<uint8_t> data;
+  std::map<std::string, int> index;
+};
+
+static int read_weight_file(const char* path, WeightFile* wf) {
+  FILE* f = fopen(path, "rb");
+  if (f == nullptr) return set_error(B200EMB_ERR_IO, "cannot open weight file %s", path);
+  char magic[8];
+  uint32_t n = 0, reserved = 0;
+  uint64_t data_offset = 0;
+  bool ok = fread(magic, 1, 8, f) == 8 && memcmp(magic, "B2EW0001", 8) == 0 && fread(&n, 4, 1, f) == 1 &&
+            fread(&reserved, 4, 1, f) == 1 && fread(&data_offset, 8, 1, f) == 1 && n < (1u << 20);
+  if (ok) {
+    wf->entries.resize(n);
+    ok = n == 0 || fread(wf->entries.data(), sizeof(TensorEntry), n, f) == n;
+  }
+  if (ok) {
+    fseek(f, 0, SEEK_END);
+    const long end = ftell(f);
+    ok = end >= (long)data_offset;
+    if (ok) {
+      wf->data.resize(end - data_offset);
+      fseek(f, (long)data_offset, SEEK_SET);
+      ok = wf->data.empty() || fread(wf->data.data(), 1, wf->data.size(), f) == wf->data.size();
+    }
+  }
+  fclose(f);
+  if (!ok) return set_error(B200EMB_ERR_IO, "weight file %s is truncated or not a b200emb weight file", path);
+  for (size_t i = 0; i < wf->entries.size(); ++i) {
+    TensorEntry& e = wf->entries[i];
+    e.name[63] = 0;
+    if (e.offset + e.nbytes > wf->data.size() || (e.offset & 255) != 0)
+      return set_error(B200EMB_ERR_IO, "weight file %s: tensor %s out of bounds", path, e.name);
+    wf->index[e.name] = (int)i;
+  }
+  return B200EMB_OK;
+}
+
+// ---- model --------------------------------------------------------------------------
+struct LayerW {
+  const __nv_bfloat16 *qkv_w, *o_w, *ffn1_w, *ffn2_w;
+  const float *qkv_b, *o_b, *ffn1_b, *ffn2_b;
+  const float *ln1_g, *ln1_b, *ln2_g, *ln2_b;
+};
+
+struct ModelW {
+  const __nv_bfloat16 *word, *pos, *type;
+  const float *emb_ln_g, *emb_ln_b;
+  std::vector<LayerW> layers;
+  const __nv_bfloat16 *head_dense_w, *head_out_w;
+  const float *head_dense_b, *head_out_b;
+};
+
+struct EventPair {
+  cudaEvent_t a, b;
+  int kclass;
+};
+
+struct DeviceCtx {
+  int dev = 0;
+  int sm_count = 0;
+  cudaStream_t stream = nullptr;
+  uint8_t* blob = nullptr;
+  ModelW w;
+  // workspaces (grown on demand)
+  int cap_tokens = 0, cap_seqs = 0, cap_tiles = 0;
+  int32_t *d_ids = nullptr, *d_types = nullptr, *d_cu = nullptr;
+  AttnTile* d_tiles = nullptr;
+  __nv_bfloat16 *x = nullptr, *x2 = nullptr, *qkv = nullptr, *ctx = nullptr, *y = nullptr, *ffn = nullptr;
+  __nv_bfloat16 *pooled = nullptr, *head_h = nullptr;
+  float* d_out = nullptr;
+  int* d_err = nullptr;
+  // pinned host staging
+  int32_t *h_ids = nullptr, *h_types = nullptr, *h_cu = nullptr;
+  AttnTile* h_tiles = nullptr;
+  float* h_out = nullptr;
+  int* h_err = nullptr;
+  cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+  std::vector<EventPair> kev;  // per-kernel event pairs (profiling mode)
+  size_t kev_used = 0;
+  // per-call bookkeeping
+  int launches = 0;
+  double gemm_flops = 0;
+  bool per_kernel = false;
+};
+
+}  // namespace b2
+
+struct b200emb_handle {
+  b200emb_model_desc desc;
+  int out_dim = 0;
+  std::vector<b2::DeviceCtx*> devs;
+  double cost_a = 1.0, cost_b = 0.0;
+};
+
+namespace b2 {
+
+template <typename T>
+static int dev_alloc(T** p, size_t count) {
+  if (*p != nullptr) {
+    cudaFree(*p);
+    *p = nullptr;
+  }
+  if (count == 0) count = 1;
+  B2_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(p), count * sizeof(T)));
+  return B200EMB_OK;
+}
+template <typename T>
+static int host_alloc(T** p, size_t count) {
+  if (*p != nullptr) {
+    cudaFreeHost(*p);
+    *p = nullptr;
+  }
+  if (count == 0) count = 1;
+  B2_CUDA_CHECK(cudaMallocHost(reinterpret_cast<void**>(p), count * sizeof(T)));
+  return B200EMB_OK;
+}
+
+static int ensure_capacity(b200emb_handle* h, DeviceCtx* c, int n_tokens, int n_seqs, int n_tiles) {
+  const b200emb_model_desc& d = h->desc;
+  int rc = 0;
+  if (n_tokens > c->cap_tokens) {
+    const size_t T = (size_t)std::max(n_tokens, std::max(d.max_tokens, 1024));
+    const size_t H = d.hidden, QKV = (size_t)(d.n_heads + 2 * d.n_kv_heads) * d.head_dim;
+    if (!rc) rc = dev_alloc(&c->d_ids, T);
+    if (!rc) rc = dev_alloc(&c->d_types, T);
+    if (!rc) rc = dev_alloc(&c->x, T * H);
+    if (!rc) rc = dev_alloc(&c->x2, T * H);
+    if (!rc) rc = dev_alloc(&c->y, T * H);
+    if (!rc) rc = dev_alloc(&c->ctx, T * (size_t)d.n_heads * d.head_dim);
+    if (!rc) rc = dev_alloc(&c->qkv, T * QKV);
+    if (!rc) rc = dev_alloc(&c->ffn, T * (size_t)d.ffn);
+    if (!rc) rc = host_alloc(&c->h_ids, T);
+    if (!rc) rc = host_alloc(&c->h_types, T);
+    if (rc) return rc;
+    c->cap_tokens = (int)T;
+  }
+  if (n_seqs > c->cap_seqs) {
+    const size_t B = (size_t)std::max(n_seqs, 256);
+    if (!rc) rc = dev_alloc(&c->d_cu, B + 1);
+    if (!rc) rc = dev_alloc(&c->d_out, B * (size_t)h->out_dim);
+    if (!rc) rc = dev_alloc(&c->pooled, B * (size_t)d.hidden);
+    if (!rc) rc = dev_alloc(&c->head_h, B * (size_t)d.hidden);
+    if (!rc) rc = host_alloc(&c->h_cu, B + 1);
+    if (!rc) rc = host_alloc(&c->h_out, B * (size_t)h->out_dim);
+    if (rc) return rc;
+    c->cap_seqs = (int)B;
+  }
+  if (n_tiles > c->cap_tiles) {
+    const size_t NT = (size_t)std::max(n_tiles, 1024);
+    if (!rc) rc = dev_alloc(&c->d_tiles, NT);
+    if (!rc) rc = host_alloc(&c->h_tiles, NT);
+    if (rc) return rc;
+    c->cap_tiles = (int)NT;
+  }
+  return B200EMB_OK;
+}
+
+template <typename T>
+static int lookup(const WeightFile& wf, const uint8_t* blob, const char* name, uint32_t dtype, uint64_t elems,
+                  const T** out, bool optional = false) {
+  auto it = wf.index.find(name);
+  if (it == wf.index.end()) {
+    *out = nullptr;
+    if (optional) return B200EMB_OK;
+    return set_error(B200EMB_ERR_IO, "weight file lacks tensor %s", name);
+  }
+  const TensorEntry& e = wf.entries[it->second];
+  uint64_t n = 1;
+  for (uint32_t i = 0; i < e.ndim && i < 4; ++i) n *= e.dims[i];
+  if (e.dtype != dtype || n != elems)
+    return set_error(B200EMB_ERR_IO, "tensor %s: expected dtype %u with %llu elements, file has dtype %u with %llu",
+                     name, dtype, (unsigned long long)elems, e.dtype, (unsigned long long)n);
+  *out = reinterpret_cast<const T*>(blob + e.offset);
+  return B200EMB_OK;
+}
+
+static int bind_weights(const b200emb_model_desc& d, const WeightFile& wf, DeviceCtx* c) {
+  const uint64_t H = d.hidden, F = d.ffn, QKV = (uint64_t)(d.n_heads + 2 * d.n_kv_heads) * d.head_dim;
+  const uint64_t HQ = (uint64_t)d.n_heads * d.head_dim;
+  const uint8_t* b = c->blob;
+  ModelW& w = c->w;
+  int rc = lookup(wf, b, "emb.word", 1, (uint64_t)d.vocab * H, &w.word);
+  if (!rc) rc = lookup(wf, b, "emb.pos", 1, (uint64_t)d.max_pos * H, &w.pos);
+  if (!rc && d.type_vocab > 0) rc = lookup(wf, b, "emb.type", 1, (uint64_t)d.type_vocab * H, &w.type);
+  if (d.type_vocab <= 0) w.type = nullptr;
+  if (!rc) rc = lookup(wf, b, "emb.ln.g", 0, H, &w.emb_ln_g);
+  if (!rc) rc = lookup(wf, b, "emb.ln.b", 0, H, &w.emb_ln_b);
+  w.layers.resize(d.n_layers);
+  char nm[96];
+  for (int l = 0; l < d.n_layers && !rc; ++l) {
+    LayerW& L = w.layers[l];
+#define B2_LK(field, suffix, dt, n)                         \
+  if (!rc) {                                                \
+    snprintf(nm, sizeof(nm), "layer.%d." suffix, l);        \
+    rc = lookup(wf, b, nm, dt, n, &L.field);                \
+  }
+    B2_LK(qkv_w, "qkv.w", 1, QKV * H)
+    B2_LK(qkv_b, "qkv.b", 0, QKV)
+    B2_LK(o_w, "o.w", 1, H * HQ)
+    B2_LK(o_b, "o.b", 0, H)
+    B2_LK(ln1_g, "ln1.g", 0, H)
+    B2_LK(ln1_b, "ln1.b", 0, H)
+    B2_LK(ffn1_w, "ffn1.w", 1, F * H)
+    B2_LK(ffn1_b, "ffn1.b", 0, F)
+    B2_LK(ffn2_w, "ffn2.w", 1, H * F)
+    B2_LK(ffn2_b, "ffn2.b", 0, H)
+    B2_LK(ln2_g, "ln2.g", 0, H)
+    B2_LK(ln2_b, "ln2.b", 0, H)
+#undef B2_LK
+  }
+  if (!rc && d.head == B200EMB_HEAD_CLASSIFIER) {
+    rc = lookup(wf, b, "head.dense.w", 1, H * H, &w.head_dense_w);
+    if (!rc) rc = lookup(wf, b, "head.dense.b", 0, H, &w.head_dense_b);
+    if (!rc) rc = lookup(wf, b, "head.out.w", 1, (uint64_t)d.n_labels * H, &w.head_out_w);
+    if (!rc) rc = lookup(wf, b, "head.out.b", 0, (uint64_t)d.n_labels, &w.head_out_b);
+  }
+  return rc;
+}
+
+static void destroy_ctx(DeviceCtx* c) {
+  if (c == nullptr) return;
+  cudaSetDevice(c->dev);
+  if (c->stream) cudaStreamSynchronize(c->stream);
+  cudaFree(c->blob);
+  cudaFree(c->d_ids); cudaFree(c->d_types); cudaFree(c->d_cu); cudaFree(c->d_tiles);
+  cudaFree(c->x); cudaFree(c->x2); cudaFree(c->qkv); cudaFree(c->ctx); cudaFree(c->y); cudaFree(c->ffn);
+  cudaFree(c->pooled); cudaFree(c->head_h); cudaFree(c->d_out); cudaFree(c->d_err);
+  cudaFreeHost(c->h_ids); cudaFreeHost(c->h_types); cudaFreeHost(c->h_cu); cudaFreeHost(c->h_tiles);
+  cudaFreeHost(c->h_out); cudaFreeHost(c->h_err);
+  for (auto& e : c->ev) if (e) cudaEventDestroy(e);
+  for (auto& p : c->kev) { cudaEventDestroy(p.a); cudaEventDestroy(p.b); }
+  if (c->stream) cudaStreamDestroy(c->stream);
+  delete c;
+}
+
+static int validate_desc(const b200emb_model_desc& d) {
+  if (d.abi_version != B200EMB_ABI_VERSION) return set_error(B200EMB_ERR_INVALID, "abi_version %d != %d", d.abi_version, B200EMB_ABI_VERSION);
+  if (d.arch != B200EMB_ARCH_BERT && d.arch != B200EMB_ARCH_XLMR)
+    return set_error(B200EMB_ERR_UNSUPPORTED, "arch %d: only the post-LayerNorm encoders (BERT, XLM-R) are built", d.arch);
+  if (d.weight_format != B200EMB_WFMT_BF16) return set_error(B200EMB_ERR_UNSUPPORTED, "weight_format %d: only bf16 is built", d.weight_format);
+  if (d.n_layers <= 0 || d.hidden <= 0 || d.n_heads <= 0 || d.ffn <= 0 || d.vocab <= 0 || d.max_pos <= 0)
+    return set_error(B200EMB_ERR_INVALID, "model dimensions must be positive");
+  if (d.n_kv_heads != d.n_heads) return set_error(B200EMB_ERR_UNSUPPORTED, "grouped-query attention needs the decoder arch");
+  if (d.head_dim != 32 && d.head_dim != 64 && d.head_dim != 128) return set_error(B200EMB_ERR_UNSUPPORTED, "head_dim %d not in {32, 64, 128}", d.head_dim);
+  if (d.n_heads * d.head_dim != d.hidden) return set_error(B200EMB_ERR_INVALID, "n_heads * head_dim must equal hidden");
+  if (d.hidden % 8 || d.ffn % 8) return set_error(B200EMB_ERR_UNSUPPORTED, "hidden and ffn must be multiples of 8");
+  if (d.pooling < B200EMB_POOL_CLS || d.pooling > B200EMB_POOL_LAST) return set_error(B200EMB_ERR_INVALID, "unknown pooling %d", d.pooling);
+  if (d.head == B200EMB_HEAD_CLASSIFIER && d.n_labels <= 0) return set_error(B200EMB_ERR_INVALID, "classifier head needs n_labels > 0");
+  if (d.head != B200EMB_HEAD_NONE && d.head != B200EMB_HEAD_CLASSIFIER) return set_error(B200EMB_ERR_INVALID, "unknown head %d", d.head);
+  if (d.pos_offset < 0 || d.pos_offset >= d.max_pos) return set_error(B200EMB_ERR_INVALID, "pos_offset out of range");
+  return B200EMB_OK;
+}
+
+// ---- one forward pass on one device -------------------------------------------------------
+struct KernelScope {  // brackets one launch with events in profiling mode and counts it
+  DeviceCtx* c;
+  int idx = -1;
+  KernelScope(DeviceCtx* c_, int kclass) : c(c_) {
+    c->launches++;
+    if (!c->per_kernel) return;
+    if (c->kev_used == c->kev.size()) {
+      EventPair p;
+      p.kclass = kclass;
+      if (cudaEventCreate(&p.a) != cudaSuccess || cudaEventCreate(&p.b) != cudaSuccess) return;
+      c->kev.push_back(p);
+    }
+    idx = (int)c->kev_used++;
+    c->kev[idx].kclass = kclass;
+    cudaEventRecord(c->kev[idx].a, c->stream);
+  }
+  ~KernelScope() {
+    if (idx >= 0) cudaEventRecord(c->kev[idx].b, c->stream);
+  }
+};
+
+static int gemm(DeviceCtx* c, const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int epi) {
+  KernelScope ks(c, B200EMB_KCLASS_GEMM);
+  c->gemm_flops += 2.0 * M * N * K;
+  return launch_gemm_bf16(A, W, bias, C, M, N, K, epi, c->sm_count, c->d_err, c->stream, 0);
+}
+
+// Enqueues every kernel of one forward on c->stream. Inputs are on the device.
+static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids, const int32_t* d_types,
+                           const int32_t* d_cu, int n_seqs, int n_tokens, int n_tiles, float* d_out,
+                           int64_t out_row_stride) {
+  const b200emb_model_desc& d = h->desc;
+  const ModelW& w = c->w;
+  const int H = d.hidden, F = d.ffn, T = n_tokens;
+  const int QKV = (d.n_heads + 2 * d.n_kv_heads) * d.head_dim;
+  int rc;
+  {
+    KernelScope ks(c, B200EMB_KCLASS_EMBED);
+    rc = launch_embed_ln(d_ids, w.type != nullptr ? d_types : nullptr, d_cu, n_seqs, T, w.word, w.pos, w.type,
+                         w.emb_ln_g, w.emb_ln_b, H, d.pos_offset, d.norm_eps, c->x, c->stream);
+    if (rc) return rc;
+  }
+  for (int l = 0; l < d.n_layers; ++l) {
+    const LayerW& L = w.layers[l];
+    rc = gemm(c, c->x, L.qkv_w, L.qkv_b, c->qkv, T, QKV, H, EPI_BIAS);
+    if (rc) return rc;
+    {
+      KernelScope ks(c, B200EMB_KCLASS_ATTN);
+      rc = launch_attention(c->qkv, c->ctx, c->d_tiles, n_tiles, d.n_heads, d.n_kv_heads, d.head_dim, 0, c->stream);
+      if (rc) return rc;
+    }
+    rc = gemm(c, c->ctx, L.o_w, L.o_b, c->y, T, H, d.n_heads * d.head_dim, EPI_BIAS);
+    if (rc) return rc;
+    {
+      KernelScope ks(c, B200EMB_KCLASS_NORM);
+      rc = launch_add_ln(c->x, c->y, L.ln1_g, L.ln1_b, T, H, d.norm_eps, c->x2, c->stream);
+      if (rc) return rc;
+    }
+    rc = gemm(c, c->x2, L.ffn1_w, L.ffn1_b, c->ffn, T, F, H, EPI_BIAS_GELU);
+    if (rc) return rc;
+    rc = gemm(c, c->ffn, L.ffn2_w, L.ffn2_b, c->y, T, H, F, EPI_BIAS);
+    if (rc) return rc;
+    {
+      KernelScope ks(c, B200EMB_KCLASS_NORM);
+      rc = launch_add_ln(c->x2, c->y, L.ln2_g, L.ln2_b, T, H, d.norm_eps, c->x, c->stream);
+      if (rc) return rc;
+    }
+  }
+  if (d.head == B200EMB_HEAD_NONE) {
+    KernelScope ks(c, B200EMB_KCLASS_POOL);
+    rc = launch_pool(c->x, d_cu, n_seqs, H, d.pooling, d.normalize, d_out, out_row_stride, 0, c->stream);
+    if (rc) return rc;
+  } else {
+    {
+      KernelScope ks(c, B200EMB_KCLASS_POOL);
+      rc = launch_pool(c->x, d_cu, n_seqs, H, d.pooling, 0, c->pooled, H, 1, c->stream);
+      if (rc) return rc;
+    }
+    rc = gemm(c, c->pooled, w.head_dense_w, w.head_dense_b, c->head_h, n_seqs, H, H, EPI_BIAS_TANH);
+    if (rc) return rc;
+    {
+      KernelScope ks(c, B200EMB_KCLASS_OTHER);
+      rc = launch_small_proj(c->head_h, w.head_out_w, w.head_out_b, n_seqs, H, d.n_labels, d_out, out_row_stride,
+                             c->stream);
+      if (rc) return rc;
+    }
+  }
+  return B200EMB_OK;
+}
+
+static int validate_batch(const b200emb_model_desc& d, const int32_t* ids, const int32_t* types, const int32_t* cu,
+                          int n_seqs, int n_tokens) {
+  if (n_seqs < 0 || n_tokens < 0) return set_error(B200EMB_ERR_INVALID, "negative batch size");
+  if (n_seqs == 0) {
+    if (n_tokens != 0) return set_error(B200EMB_ERR_INVALID, "n_tokens must be 0 for an empty batch");
+    return B200EMB_OK;
+  }
+  if (ids == nullptr || cu == nullptr) return set_error(B200EMB_ERR_INVALID, "null input pointer");
+  if (cu[0] != 0) return set_error(B200EMB_ERR_INVALID, "cu_seqlens[0] must be 0");
+  for (int i = 0; i < n_seqs; ++i) {
+    const int len = cu[i + 1] - cu[i];
+    if (len <= 0) return set_error(B200EMB_ERR_INVALID, "cu_seqlens must be strictly increasing (sequence %d has length %d)", i, len);
+    if (len + d.pos_offset > d.max_pos)
+      return set_error(B200EMB_ERR_INVALID, "sequence %d has %d tokens; the position table holds %d", i, len, d.max_pos - d.pos_offset);
+  }
+  if (cu[n_seqs] != n_tokens) return set_error(B200EMB_ERR_INVALID, "cu_seqlens[n_seqs] = %d != n_tokens = %d", cu[n_seqs], n_tokens);
+  for (int t = 0; t < n_tokens; ++t) {
+    if (ids[t] < 0 || ids[t] >= d.vocab) return set_error(B200EMB_ERR_INVALID, "input_ids[%d] = %d outside the vocabulary of %d", t, ids[t], d.vocab);
+  }
+  if (types != nullptr && d.type_vocab > 0) {
+    for (int t = 0; t < n_tokens; ++t)
+      if (types[t] < 0 || types[t] >= d.type_vocab) return set_error(B200EMB_ERR_INVALID, "token_type_ids[%d] = %d out of range", t, types[t]);
+  }
+  return B200EMB_OK;
+}
+
+struct ShardResult {
+  int rc = 0;
+  std::string msg;
+  float h2d_ms = 0, kernels_ms = 0, d2h_ms = 0;
+};
+
+static void collect_kernel_times(DeviceCtx* c, b200emb_timing* timing) {
+  for (size_t i = 0; i < c->kev_used; ++i) {
+    float ms = 0;
+    if (cudaEventElapsedTime(&ms, c->kev[i].a, c->kev[i].b) == cudaSuccess) {
+      timing->kclass_ms[c->kev[i].kclass] += ms;
+      timing->kclass_launches[c->kev[i].kclass] += 1;
+    }
+  }
+}
+
+// Runs one shard (host inputs, shard-local cu_seqlens) on device context c and leaves the
+// result rows in dst (row stride dst_stride floats).
+static void run_shard(b200emb_handle* h, DeviceCtx* c, const int32_t* ids, const int32_t* types, const int32_t* cu,
+                      int n_seqs, int n_tokens, float* dst, int64_t dst_stride, bool per_kernel, ShardResult* res) {
+  auto fail = [&](int rc) {
+    res->rc = rc;
+    res->msg = g_err;
+  };
+  if (cudaSetDevice(c->dev) != cudaSuccess) return fail(set_error(B200EMB_ERR_CUDA, "cudaSetDevice(%d) failed", c->dev));
+  c->launches = 0;
+  c->gemm_flops = 0;
+  c->per_kernel = per_kernel;
+  c->kev_used = 0;
+  if (n_seqs == 0) return;
+  const int n_tiles = attention_build_tiles(cu, n_seqs, nullptr);
+  int rc = ensure_capacity(h, c, n_tokens, n_seqs, n_tiles);
+  if (rc) return fail(rc);
+  attention_build_tiles(cu, n_seqs, c->h_tiles);
+  cudaStream_t s = c->stream;
+  const bool use_types = types != nullptr && h->desc.type_vocab > 0;
+#define B2_TRY(expr)                                                                              \
+  do {                                                                                            \
+    cudaError_t e__ = (expr);                                                                     \
+    if (e__ != cudaSuccess) return fail(set_error(B200EMB_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e__))); \
+  } while (0)
+  B2_TRY(cudaEventRecord(c->ev[0], s));
+  B2_TRY(cudaMemcpyAsync(c->d_ids, ids, sizeof(int32_t) * n_tokens, cudaMemcpyHostToDevice, s));
+  if (use_types) B2_TRY(cudaMemcpyAsync(c->d_types, types, sizeof(int32_t) * n_tokens, cudaMemcpyHostToDevice, s));
+  B2_TRY(cudaMemcpyAsync(c->d_cu, cu, sizeof(int32_t) * (n_seqs + 1), cudaMemcpyHostToDevice, s));
+  B2_TRY(cudaMemcpyAsync(c->d_tiles, c->h_tiles, sizeof(AttnTile) * n_tiles, cudaMemcpyHostToDevice, s));
+  B2_TRY(cudaEventRecord(c->ev[1], s));
+  rc = enqueue_forward(h, c, c->d_ids, use_types ? c->d_types : nullptr, c->d_cu, n_seqs, n_tokens, n_tiles, c->d_out,
+                       h->out_dim);
+  if (rc) {
+    cudaStreamSynchronize(s);
+    return fail(rc);
+  }
+  B2_TRY(cudaEventRecord(c->ev[2], s));
+  B2_TRY(cudaMemcpy2DAsync(dst, sizeof(float) * dst_stride, c->d_out, sizeof(float) * h->out_dim,
+                           sizeof(float) * h->out_dim, n_seqs, cudaMemcpyDeviceToHost, s));
+  B2_TRY(cudaMemcpyAsync(c->h_err, c->d_err, sizeof(int), cudaMemcpyDeviceToHost, s));
+  B2_TRY(cudaEventRecord(c->ev[3], s));
+  B2_TRY(cudaStreamSynchronize(s));
+#undef B2_TRY
+  cudaEventElapsedTime(&res->h2d_ms, c->ev[0], c->ev[1]);
+  cudaEventElapsedTime(&res->kernels_ms, c->ev[1], c->ev[2]);
+  cudaEventElapsedTime(&res->d2h_ms, c->ev[2], c->ev[3]);
+  if (*c->h_err != 0) {
+    const int code = *c->h_err;
+    cudaMemsetAsync(c->d_err, 0, sizeof(int), s);
+    cudaStreamSynchronize(s);
+    return fail(set_error(B200EMB_ERR_DEVICE_WAIT, "a device-side wait gave up (role %d) on device %d", code, c->dev));
+  }
+}
+
+static void partition_lpt(const int32_t* lens, int n, int n_shards, double a, double b, int32_t* shard_of) {
+  std::vector<int> order(n);
+  for (int i = 0; i < n; ++i) order[i] = i;
+  auto cost = [&](int i) { return a * lens[i] + b * (double)lens[i] * lens[i]; };
+  std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return cost(x) > cost(y); });
+  std::vector<double> load(n_shards, 0.0);
+  for (int idx = 0; idx < n; ++idx) {
+    const int i = order[idx];
+    int best = 0;
+    for (int s = 1; s < n_shards; ++s)
+      if (load[s] < load[best]) best = s;
+    shard_of[i] = best;
+    load[best] += cost(i);
+  }
+}
+
+}  // namespace b2
+
+// =====================================================================================
+// C ABI
+// =====================================================================================
+using namespace b2;
+
+extern "C" {
+
+const char* b200emb_last_error(void) { return g_err; }
+
+int b200emb_device_count(void) {
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess) return -set_error(B200EMB_ERR_CUDA, "cudaGetDeviceCount: %s", cudaGetErrorString(e));
+  return n;
+}
+
+int b200emb_partition(const int32_t* lens, int32_t n_seqs, int32_t n_shards, double cost_linear,
+                      double cost_quadratic, int32_t* shard_of) {
+  if (n_seqs < 0 || n_shards <= 0 || (n_seqs > 0 && (lens == nullptr || shard_of == nullptr)))
+    return set_error(B200EMB_ERR_INVALID, "partition: bad arguments");
+  partition_lpt(lens, n_seqs, n_shards, cost_linear, cost_quadratic, shard_of);
+  return B200EMB_OK;
+}
+
+int b200emb_create(const b200emb_model_desc* desc, const char* weight_path, const int32_t* device_ids,
+                   int32_t n_devices, b200emb_handle** out) {
+  if (desc == nullptr || weight_path == nullptr || out == nullptr || n_devices <= 0 || device_ids == nullptr)
+    return set_error(B200EMB_ERR_INVALID, "create: null argument or no device");
+  *out = nullptr;
+  int rc = validate_desc(*desc);
+  if (rc) return rc;
+  int visible = 0;
+  if (cudaGetDeviceCount(&visible) != cudaSuccess || visible <= 0)
+    return set_error(B200EMB_ERR_CUDA, "no CUDA device is usable; this library has no CPU path");
+  for (int i = 0; i < n_devices; ++i)
+    if (device_ids[i] < 0 || device_ids[i] >= visible)
+      return set_error(B200EMB_ERR_INVALID, "device id %d not in [0, %d)", device_ids[i], visible);
+  WeightFile wf;
+  rc = read_weight_file(weight_path, &wf);
+  if (rc) return rc;
+
+  b200emb_handle* h = new b200emb_handle();
+  h->desc = *desc;
+  h->out_dim = desc->head == B200EMB_HEAD_CLASSIFIER ? desc->n_labels : desc->hidden;
+  {
+    const double H = desc->hidden, F = desc->ffn;
+    const double QKV = (double)(desc->n_heads + 2 * desc->n_kv_heads) * desc->head_dim;
+    h->cost_a = 2.0 * H * QKV + 2.0 * H * H + 4.0 * H * F;  // GEMM flops per token per layer
+    h->cost_b = 4.0 * H;                                     // attention flops per token pair per layer
+  }
+  for (int i = 0; i < n_devices && !rc; ++i) {
+    DeviceCtx* c = new DeviceCtx();
+    h->devs.push_back(c);
+    c->dev = device_ids[i];
+    cudaError_t e = cudaSetDevice(c->dev);
+    cudaDeviceProp prop;
+    if (e == cudaSuccess) e = cudaGetDeviceProperties(&prop, c->dev);
+    if (e != cudaSuccess) {
+      rc = set_error(B200EMB_ERR_CUDA, "device %d: %s", c->dev, cudaGetErrorString(e));
+      break;
+    }
+    if (prop.major != 10) {
+      rc = set_error(B200EMB_ERR_UNSUPPORTED, "device %d is sm_%d%d; the kernels are built for sm_100a only", c->dev,
+                     prop.major, prop.minor);
+      break;
+    }
+    c->sm_count = prop.multiProcessorCount;
+    rc = kernels_init_device();
+    if (rc) break;
+#define B2_CR(expr)                                                                                   \
+  if (!rc) {                                                                                          \
+    cudaError_t e2 = (expr);                                                                          \
+    if (e2 != cudaSuccess) rc = set_error(B200EMB_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e2)); \
+  }
+    B2_CR(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+    for (int k = 0; k < 4; ++k) B2_CR(cudaEventCreate(&c->ev[k]));
+    B2_CR(cudaMalloc(reinterpret_cast<void**>(&c->blob), std::max<size_t>(wf.data.size(), 256)));
+    B2_CR(cudaMemcpy(c->blob, wf.data.data(), wf.data.size(), cudaMemcpyHostToDevice));
+    B2_CR(cudaMalloc(reinterpret_cast<void**>(&c->d_err), sizeof(int)));
+    B2_CR(cudaMemset(c->d_err, 0, sizeof(int)));
+    B2_CR(cudaMallocHost(reinterpret_cast<void**>(&c->h_err), sizeof(int)));
+#undef B2_CR
+    if (!rc) rc = bind_weights(*desc, wf, c);
+    if (!rc) rc = ensure_capacity(h, c, std::max(desc->max_tokens, 1), 256, 1024);
+  }
+  if (rc) {
+    std::string keep = g_err;
+    b200emb_destroy(h);
+    snprintf(g_err, sizeof(g_err), "%s", keep.c_str());
+    return rc;
+  }
+  *out = h;
+  return B200EMB_OK;
+}
+
+int b200emb_destroy(b200emb_handle* h) {
+  if (h == nullptr) return B200EMB_OK;
+  for (DeviceCtx* c : h->devs) destroy_ctx(c);
+  delete h;
+  return B200EMB_OK;
+}
+
+int b200emb_forward(b200emb_handle* h, const int32_t* input_ids, const int32_t* token_type_ids,
+                    const int32_t* cu_seqlens, int32_t n_seqs, int32_t n_tokens, float* out, int64_t out_row_stride,
+                    b200emb_timing* timing) {
+  if (h == nullptr) return set_error(B200EMB_ERR_INVALID, "null handle");
+  const auto t0 = std::chrono::steady_clock::now();
+  int rc = validate_batch(h->desc, input_ids, token_type_ids, cu_seqlens, n_seqs, n_tokens);
+  if (rc) return rc;
+  if (n_seqs > 0 && (out == nullptr || out_row_stride < h->out_dim))
+    return set_error(B200EMB_ERR_INVALID, "output buffer missing or row stride %lld < %d", (long long)out_row_stride, h->out_dim);
+  const bool per_kernel = timing != nullptr && timing->per_kernel != 0;
+  const int G = (int)h->devs.size();
+  std::vector<ShardResult> res(G);
+
+  if (G == 1 || n_seqs < 2) {
+    run_shard(h, h->devs[0], input_ids, token_type_ids, cu_seqlens, n_seqs, n_tokens, out, out_row_stride, per_kernel,
+              &res[0]);
+  } else {
+    // Token-balanced split: whole sequences go to the least-loaded device, most expensive
+    // first; each device gets its own packed ids / cu_seqlens; rows return to batch order.
+    std::vector<int32_t> lens(n_seqs), shard_of(n_seqs);
+    for (int i = 0; i < n_seqs; ++i) lens[i] = cu_seqlens[i + 1] - cu_seqlens[i];
+    partition_lpt(lens.data(), n_seqs, G, h->cost_a, h->cost_b, shard_of.data());
+    std::vector<std::vector<int>> members(G);
+    for (int i = 0; i < n_seqs; ++i) members[shard_of[i]].push_back(i);
+    std::vector<std::thread> threads;
+    for (int g = 0; g < G; ++g) {
+      threads.emplace_back([&, g]() {
+        DeviceCtx* c = h->devs[g];
+        const std::vector<int>& mem = members[g];
+        int tok = 0;
+        for (int i : mem) tok += lens[i];
+        ShardResult* r = &res[g];
+        if (mem.empty()) return;
+        if (cudaSetDevice(c->dev) != cudaSuccess) {
+          r->rc = B200EMB_ERR_CUDA;
+          r->msg = "cudaSetDevice failed";
+          return;
+        }
+        int rc2 = ensure_capacity(h, c, tok, (int)mem.size(), 0);
+        if (rc2) {
+          r->rc = rc2;
+          r->msg = g_err;
+          return;
+        }
+        int pos = 0;
+        c->h_cu[0] = 0;
+        for (size_t k = 0; k < mem.size(); ++k) {
+          const int i = mem[k];
+          memcpy(c->h_ids + pos, input_ids + cu_seqlens[i], sizeof(int32_t) * lens[i]);
+          if (token_type_ids != nullptr) memcpy(c->h_types + pos, token_type_ids + cu_seqlens[i], sizeof(int32_t) * lens[i]);
+          pos += lens[i];
+          c->h_cu[k + 1] = pos;
+        }
+        run_shard(h, c, c->h_ids, token_type_ids != nullptr ? c->h_types : nullptr, c->h_cu, (int)mem.size(), tok,
+                  c->h_out, h->out_dim, per_kernel, r);
+        if (r->rc == 0) {
+          for (size_t k = 0; k < mem.size(); ++k)
+            memcpy(out + (size_t)mem[k] * out_row_stride, c->h_out + k * (size_t)h->out_dim, sizeof(float) * h->out_dim);
+        }
+      });
+    }
+    for (auto& t : threads) t.join();
+  }
+
+  for (int g = 0; g < G; ++g)
+    if (res[g].rc != 0) return set_error(res[g].rc, "%s", res[g].msg.c_str());
+  if (timing != nullptr) {
+    const int pk = timing->per_kernel;
+    memset(timing, 0, sizeof(*timing));
+    timing->per_kernel = pk;
+    timing->n_devices = G;
+    for (int g = 0; g < G; ++g) {
+      timing->h2d_ms = std::max(timing->h2d_ms, res[g].h2d_ms);
+      timing->kernels_ms = std::max(timing->kernels_ms, res[g].kernels_ms);
+      timing->d2h_ms = std::max(timing->d2h_ms, res[g].d2h_ms);
+      timing->launches += h->devs[g]->launches;
+    }
+    timing->gemm_flops = h->devs[0]->gemm_flops;
+    if (per_kernel) {
+      cudaSetDevice(h->devs[0]->dev);
+      collect_kernel_times(h->devs[0], timing);
+    }
+    timing->total_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+  }
+  return B200EMB_OK;
+}
+
+int b200emb_forward_device(b200emb_handle* h, const int32_t* d_input_ids, const int32_t* d_token_type_ids,
+                           const int32_t* d_cu_seqlens, const int32_t* h_cu_seqlens, int32_t n_seqs, int32_t n_tokens,
+                           float* d_out, int64_t out_row_stride, b200emb_timing* timing) {
+  if (h == nullptr) return set_error(B200EMB_ERR_INVALID, "null handle");
+  if (h->devs.size() != 1) return set_error(B200EMB_ERR_UNSUPPORTED, "forward_device needs a single-device handle");
+  if (n_seqs <= 0 || n_tokens <= 0 || d_input_ids == nullptr || d_cu_seqlens == nullptr || h_cu_seqlens == nullptr ||
+      d_out == nullptr || out_row_stride < h->out_dim)
+    return set_error(B200EMB_ERR_INVALID, "forward_device: bad arguments");
+  if (h_cu_seqlens[0] != 0 || h_cu_seqlens[n_seqs] != n_tokens)
+    return set_error(B200EMB_ERR_INVALID, "forward_device: cu_seqlens does not span n_tokens");
+  for (int i = 0; i < n_seqs; ++i) {
+    const int len = h_cu_seqlens[i + 1] - h_cu_seqlens[i];
+    if (len <= 0 || len + h->desc.pos_offset > h->desc.max_pos)
+      return set_error(B200EMB_ERR_INVALID, "forward_device: sequence %d has invalid length %d", i, len);
+  }
+  const auto t0 = std::chrono::steady_clock::now();
+  DeviceCtx* c = h->devs[0];
+  B2_CUDA_CHECK(cudaSetDevice(c->dev));
+  c->launches = 0;
+  c->gemm_flops = 0;
+  c->per_kernel = timing != nullptr && timing->per_kernel != 0;
+  c->kev_used = 0;
+  const int n_tiles = attention_build_tiles(h_cu_seqlens, n_seqs, nullptr);
+  int rc = ensure_capacity(h, c, n_tokens, n_seqs, n_tiles);
+  if (rc) return rc;
+  attention_build_tiles(h_cu_seqlens, n_seqs, c->h_tiles);
+  cudaStream_t s = c->stream;
+  B2_CUDA_CHECK(cudaEventRecord(c->ev[0], s));
+  B2_CUDA_CHECK(cudaMemcpyAsync(c->d_tiles, c->h_tiles, sizeof(AttnTile) * n_tiles, cudaMemcpyHostToDevice, s));
+  B2_CUDA_CHECK(cudaEventRecord(c->ev[1], s));
+  rc = enqueue_forward(h, c, d_input_ids, d_token_type_ids, d_cu_seqlens, n_seqs, n_tokens, n_tiles, d_out,
+                       out_row_stride);
+  if (rc) {
+    cudaStreamSynchronize(s);
+    return rc;
+  }
+  B2_CUDA_CHECK(cudaEventRecord(c->ev[2], s));
+  B2_CUDA_CHECK(cudaMemcpyAsync(c->h_err, c->d_err, sizeof(int), cudaMemcpyDeviceToHost, s));
+  B2_CUDA_CHECK(cudaStreamSynchronize(s));
+  if (*c->h_err != 0) {
+    const int code = *c->h_err;
+    cudaMemsetAsync(c->d_err, 0, sizeof(int), s);
+    cudaStreamSynchronize(s);
+    return set_error(B200EMB_ERR_DEVICE_WAIT, "a device-side wait gave up (role %d)", code);
+  }
+  if (timing != nullptr) {
+    const int pk = timing->per_kernel;
+    memset(timing, 0, sizeof(*timing));
+    timing->per_kernel = pk;
+    timing->n_devices = 1;
+    cudaEventElapsedTime(&timing->h2d_ms, c->ev[0], c->ev[1]);
+    cudaEventElapsedTime(&timing->kernels_ms, c->ev[1], c->ev[2]);
+    timing->launches = c->launches;
+    timing->gemm_flops = c->gemm_flops;
+    if (pk) collect_kernel_times(c, timing);
+    timing->total_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+  }
+  return B200EMB_OK;
+}
+
+// ---- single kernels ---------------------------------------------------------------------
+
+static int current_sm_count(int* out) {
+  int dev = 0;
+  B2_CUDA_CHECK(cudaGetDevice(&dev));
+  B2_CUDA_CHECK(cudaDeviceGetAttribute(out, cudaDevAttrMultiProcessorCount, dev));
+  return B200EMB_OK;
+}
+
+int b200emb_op_gemm_bf16(const void* A, const void* W, const float* bias, void* C, int32_t M, int32_t N, int32_t K,
+                         int32_t epilogue, void* stream) {
+  if (A == nullptr || W == nullptr || C == nullptr) return set_error(B200EMB_ERR_INVALID, "gemm: null pointer");
+  int rc = kernels_init_device();
+  if (rc) return rc;
+  int sms = 0;
+  rc = current_sm_count(&sms);
+  if (rc) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int* d_err = nullptr;
+  B2_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&d_err), sizeof(int)));
+  cudaMemsetAsync(d_err, 0, sizeof(int), s);
+  // epilogue values >= 0x100 select the tile width in the upper bits (tests only): (bn << 8) | epi
+  const int force_bn = epilogue >> 8;
+  rc = launch_gemm_bf16(A, W, bias, C, M, N, K, epilogue & 0xff, sms, d_err, s, force_bn);
+  int herr = 0;
+  cudaError_t e = cudaMemcpyAsync(&herr, d_err, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  cudaFree(d_err);
+  if (rc) return rc;
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "gemm: %s", cudaGetErrorString(e));
+  if (herr != 0) return set_error(B200EMB_ERR_DEVICE_WAIT, "gemm: a device-side wait gave up (role %d)", herr);
+  return B200EMB_OK;
+}
+
+int b200emb_op_attention(const void* qkv, void* out, const int32_t* d_cu_seqlens, const int32_t* h_cu_seqlens,
+                         int32_t n_seqs, int32_t n_tokens, int32_t n_heads, int32_t n_kv_heads, int32_t head_dim,
+                         int32_t causal, void* stream) {
+  (void)d_cu_seqlens;
+  if (qkv == nullptr || out == nullptr || h_cu_seqlens == nullptr || n_seqs <= 0)
+    return set_error(B200EMB_ERR_INVALID, "attention: null pointer or empty batch");
+  if (h_cu_seqlens[0] != 0 || h_cu_seqlens[n_seqs] != n_tokens)
+    return set_error(B200EMB_ERR_INVALID, "attention: cu_seqlens does not span n_tokens");
+  for (int i = 0; i < n_seqs; ++i)
+    if (h_cu_seqlens[i + 1] <= h_cu_seqlens[i]) return set_error(B200EMB_ERR_INVALID, "attention: empty sequence %d", i);
+  int rc = kernels_init_device();
+  if (rc) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int n_tiles = attention_build_tiles(h_cu_seqlens, n_seqs, nullptr);
+  std::vector<AttnTile> tiles(n_tiles);
+  attention_build_tiles(h_cu_seqlens, n_seqs, tiles.data());
+  AttnTile* d_tiles = nullptr;
+  B2_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&d_tiles), sizeof(AttnTile) * n_tiles));
+  cudaMemcpyAsync(d_tiles, tiles.data(), sizeof(AttnTile) * n_tiles, cudaMemcpyHostToDevice, s);
+  rc = launch_attention(qkv, out, d_tiles, n_tiles, n_heads, n_kv_heads, head_dim, causal, s);
+  cudaError_t e = cudaStreamSynchronize(s);
+  cudaFree(d_tiles);
+  if (rc) return rc;
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "attention: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
+int b200emb_op_embed_ln(const int32_t* ids, const int32_t* types, const int32_t* d_cu_seqlens, int32_t n_seqs,
+                        int32_t n_tokens, const void* word, const void* pos, const void* type_table,
+                        const float* gamma, const float* beta, int32_t hidden, int32_t pos_offset, float eps,
+                        void* out, void* stream) {
+  if (ids == nullptr || d_cu_seqlens == nullptr || word == nullptr || out == nullptr)
+    return set_error(B200EMB_ERR_INVALID, "embed_ln: null pointer");
+  return launch_embed_ln(ids, types, d_cu_seqlens, n_seqs, n_tokens, word, pos, type_table, gamma, beta, hidden,
+                         pos_offset, eps, out, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int b200emb_op_add_ln(const void* x, const void* y, const float* gamma, const float* beta, int32_t n_rows,
+                      int32_t hidden, float eps, void* out, void* stream) {
+  if (x == nullptr || gamma == nullptr || beta == nullptr || out == nullptr)
+    return set_error(B200EMB_ERR_INVALID, "add_ln: null pointer");
+  return launch_add_ln(x, y, gamma, beta, n_rows, hidden, eps, out, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int b200emb_op_pool(const void* x, const int32_t* d_cu_seqlens, int32_t n_seqs, int32_t hidden, int32_t pooling,
+                    int32_t normalize, void* out, int64_t out_row_stride, int32_t out_bf16, void* stream) {
+  if (x == nullptr || d_cu_seqlens == nullptr || out == nullptr) return set_error(B200EMB_ERR_INVALID, "pool: null pointer");
+  return launch_pool(x, d_cu_seqlens, n_seqs, hidden, pooling, normalize, out, out_row_stride, out_bf16,
+                     reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

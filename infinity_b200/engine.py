@@ -1,0 +1,112 @@
+"""Python owner of one ``b200emb_handle``: builds the model descriptor, keeps pinned host
+buffers for results, and calls ``b200emb_forward`` through ctypes.
+
+torch is used here only to own pinned host memory and (for the device-resident variant)
+device buffers whose raw pointers cross the C ABI; no torch operator runs on the path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+
+from . import _lib
+from .configs import Batch, ModelSpec
+
+
+def make_desc(spec: ModelSpec, max_tokens: int = 0) -> _lib.ModelDesc:
+    d = _lib.ModelDesc()
+    d.abi_version = _lib.ABI_VERSION
+    d.arch = _lib.ARCH[spec.arch]
+    d.n_layers, d.hidden, d.n_heads, d.n_kv_heads = spec.n_layers, spec.hidden, spec.n_heads, spec.n_kv_heads
+    d.head_dim, d.ffn, d.vocab, d.max_pos = spec.head_dim, spec.ffn, spec.vocab, spec.max_pos
+    d.type_vocab, d.pos_offset = spec.type_vocab, spec.pos_offset
+    d.norm_eps, d.rope_theta = spec.norm_eps, spec.rope_theta
+    d.n_experts, d.top_k, d.moe_every = spec.n_experts, spec.top_k, spec.moe_every
+    d.pooling = _lib.POOL[spec.pooling]
+    d.normalize = 1 if spec.normalize else 0
+    d.head = _lib.HEAD[spec.head]
+    d.n_labels = spec.n_labels
+    d.weight_format = _lib.WFMT[spec.weight_format]
+    d.max_tokens = max_tokens
+    return d
+
+
+def timing_dict(t: _lib.Timing) -> Dict:
+    return {
+        "n_devices": t.n_devices, "h2d_ms": t.h2d_ms, "kernels_ms": t.kernels_ms, "d2h_ms": t.d2h_ms,
+        "total_ms": t.total_ms, "launches": t.launches, "gemm_flops": t.gemm_flops,
+        "kclass_ms": {n: t.kclass_ms[i] for i, n in enumerate(_lib.KCLASS_NAMES) if t.kclass_launches[i]},
+        "kclass_launches": {n: t.kclass_launches[i] for i, n in enumerate(_lib.KCLASS_NAMES) if t.kclass_launches[i]},
+    }
+
+
+class B200Model:
+    """One model replica set (weights replicated on ``device_ids``) behind the C ABI."""
+
+    def __init__(self, spec: ModelSpec, weight_path: str, device_ids: Sequence[int] = (0,), max_tokens: int = 0):
+        self.spec = spec
+        self._lib = _lib.load()
+        self._handle = C.c_void_p()
+        desc = make_desc(spec, max_tokens)
+        ids = (C.c_int32 * len(device_ids))(*device_ids)
+        _lib.check(self._lib.b200emb_create(C.byref(desc), str(weight_path).encode(), ids, len(device_ids),
+                                            C.byref(self._handle)))
+        self.device_ids = list(device_ids)
+        self.last_timing: Optional[Dict] = None
+
+    def close(self) -> None:
+        if getattr(self, "_handle", None) is not None and self._handle.value:
+            self._lib.b200emb_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def forward_arrays(self, input_ids: np.ndarray, cu_seqlens: np.ndarray,
+                       token_type_ids: Optional[np.ndarray] = None, out: Optional[np.ndarray] = None,
+                       per_kernel: bool = False) -> np.ndarray:
+        """Host arrays in, ``[n_seqs, out_dim]`` float32 out (row i = sequence i)."""
+        ids = np.ascontiguousarray(input_ids, dtype=np.int32)
+        cu = np.ascontiguousarray(cu_seqlens, dtype=np.int32)
+        tt = None if token_type_ids is None else np.ascontiguousarray(token_type_ids, dtype=np.int32)
+        n_seqs = len(cu) - 1
+        n_tokens = int(len(ids))
+        if out is None:
+            out = np.empty((n_seqs, self.spec.out_dim), dtype=np.float32)
+        assert out.dtype == np.float32 and out.flags.c_contiguous and out.shape == (n_seqs, self.spec.out_dim)
+        timing = _lib.Timing()
+        timing.per_kernel = 1 if per_kernel else 0
+        _lib.check(self._lib.b200emb_forward(
+            self._handle, ids.ctypes.data, None if tt is None else tt.ctypes.data, cu.ctypes.data, n_seqs, n_tokens,
+            out.ctypes.data, self.spec.out_dim, C.byref(timing)))
+        self.last_timing = timing_dict(timing)
+        return out
+
+    def forward(self, batch: Batch, **kw) -> np.ndarray:
+        return self.forward_arrays(batch.input_ids, batch.cu_seqlens, batch.token_type_ids, **kw)
+
+    def forward_device(self, d_ids: int, d_types: Optional[int], d_cu: int, h_cu: np.ndarray, n_tokens: int,
+                       d_out: int, per_kernel: bool = False) -> Dict:
+        """Device-resident variant: raw device pointers in, result stays on the device."""
+        cu = np.ascontiguousarray(h_cu, dtype=np.int32)
+        timing = _lib.Timing()
+        timing.per_kernel = 1 if per_kernel else 0
+        _lib.check(self._lib.b200emb_forward_device(self._handle, d_ids, d_types, d_cu, cu.ctypes.data, len(cu) - 1,
+                                                    n_tokens, d_out, self.spec.out_dim, C.byref(timing)))
+        self.last_timing = timing_dict(timing)
+        return self.last_timing
+
+
+def partition(lengths: Sequence[int], n_shards: int, cost_linear: float = 1.0, cost_quadratic: float = 0.0) -> np.ndarray:
+    """Token-balanced assignment of sequences to shards (the library's own partitioner)."""
+    lens = np.ascontiguousarray(lengths, dtype=np.int32)
+    out = np.zeros(len(lens), dtype=np.int32)
+    lib = _lib.load()
+    _lib.check(lib.b200emb_partition(lens.ctypes.data, len(lens), n_shards, cost_linear, cost_quadratic,
+                                     out.ctypes.data))
+    return out

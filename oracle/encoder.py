@@ -1,0 +1,109 @@
+"""Plain-torch fp32 restatement of the post-LayerNorm encoder forward (test infrastructure).
+
+The reference computes this step by calling third-party code:
+``SentenceTransformer.forward`` at infinity_emb/transformer/embedder/sentence_transformer.py:124
+and ``AutoModelForSequenceClassification`` at infinity_emb/transformer/crossencoder/torch.py:106,
+i.e. ``transformers`` ``BertModel`` / ``XLMRobertaForSequenceClassification`` (locked 4.47.0;
+not in the reference tree). This file restates that published algorithm -- embeddings
+(word + token-type + position, LayerNorm), N x [self-attention, output dense + residual +
+LayerNorm, GELU feed-forward + residual + LayerNorm], then either pooling + L2 normalise
+(infinity_emb/transformer/utils_optimum.py:29-47, sentence_transformer.py:142-145) or the
+classification head ``out_proj(tanh(dense(h[:, 0])))`` -- on PADDED, length-sorted batches,
+which is how the reference's CPU path runs it (fp32 on CPU: infinity_emb/inference/loading_strategy.py:87-88;
+padding: crossencoder/torch.py:95-97). ``tests/test_oracle.py`` checks it against the local
+``transformers`` classes loaded with the same weights.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from . import pooling as P
+
+
+def _ln(x, g, b, eps):
+    return F.layer_norm(x, (x.shape[-1],), g, b, eps)
+
+
+@torch.no_grad()
+def encoder_hidden(spec, W: Dict[str, torch.Tensor], ids: torch.Tensor, mask: torch.Tensor,
+                   types: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """ids, mask, types: [B, L] (right padded). Returns the last hidden state [B, L, H] in fp32."""
+    B, L = ids.shape
+    H, nh, d = spec.hidden, spec.n_heads, spec.head_dim
+    pos = torch.arange(L).unsqueeze(0).expand(B, L) + spec.pos_offset
+    if spec.arch == "xlmr":
+        # padded positions take the padding index (pos_offset - 1), as create_position_ids_from_input_ids does
+        pos = torch.where(mask.bool(), pos, torch.full_like(pos, spec.pos_offset - 1))
+    x = W["emb.word"][ids]
+    if spec.type_vocab > 0:
+        tt = types if types is not None else torch.zeros_like(ids)
+        x = x + W["emb.type"][tt]
+    x = x + W["emb.pos"][pos]
+    x = _ln(x, W["emb.ln.g"], W["emb.ln.b"], spec.norm_eps)
+    neg = torch.finfo(torch.float32).min
+    add_mask = (1.0 - mask.float())[:, None, None, :] * neg
+    for l in range(spec.n_layers):
+        p = f"layer.{l}."
+        qkv = x @ W[p + "qkv.w"].t() + W[p + "qkv.b"]
+        q, k, v = qkv.split(H, dim=-1)
+        q = q.view(B, L, nh, d).transpose(1, 2)
+        k = k.view(B, L, nh, d).transpose(1, 2)
+        v = v.view(B, L, nh, d).transpose(1, 2)
+        s = q @ k.transpose(-1, -2) / math.sqrt(d) + add_mask
+        a = torch.softmax(s, dim=-1) @ v
+        a = a.transpose(1, 2).reshape(B, L, H)
+        x = _ln(x + a @ W[p + "o.w"].t() + W[p + "o.b"], W[p + "ln1.g"], W[p + "ln1.b"], spec.norm_eps)
+        f = F.gelu(x @ W[p + "ffn1.w"].t() + W[p + "ffn1.b"])
+        x = _ln(x + f @ W[p + "ffn2.w"].t() + W[p + "ffn2.b"], W[p + "ln2.g"], W[p + "ln2.b"], spec.norm_eps)
+    return x
+
+
+def pad_batch(seqs, types=None, pad_id: int = 0):
+    B, L = len(seqs), max(len(s) for s in seqs)
+    ids = torch.full((B, L), pad_id, dtype=torch.long)
+    mask = torch.zeros((B, L), dtype=torch.long)
+    tt = torch.zeros((B, L), dtype=torch.long)
+    for i, s in enumerate(seqs):
+        ids[i, : len(s)] = torch.as_tensor(np.asarray(s), dtype=torch.long)
+        mask[i, : len(s)] = 1
+        if types is not None:
+            tt[i, : len(s)] = torch.as_tensor(np.asarray(types[i]), dtype=torch.long)
+    return ids, mask, tt
+
+
+@torch.no_grad()
+def forward_padded(spec, W, ids, mask, types=None) -> np.ndarray:
+    """One padded batch -> [B, out_dim] float32 (embeddings, or raw logits for classifier heads)."""
+    h = encoder_hidden(spec, W, ids, mask, types)
+    if spec.head == "classifier":
+        c = torch.tanh(h[:, 0] @ W["head.dense.w"].t() + W["head.dense.b"])
+        return (c @ W["head.out.w"].t() + W["head.out.b"]).float().numpy()
+    pooled = P.POOLERS[spec.pooling](h.numpy(), mask.numpy())
+    pooled = pooled.astype(np.float32)  # sentence_transformer.py:142: embeddings go to fp32 first
+    if spec.normalize:
+        pooled = P.normalize(pooled)
+    return pooled.astype(np.float32)
+
+
+def forward_batch(spec, W, batch, batch_size: int = 32, sort: bool = True) -> np.ndarray:
+    """A ragged batch through the reference's CPU recipe: (optionally) sort by length, cut
+    into padded sub-batches of ``batch_size`` (EngineArgs.batch_size default 32), run each,
+    and return rows in the original order."""
+    seqs = batch.sequences()
+    types = None
+    if batch.token_type_ids is not None:
+        cu = batch.cu_seqlens
+        types = [batch.token_type_ids[cu[i]: cu[i + 1]] for i in range(batch.n_seqs)]
+    order = np.argsort(batch.lengths, kind="stable") if sort else np.arange(batch.n_seqs)
+    out = np.zeros((batch.n_seqs, spec.out_dim), dtype=np.float32)
+    pad_id = 1 if spec.arch == "xlmr" else 0
+    for s in range(0, batch.n_seqs, batch_size):
+        idx = order[s: s + batch_size]
+        ids, mask, tt = pad_batch([seqs[i] for i in idx], [types[i] for i in idx] if types else None, pad_id)
+        out[idx] = forward_padded(spec, W, ids, mask, tt if types else None)
+    return out

@@ -1,0 +1,129 @@
+"""End-to-end parity of the CUDA forward (through the C ABI, host buffers in and out)
+against the fp32 CPU oracle on the same seeded weights and inputs.
+
+Tolerances (bf16 compute against the fp32 oracle that sees the same stored weights):
+cosine >= 0.9999 per embedding; classifier logits within 1e-2 absolute.
+"""
+import numpy as np
+import pytest
+import torch
+
+from infinity_b200 import configs as cf
+from infinity_b200 import weights as wt
+from infinity_b200.engine import B200Model
+from oracle import encoder as enc
+
+pytestmark = pytest.mark.gpu
+
+COS_TOL = 0.9999
+LOGIT_TOL = 1e-2
+
+
+def cosines(a, b):
+    return (a * b).sum(1) / (np.linalg.norm(a, axis=1) * np.linalg.norm(b, axis=1))
+
+
+def build_model(tmp_path, spec, seed, perturb, device_ids=(0,)):
+    master = cf.init_weights(spec, seed, perturb=perturb)
+    path = tmp_path / f"{spec.name}.b2ew"
+    wt.save_weights(path, cf.runtime_tensors(master))
+    return B200Model(spec, str(path), device_ids), cf.oracle_tensors(spec, master)
+
+
+@pytest.mark.parametrize("pooling", ["cls", "mean", "last"])
+@pytest.mark.parametrize("hidden,heads,hd", [(128, 4, 32), (256, 4, 64), (512, 4, 128)])
+def test_tiny_encoder_matches_oracle(tmp_path, pooling, hidden, heads, hd):
+    spec = cf.tiny_spec("bert", hidden=hidden, n_heads=heads, n_kv_heads=heads, head_dim=hd, ffn=2 * hidden,
+                        pooling=pooling)
+    model, W = build_model(tmp_path, spec, 11, perturb=True)
+    batch = cf.random_batch(spec, [1, 2, 9, 64, 65, 127, 128, 160, 33, 77], 5, with_types=True)
+    got = model.forward(batch)
+    ref = enc.forward_batch(spec, W, batch)
+    assert got.shape == ref.shape == (batch.n_seqs, hidden)
+    cos = cosines(got, ref)
+    assert cos.min() >= COS_TOL, cos
+    np.testing.assert_allclose(np.linalg.norm(got, axis=1), 1.0, atol=1e-5)
+    model.close()
+
+
+def test_tiny_reranker_matches_oracle(tmp_path):
+    spec = cf.tiny_spec("xlmr")
+    model, W = build_model(tmp_path, spec, 12, perturb=True)
+    batch = cf.random_batch(spec, [4, 30, 99, 158, 64], 6)
+    got = model.forward(batch)
+    ref = enc.forward_batch(spec, W, batch)
+    assert got.shape == (5, 1)
+    assert np.abs(got - ref).max() <= LOGIT_TOL, (got, ref)
+    model.close()
+
+
+def test_order_and_batch_independence(tmp_path):
+    """Row i belongs to sequence i whatever the order, and a sequence's embedding does not
+    depend on its neighbours in the batch (bit-exact: same kernels, same per-row math)."""
+    spec = cf.tiny_spec("bert")
+    model, _ = build_model(tmp_path, spec, 13, perturb=True)
+    lens = [5, 150, 31, 64, 100, 7, 129]
+    batch = cf.random_batch(spec, lens, 8)
+    full = model.forward(batch)
+    seqs = batch.sequences()
+    perm = [3, 0, 6, 2, 5, 1, 4]
+    permuted = model.forward(cf.pack([seqs[i] for i in perm]))
+    assert np.array_equal(permuted, full[perm])
+    single = model.forward(cf.pack([seqs[1]]))
+    assert np.array_equal(single[0], full[1])
+    model.close()
+
+
+def test_invalid_inputs_are_rejected(tmp_path):
+    from infinity_b200._lib import B200EmbError
+    spec = cf.tiny_spec("bert")
+    model, _ = build_model(tmp_path, spec, 14, perturb=False)
+    ids = np.array([1, 2, 3, 4], dtype=np.int32)
+    with pytest.raises(B200EmbError, match="strictly increasing"):
+        model.forward_arrays(ids, np.array([0, 2, 2, 4], dtype=np.int32))
+    with pytest.raises(B200EmbError, match="cu_seqlens\\[0\\]"):
+        model.forward_arrays(ids, np.array([1, 4], dtype=np.int32))
+    with pytest.raises(B200EmbError, match="vocabulary"):
+        model.forward_arrays(np.array([1, 2, 3, spec.vocab], dtype=np.int32), np.array([0, 4], dtype=np.int32))
+    with pytest.raises(B200EmbError, match="position table"):
+        long = np.ones(spec.max_pos + 1, dtype=np.int32)
+        model.forward_arrays(long, np.array([0, len(long)], dtype=np.int32))
+    # empty batch: no work, no error
+    out = model.forward_arrays(np.zeros(0, np.int32), np.zeros(1, np.int32))
+    assert out.shape == (0, spec.hidden)
+    model.close()
+
+
+def test_config1_bge_small_shape(tmp_path):
+    """Configuration 1 in full: 32 sequences, 7715 tokens, CLS pooling, fp32 master weights."""
+    spec = cf.BGE_SMALL
+    model, W = build_model(tmp_path, spec, cf.SEEDS["c1"][2], perturb=False)
+    batch = cf.synth_batch("c1")
+    assert batch.n_tokens == 7715
+    got = model.forward(batch)
+    ref = enc.forward_batch(spec, W, batch)
+    cos = cosines(got, ref)
+    print("c1 cosine min/mean", cos.min(), cos.mean())
+    assert cos.min() >= COS_TOL
+    model.close()
+
+
+def test_config2_bert_large_shape_subset(tmp_path):
+    """Configuration 2 weights, 48 of its sequences (the oracle needs ~1 s per sequence on CPU);
+    the GPU runs the full 1024-sequence batch and the rows of the subset must be identical."""
+    spec = cf.BERT_LARGE
+    model, W = build_model(tmp_path, spec, cf.SEEDS["c2"][2], perturb=False)
+    batch = cf.synth_batch("c2")
+    full = model.forward(batch)
+    assert full.shape == (1024, 1024) and np.isfinite(full).all()
+    np.testing.assert_allclose(np.linalg.norm(full, axis=1), 1.0, atol=1e-5)
+    pick = list(range(0, 1024, 22))[:48]
+    seqs = batch.sequences()
+    sub = cf.pack([seqs[i] for i in pick])
+    got = model.forward(sub)
+    assert np.array_equal(got, full[pick])
+    ref = enc.forward_batch(spec, W, sub)
+    cos = cosines(got, ref)
+    print("c2 cosine min/mean", cos.min(), cos.mean())
+    assert cos.min() >= COS_TOL
+    model.close()
