@@ -1,0 +1,100 @@
+"""Runs one kernel a few times on seeded inputs, for profiling a small case under ncu:
+
+    python -m infinity_b200.kernel_case gemm --m 32768 --n 3072 --k 1024 --epi bias --launches 3
+    python -m infinity_b200.kernel_case attention --seqs 256 --len 384 --heads 16 --head-dim 64 --launches 3
+    python -m infinity_b200.kernel_case add_ln --rows 65536 --hidden 1024 --launches 3
+
+Every case checks its result against a torch computation before exiting 0.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+
+import numpy as np
+import torch
+
+from . import _lib
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm", "attention", "add_ln"])
+    ap.add_argument("--m", type=int, default=32768)
+    ap.add_argument("--n", type=int, default=3072)
+    ap.add_argument("--k", type=int, default=1024)
+    ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--epi", default="bias", choices=list(_lib.EPI))
+    ap.add_argument("--seqs", type=int, default=256)
+    ap.add_argument("--len", type=int, default=384)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--kv-heads", type=int, default=0)
+    ap.add_argument("--head-dim", type=int, default=64)
+    ap.add_argument("--causal", type=int, default=0)
+    ap.add_argument("--rows", type=int, default=65536)
+    ap.add_argument("--hidden", type=int, default=1024)
+    ap.add_argument("--launches", type=int, default=3)
+    a = ap.parse_args()
+    lib = _lib.load()
+    torch.manual_seed(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    if a.kernel == "gemm":
+        A = torch.randn(a.m, a.k, device="cuda").to(torch.bfloat16)
+        W = (torch.randn(a.n, a.k, device="cuda") / math.sqrt(a.k)).to(torch.bfloat16)
+        bias = torch.randn(a.n, device="cuda")
+        Cm = torch.empty(a.m, a.n, dtype=torch.bfloat16, device="cuda")
+        torch.cuda.synchronize()
+        for _ in range(a.launches):
+            _lib.check(lib.b200emb_op_gemm_bf16(A.data_ptr(), W.data_ptr(), bias.data_ptr(), Cm.data_ptr(), a.m, a.n,
+                                                a.k, _lib.EPI[a.epi] | (a.bn << 8), stream))
+        rows = slice(0, min(a.m, 2048))
+        ref = A[rows].float() @ W.float().t() + bias
+        if a.epi == "gelu":
+            ref = torch.nn.functional.gelu(ref)
+        elif a.epi == "tanh":
+            ref = torch.tanh(ref)
+        err = (Cm[rows].float() - ref).abs().max().item()
+        assert err < 0.05, err
+        print(f"gemm {a.m}x{a.n}x{a.k} ok, max abs err {err:.4f}")
+    elif a.kernel == "attention":
+        nkv = a.kv_heads or a.heads
+        cu = (np.arange(a.seqs + 1) * a.len).astype(np.int32)
+        T = int(cu[-1])
+        qkv = torch.randn(T, (a.heads + 2 * nkv) * a.head_dim, device="cuda").to(torch.bfloat16)
+        out = torch.empty(T, a.heads * a.head_dim, dtype=torch.bfloat16, device="cuda")
+        d_cu = torch.from_numpy(cu).cuda()
+        torch.cuda.synchronize()
+        for _ in range(a.launches):
+            _lib.check(lib.b200emb_op_attention(qkv.data_ptr(), out.data_ptr(), d_cu.data_ptr(), cu.ctypes.data,
+                                                a.seqs, T, a.heads, nkv, a.head_dim, a.causal, stream))
+        q, k, v = qkv[: a.len].float().split([a.heads * a.head_dim, nkv * a.head_dim, nkv * a.head_dim], dim=1)
+        rep = a.heads // nkv
+        qh = q.view(a.len, a.heads, a.head_dim).transpose(0, 1)
+        kh = k.view(a.len, nkv, a.head_dim).transpose(0, 1).repeat_interleave(rep, 0)
+        vh = v.view(a.len, nkv, a.head_dim).transpose(0, 1).repeat_interleave(rep, 0)
+        s = qh @ kh.transpose(1, 2) / math.sqrt(a.head_dim)
+        if a.causal:
+            s = s.masked_fill(torch.ones(a.len, a.len, device="cuda").triu(1).bool(), float("-inf"))
+        ref = (torch.softmax(s, -1) @ vh).transpose(0, 1).reshape(a.len, -1)
+        err = (out[: a.len].float() - ref).abs().max().item()
+        assert err < 2e-2, err
+        print(f"attention {a.seqs}x{a.len} ok, max abs err {err:.4f}")
+    else:
+        x = torch.randn(a.rows, a.hidden, device="cuda").to(torch.bfloat16)
+        y = torch.randn(a.rows, a.hidden, device="cuda").to(torch.bfloat16)
+        g = torch.ones(a.hidden, device="cuda")
+        b = torch.zeros(a.hidden, device="cuda")
+        out = torch.empty_like(x)
+        torch.cuda.synchronize()
+        for _ in range(a.launches):
+            _lib.check(lib.b200emb_op_add_ln(x.data_ptr(), y.data_ptr(), g.data_ptr(), b.data_ptr(), a.rows, a.hidden,
+                                             1e-12, out.data_ptr(), stream))
+        torch.cuda.synchronize()
+        ref = torch.nn.functional.layer_norm(x[:1024].float() + y[:1024].float(), (a.hidden,), g, b, 1e-12)
+        err = (out[:1024].float() - ref).abs().max().item()
+        assert err < 3e-2, err
+        print(f"add_ln {a.rows}x{a.hidden} ok, max abs err {err:.4f}")
+
+
+if __name__ == "__main__":
+    main()
