@@ -167,7 +167,8 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
     from infinity_b200 import _lib, configs as cf, weights as wt
-    from infinity_b200.engine import B200Model, partition
+    from infinity_b200.engine import B200Model
+    from infinity_b200.sharding import shard_indices
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -210,11 +211,7 @@ def run_ours(args):
     # global batch -> token-balanced shards (whole sequences; cost a*L + b*L^2 as in the library)
     seqs = global_batch(world)
     lens = np.array([len(s) for s in seqs], dtype=np.int32)
-    H, F, QKV = spec.hidden, spec.ffn, 3 * spec.hidden
-    cost_a = 2.0 * H * QKV + 2.0 * H * H + 4.0 * H * F
-    cost_b = 4.0 * H
-    shard_of = partition(lens, world, cost_a, cost_b) if world > 1 else np.zeros(len(seqs), np.int32)
-    mine = [i for i in range(len(seqs)) if shard_of[i] == rank]
+    mine = shard_indices(lens, world, spec)[rank]
     batch = cf.pack([seqs[i] for i in mine])
     total_tokens = int(lens.sum())
 

@@ -1,0 +1,175 @@
+"""Drop-in backends for the infinity_emb engine: the five-method interface of
+``BaseTransformer`` (infinity_emb/transformer/abstract.py:44-69) over the CUDA library.
+
+  B200Embedder      capabilities {"embed"}     replaces SentenceTransformerPatched
+                    (infinity_emb/transformer/embedder/sentence_transformer.py:54-169)
+  B200CrossEncoder  capabilities {"rerank"}    replaces CrossEncoderPatched
+                    (infinity_emb/transformer/crossencoder/torch.py:41-123)
+  B200Classifier    capabilities {"classify"}  replaces SentenceClassifier
+                    (infinity_emb/transformer/classifier/torch.py:21-91)
+
+The classes are duck-typed (this package does not import infinity_emb), so an instance can
+be handed to the reference's ``BatchHandler(model_replicas=[backend], ...)`` as it is.
+Same method names, argument meaning and return conventions as the reference:
+``encode_pre`` is called from the batcher's tokenisation thread, ``encode_core`` from its
+inference thread (never re-entered for one object), ``encode_post`` from its
+post-processing thread, ``tokenize_lengths`` from a thread pool. An exception in any of
+them propagates, as in the reference (batch_handler.py:556-558, 586-588, 622-624).
+"""
+from __future__ import annotations
+
+import threading
+from time import perf_counter
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from .configs import ModelSpec
+from .engine import B200Model
+from .packing import HFTokenizer, IdStringTokenizer, PackedFeatures
+
+
+class _B200Backend:
+    capabilities: set = set()
+
+    def __init__(self, *, engine_args: Any = None, spec: ModelSpec, weight_path: Optional[str] = None,
+                 device_ids: Sequence[int] = (0,), tokenizer: Any = None, model: Any = None,
+                 ring_size: int = 10):
+        """``model``: an object with ``forward_arrays(ids, cu, types, out=)`` (tests inject a
+        stand-in); by default a :class:`B200Model` on ``device_ids`` is created, which fails
+        loudly when the CUDA library or a GPU is missing."""
+        self.engine_args = engine_args
+        self.spec = spec
+        self.tokenizer = tokenizer if tokenizer is not None else IdStringTokenizer(spec.max_len)
+        self.model = model if model is not None else B200Model(spec, weight_path, device_ids)
+        # Results travel through two bounded queues (depth 3 and 5, batch_handler.py:499-500)
+        # before the batcher hands rows out, so up to ~9 batches are alive per replica:
+        # result buffers come from a ring of ring_size reusable arrays.
+        self._ring: List[Optional[np.ndarray]] = [None] * ring_size
+        self._ring_pos = 0
+        self._lock = threading.Lock()
+
+    # -- shared pieces ----------------------------------------------------------------
+    def _result_buffer(self, n_seqs: int) -> np.ndarray:
+        with self._lock:
+            slot = self._ring_pos
+            self._ring_pos = (self._ring_pos + 1) % len(self._ring)
+        buf = self._ring[slot]
+        if buf is None or buf.shape[0] < n_seqs:
+            buf = _pinned_empty(max(n_seqs, 64), self.spec.out_dim)
+            self._ring[slot] = buf
+        return buf[:n_seqs]
+
+    def encode_core(self, features: PackedFeatures) -> np.ndarray:
+        """runs the forward on the GPU(s); returns ``[n_seqs, out_dim]`` float32"""
+        out = self._result_buffer(features.n_seqs)
+        self.model.forward_arrays(features.input_ids, features.cu_seqlens, features.token_type_ids, out=out)
+        return out
+
+    def tokenize_lengths(self, sentences: List[str]) -> List[int]:
+        return self.tokenizer.lengths(sentences)
+
+    def _warmup_inputs(self, batch_size: int, n_tokens: int) -> list:
+        raise NotImplementedError
+
+    def warmup(self, *, batch_size: int = 64, n_tokens: int = 1) -> Tuple[float, float, str]:
+        """Same contract as ``run_warmup`` (abstract.py:228-250): returns embeddings per
+        second, inference seconds and a log string."""
+        inputs = self._warmup_inputs(batch_size, n_tokens)
+        start = perf_counter()
+        feat = self.encode_pre(inputs)
+        t_tok = perf_counter()
+        out = self.encode_core(feat)
+        t_inf = perf_counter()
+        self.encode_post(out)
+        t_post = perf_counter()
+        log = (f"Getting timings for batch_size={batch_size} and avg tokens per sentence={feat.n_tokens / max(batch_size, 1):.1f}\n"
+               f"\t{(t_tok - start) * 1000:.2f} \t ms tokenization\n"
+               f"\t{(t_inf - t_tok) * 1000:.2f} \t ms inference\n"
+               f"\t{(t_post - t_inf) * 1000:.2f} \t ms post-processing\n"
+               f"\t{(t_post - start) * 1000:.2f} \t ms total\n"
+               f"embeddings/sec: {batch_size / (t_post - start):.2f}")
+        return batch_size / (t_post - start), t_inf - t_tok, log
+
+
+def _pinned_empty(rows: int, cols: int) -> np.ndarray:
+    """float32 host array in page-locked memory when torch + CUDA are present (the D2H copy
+    of the result is then asynchronous on the library's stream); plain numpy otherwise."""
+    try:
+        import torch
+        if torch.cuda.is_available():
+            t = torch.empty(rows, cols, dtype=torch.float32).pin_memory()
+            return t.numpy()  # the array keeps the pinned tensor alive
+    except Exception:
+        pass
+    return np.empty((rows, cols), dtype=np.float32)
+
+
+class B200Embedder(_B200Backend):
+    capabilities = {"embed"}
+
+    def _warmup_inputs(self, batch_size, n_tokens):
+        if isinstance(self.tokenizer, IdStringTokenizer):
+            return [" ".join(["1"] * max(n_tokens, 1))] * batch_size
+        return ["warm " * n_tokens] * batch_size
+
+    def encode_pre(self, sentences: List[str]) -> PackedFeatures:
+        """tokenises and packs the batch (no padding)"""
+        return self.tokenizer.encode(sentences)
+
+    def encode_post(self, embedding: np.ndarray, skip_quanitzation: bool = True) -> np.ndarray:
+        """float32 rows, already pooled and L2-normalised on the device (the reference does
+        this step on the CPU: sentence_transformer.py:142-145)."""
+        return embedding
+
+
+class B200CrossEncoder(_B200Backend):
+    capabilities = {"rerank"}
+
+    def _warmup_inputs(self, batch_size, n_tokens):
+        s = " ".join(["1"] * max(n_tokens, 1)) if isinstance(self.tokenizer, IdStringTokenizer) else "warm " * n_tokens
+        return [(s, s)] * batch_size
+
+    def encode_pre(self, queries_docs: List[Tuple[str, str]]) -> PackedFeatures:
+        """strips, pair-tokenises with longest-first truncation (crossencoder/torch.py:91-98) and packs"""
+        return self.tokenizer.encode_pairs(queries_docs)
+
+    def encode_post(self, out_features: np.ndarray) -> np.ndarray:
+        """flat float32 raw logits (crossencoder/torch.py:110-111); the batcher applies the sigmoid"""
+        return np.ascontiguousarray(out_features, dtype=np.float32).reshape(-1)
+
+
+class B200Classifier(_B200Backend):
+    capabilities = {"classify"}
+
+    def __init__(self, *, labels: Optional[Sequence[str]] = None, **kw):
+        super().__init__(**kw)
+        n = self.spec.n_labels
+        self.labels = list(labels) if labels is not None else [f"LABEL_{i}" for i in range(n)]
+        if len(self.labels) != n:
+            raise ValueError(f"{len(self.labels)} labels for a head with {n} outputs")
+
+    def _warmup_inputs(self, batch_size, n_tokens):
+        if isinstance(self.tokenizer, IdStringTokenizer):
+            return [" ".join(["1"] * max(n_tokens, 1))] * batch_size
+        return ["warm " * n_tokens] * batch_size
+
+    def encode_pre(self, sentences: List[str]) -> PackedFeatures:
+        return self.tokenizer.encode(sentences)
+
+    def encode_post(self, logits: np.ndarray) -> List[List[Dict[str, Any]]]:
+        """What the HF text-classification pipeline returns with ``top_k=None``
+        (classifier/torch.py:38-46, 74-80): per input, one dict per label sorted by score
+        descending; softmax over the labels, or a sigmoid for a single-label head."""
+        x = np.asarray(logits, dtype=np.float64)
+        if x.shape[1] == 1:
+            scores = 1.0 / (1.0 + np.exp(-x))
+        else:
+            z = x - x.max(axis=1, keepdims=True)
+            e = np.exp(z)
+            scores = e / e.sum(axis=1, keepdims=True)
+        out = []
+        for row in scores:
+            order = np.argsort(-row, kind="stable")
+            out.append([{"label": self.labels[j], "score": float(row[j])} for j in order])
+        return out

@@ -1,0 +1,179 @@
+"""Host-side logic that needs no GPU: weight file round trip, packing, pair truncation,
+classifier post-processing, and the backends driven by the reference's own BatchHandler
+(when the reference tree is present) with a stand-in for the device model."""
+import asyncio
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from infinity_b200 import configs as cf
+from infinity_b200 import packing as pk
+from infinity_b200 import weights as wt
+from infinity_b200.backend import B200Classifier, B200CrossEncoder, B200Embedder
+
+REF = Path("/root/reference/libs/infinity_emb")
+
+
+def test_weight_file_round_trip(tmp_path):
+    spec = cf.tiny_spec("xlmr")
+    tensors = cf.runtime_tensors(cf.init_weights(spec, 3, perturb=True))
+    path = tmp_path / "w.b2ew"
+    wt.save_weights(path, tensors)
+    back = wt.load_weights(path)
+    assert list(back) == list(tensors)
+    for k in tensors:
+        assert back[k].dtype == tensors[k].dtype and back[k].shape == tensors[k].shape
+        assert torch.equal(back[k].view(torch.int16) if back[k].dtype == torch.bfloat16 else back[k],
+                           tensors[k].view(torch.int16) if tensors[k].dtype == torch.bfloat16 else tensors[k])
+
+
+def test_packing_is_bit_exact_against_the_padded_layout():
+    """cu_seqlens / token stream == what mask.nonzero() selects from the reference's padded batch."""
+    from oracle import encoder as enc
+    rng = np.random.default_rng(1)
+    seqs = [rng.integers(0, 1000, size=L) for L in [5, 1, 64, 33, 512, 2]]
+    packed = pk.pack_sequences(seqs)
+    ids, mask, _ = enc.pad_batch(seqs)
+    assert np.array_equal(packed.input_ids, ids[mask.bool()].numpy().astype(np.int32))
+    assert np.array_equal(packed.cu_seqlens, np.concatenate([[0], np.cumsum(mask.sum(1).numpy())]))
+    assert packed.n_seqs == 6 and packed.n_tokens == sum(len(s) for s in seqs)
+    with pytest.raises(ValueError):
+        pk.pack_sequences([[1, 2], []])
+    empty = pk.pack_sequences([])
+    assert empty.n_seqs == 0 and empty.n_tokens == 0
+
+
+def test_pair_truncation_longest_first():
+    q, d = pk.truncate_pair_longest_first(list(range(10)), list(range(100, 130)), 20)
+    assert len(q) + len(d) == 20 and q == list(range(10)) and d == list(range(100, 110))
+    q, d = pk.truncate_pair_longest_first(list(range(30)), list(range(5)), 20)
+    assert len(q) == 15 and len(d) == 5
+    q, d = pk.truncate_pair_longest_first([1, 2], [3], 20)
+    assert (q, d) == ([1, 2], [3])
+    tok = pk.IdStringTokenizer(max_len=16)
+    f = tok.encode_pairs([(" 5 6 7 ", "8 9"), ("1 " * 20, "2 " * 20)])
+    assert f.input_ids[: f.cu_seqlens[1]].tolist() == [0, 5, 6, 7, 2, 2, 8, 9, 2]
+    assert f.cu_seqlens[2] - f.cu_seqlens[1] == 16
+    assert tok.lengths(["1 2 3", "4"]) == [3, 1]
+
+
+def test_hf_tokenizer_packs_without_padding():
+    import tokenizers
+    from tokenizers import models, pre_tokenizers, processors
+    vocab = {"[PAD]": 0, "[UNK]": 1, "[CLS]": 2, "[SEP]": 3, "hello": 4, "world": 5, "warm": 6, "a": 7}
+    tok = tokenizers.Tokenizer(models.WordLevel(vocab, unk_token="[UNK]"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    tok.post_processor = processors.TemplateProcessing(
+        single="[CLS] $A [SEP]", pair="[CLS] $A [SEP] $B:1 [SEP]:1", special_tokens=[("[CLS]", 2), ("[SEP]", 3)])
+    t = pk.HFTokenizer(tok, max_len=8)
+    f = t.encode(["hello world", "a", "warm " * 20])
+    assert f.input_ids[:4].tolist() == [2, 4, 5, 3]
+    assert np.diff(f.cu_seqlens).tolist() == [4, 3, 8]
+    p = t.encode_pairs([("hello", "world a")])
+    assert p.input_ids.tolist() == [2, 4, 3, 5, 7, 3] and p.token_type_ids.tolist() == [0, 0, 0, 1, 1, 1]
+    assert t.lengths(["hello world", "a"]) == [2, 1]
+
+
+class FakeDeviceModel:
+    """Stands in for B200Model: row i = [n_tokens_i, sum(ids_i), first id, ...]."""
+
+    def __init__(self, out_dim):
+        self.out_dim = out_dim
+        self.calls = []
+
+    def forward_arrays(self, ids, cu, types=None, out=None, **kw):
+        n = len(cu) - 1
+        self.calls.append(n)
+        for i in range(n):
+            seg = ids[cu[i]: cu[i + 1]]
+            out[i, :] = 0.0
+            out[i, 0] = len(seg)
+            if self.out_dim > 1:
+                out[i, 1] = float(seg.sum())
+        return out
+
+
+def test_classifier_post_processing():
+    spec = cf.tiny_spec("xlmr", n_labels=3)
+    clf = B200Classifier(spec=spec, model=FakeDeviceModel(3), labels=["neg", "neu", "pos"])
+    out = clf.encode_post(np.array([[0.0, 2.0, 1.0], [5.0, -1.0, 0.0]], dtype=np.float32))
+    assert [d["label"] for d in out[0]] == ["neu", "pos", "neg"]
+    assert abs(sum(d["score"] for d in out[0]) - 1.0) < 1e-6
+    assert out[1][0]["label"] == "neg" and out[1][0]["score"] > 0.99
+    single = B200Classifier(spec=cf.tiny_spec("xlmr", n_labels=1), model=FakeDeviceModel(1))
+    assert abs(single.encode_post(np.array([[0.0]], dtype=np.float32))[0][0]["score"] - 0.5) < 1e-7
+    with pytest.raises(ValueError):
+        B200Classifier(spec=spec, model=FakeDeviceModel(3), labels=["a"])
+
+
+def test_backend_warmup_contract():
+    spec = cf.tiny_spec("bert")
+    emb = B200Embedder(spec=spec, model=FakeDeviceModel(spec.hidden))
+    eps, seconds, log = emb.warmup(batch_size=4, n_tokens=7)
+    assert eps > 0 and seconds >= 0 and "embeddings/sec" in log
+    ce = B200CrossEncoder(spec=cf.tiny_spec("xlmr"), model=FakeDeviceModel(1))
+    assert ce.warmup(batch_size=2, n_tokens=3)[0] > 0
+    assert emb.capabilities == {"embed"} and ce.capabilities == {"rerank"}
+
+
+@pytest.fixture(scope="module")
+def reference():
+    if not REF.exists():
+        pytest.skip("reference tree not mounted on this machine")
+    sys.path.insert(0, str(Path(__file__).parent / "golden"))
+    import make_golden
+    return make_golden.import_reference(str(REF))
+
+
+def test_embed_through_the_reference_batch_handler(reference):
+    """The reference's fake-backend pins (tests/unit_test/test_engine.py:24-35: row i carries
+    the length of sentence i; usage == sum of lengths) with our backend behind its BatchHandler."""
+    from infinity_emb.inference.batch_handler import BatchHandler
+    spec = cf.tiny_spec("bert")
+    backend = B200Embedder(spec=spec, model=FakeDeviceModel(spec.hidden))
+    rng = np.random.default_rng(0)
+    sentences = [" ".join(map(str, rng.integers(1, 900, size=int(L)))) for L in rng.integers(1, 120, size=100)]
+
+    async def run():
+        bh = BatchHandler(model_replicas=[backend], max_batch_size=16, lengths_via_tokenize=True)
+        await bh.spawn()
+        try:
+            return await bh.embed(sentences)
+        finally:
+            await bh.shutdown()
+
+    embeddings, usage = asyncio.run(run())
+    assert usage == sum(len(s.split()) for s in sentences)
+    assert len(embeddings) == len(sentences)
+    for s, e in zip(sentences, embeddings):
+        toks = [int(x) for x in s.split()]
+        assert e.shape == (spec.hidden,) and e[0] == len(toks) and e[1] == float(sum(toks))
+    assert max(backend.model.calls) <= 16
+
+
+def test_rerank_through_the_reference_batch_handler(reference):
+    """Raw logits go back flat; the batcher applies the sigmoid and sorts (batch_handler.py:208-219)."""
+    from infinity_emb.inference.batch_handler import BatchHandler
+    spec = cf.tiny_spec("xlmr")
+    backend = B200CrossEncoder(spec=spec, model=FakeDeviceModel(1))
+    query = "7 8 9"
+    docs = ["1 2", "1 2 3 4 5 6", "1"]
+
+    async def run():
+        bh = BatchHandler(model_replicas=[backend], max_batch_size=8)
+        await bh.spawn()
+        try:
+            return await bh.rerank(query=query, docs=docs, raw_scores=False)
+        finally:
+            await bh.shutdown()
+
+    results, usage = asyncio.run(run())
+    # logit = token count of [start] q [sep][sep] d [end]
+    want = {i: 1 / (1 + np.exp(-(len(query.split()) + len(d.split()) + 4))) for i, d in enumerate(docs)}
+    assert [r.index for r in results] == [1, 0, 2]
+    for r in results:
+        assert abs(r.relevance_score - want[r.index]) < 1e-6

@@ -1,0 +1,131 @@
+"""Pins the oracle: pooling / normalisation and batch formation against golden vectors the
+reference's own code produced (tests/golden/make_golden.py), and the encoder restatement
+against the locally installed ``transformers`` model classes the reference calls."""
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from infinity_b200 import configs as cf
+from oracle import batching as OB
+from oracle import encoder as enc
+from oracle import pooling as OP
+
+GOLD = Path(__file__).parent / "golden"
+
+
+def test_pooling_matches_reference_golden():
+    g = np.load(GOLD / "pooling_golden.npz")
+    for name in "abcd":
+        h, m = g[f"{name}_hidden"], g[f"{name}_mask"]
+        assert np.array_equal(OP.mean_pooling(h, m), g[f"{name}_mean"])
+        assert np.array_equal(OP.cls_token_pooling(h, m), g[f"{name}_cls"])
+        assert np.array_equal(OP.normalize(OP.mean_pooling(h, m)), g[f"{name}_mean_norm"])
+        assert np.array_equal(OP.normalize(OP.cls_token_pooling(h, m)), g[f"{name}_cls_norm"])
+    assert np.array_equal(OP.normalize(g["zero_in"]), g["zero_norm"])
+    assert np.array_equal(OP.mean_pooling(g["allmasked_hidden"], g["allmasked_mask"]), g["allmasked_mean"])
+
+
+def test_ragged_pooling_equals_padded():
+    g = np.load(GOLD / "pooling_golden.npz")
+    h, m = g["b_hidden"], g["b_mask"]
+    lens = m.sum(1)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    ragged = np.concatenate([h[i, : lens[i]] for i in range(len(lens))])
+    assert np.array_equal(OP.pool_ragged(ragged, cu, "mean", True), g["b_mean_norm"])
+    assert np.array_equal(OP.pool_ragged(ragged, cu, "cls", False), g["b_cls"])
+    last = OP.pool_ragged(ragged, cu, "last", False)
+    assert np.array_equal(last, np.stack([h[i, lens[i] - 1] for i in range(len(lens))]))
+
+
+def test_batch_former_matches_reference_golden():
+    g = json.loads((GOLD / "batching_golden.json").read_text())
+    assert len(g["cases"]) >= 7
+    for case in g["cases"]:
+        got = OB.pop_all_batches(case["priorities"], case["size"], case["max_n_batches"])
+        assert got == case["batches"]
+    # exactly `size` queued items come out in submission order, unsorted
+    first = g["cases"][0]
+    assert first["batches"] == [list(range(32))]
+    assert g["char_lengths"]["lengths"] == [2, 3, 17] and g["char_lengths"]["total"] == 22
+
+
+def _bert_state_dict(spec, W):
+    sd = {
+        "embeddings.word_embeddings.weight": W["emb.word"],
+        "embeddings.position_embeddings.weight": W["emb.pos"],
+        "embeddings.token_type_embeddings.weight": W["emb.type"],
+        "embeddings.LayerNorm.weight": W["emb.ln.g"], "embeddings.LayerNorm.bias": W["emb.ln.b"],
+    }
+    H = spec.hidden
+    for l in range(spec.n_layers):
+        p, q = f"layer.{l}.", f"encoder.layer.{l}."
+        wq, wk, wv = W[p + "qkv.w"].split(H, 0)
+        bq, bk, bv = W[p + "qkv.b"].split(H, 0)
+        sd.update({
+            q + "attention.self.query.weight": wq, q + "attention.self.query.bias": bq,
+            q + "attention.self.key.weight": wk, q + "attention.self.key.bias": bk,
+            q + "attention.self.value.weight": wv, q + "attention.self.value.bias": bv,
+            q + "attention.output.dense.weight": W[p + "o.w"], q + "attention.output.dense.bias": W[p + "o.b"],
+            q + "attention.output.LayerNorm.weight": W[p + "ln1.g"], q + "attention.output.LayerNorm.bias": W[p + "ln1.b"],
+            q + "intermediate.dense.weight": W[p + "ffn1.w"], q + "intermediate.dense.bias": W[p + "ffn1.b"],
+            q + "output.dense.weight": W[p + "ffn2.w"], q + "output.dense.bias": W[p + "ffn2.b"],
+            q + "output.LayerNorm.weight": W[p + "ln2.g"], q + "output.LayerNorm.bias": W[p + "ln2.b"],
+        })
+    return sd
+
+
+def test_encoder_matches_transformers_bert():
+    """The restatement against ``transformers.BertModel`` (the class behind
+    SentenceTransformer.forward at sentence_transformer.py:124) with identical weights."""
+    from transformers import BertConfig, BertModel
+    spec = cf.tiny_spec("bert", hidden=64, n_heads=4, n_kv_heads=4, head_dim=16, ffn=128, vocab=300, max_pos=64)
+    W = cf.oracle_tensors(spec, cf.init_weights(spec, 5, perturb=True))
+    cfg = BertConfig(vocab_size=spec.vocab, hidden_size=spec.hidden, num_hidden_layers=spec.n_layers,
+                     num_attention_heads=spec.n_heads, intermediate_size=spec.ffn, max_position_embeddings=spec.max_pos,
+                     type_vocab_size=2, layer_norm_eps=spec.norm_eps, hidden_act="gelu",
+                     hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    model = BertModel(cfg, add_pooling_layer=False).eval()
+    missing, unexpected = model.load_state_dict(_bert_state_dict(spec, W), strict=False)
+    assert not unexpected and all("position_ids" in m for m in missing), (missing, unexpected)
+    batch = cf.random_batch(spec, [3, 17, 64, 40], 9, with_types=True)
+    cu = batch.cu_seqlens
+    types = [batch.token_type_ids[cu[i]: cu[i + 1]] for i in range(batch.n_seqs)]
+    ids, mask, tt = enc.pad_batch(batch.sequences(), types)
+    with torch.no_grad():
+        ref = model(input_ids=ids, attention_mask=mask, token_type_ids=tt).last_hidden_state
+    got = enc.encoder_hidden(spec, W, ids, mask, tt)
+    m = mask.bool()
+    assert (got[m] - ref[m]).abs().max().item() < 2e-5
+
+
+def test_reranker_matches_transformers_xlmr():
+    """The restatement against ``XLMRobertaForSequenceClassification`` (what
+    AutoModelForSequenceClassification resolves to at crossencoder/torch.py:106)."""
+    from transformers import XLMRobertaConfig, XLMRobertaForSequenceClassification
+    spec = cf.tiny_spec("xlmr", hidden=64, n_heads=4, n_kv_heads=4, head_dim=16, ffn=128, vocab=300, max_pos=66)
+    W = cf.oracle_tensors(spec, cf.init_weights(spec, 6, perturb=True))
+    cfg = XLMRobertaConfig(vocab_size=spec.vocab, hidden_size=spec.hidden, num_hidden_layers=spec.n_layers,
+                           num_attention_heads=spec.n_heads, intermediate_size=spec.ffn,
+                           max_position_embeddings=spec.max_pos, type_vocab_size=1, layer_norm_eps=spec.norm_eps,
+                           hidden_act="gelu", hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0,
+                           num_labels=1, pad_token_id=1, classifier_dropout=0.0)
+    model = XLMRobertaForSequenceClassification(cfg).eval()
+    sd = {"roberta." + k: v for k, v in _bert_state_dict(spec, W).items()}
+    sd.update({"classifier.dense.weight": W["head.dense.w"], "classifier.dense.bias": W["head.dense.b"],
+               "classifier.out_proj.weight": W["head.out.w"], "classifier.out_proj.bias": W["head.out.b"]})
+    missing, unexpected = model.load_state_dict(sd, strict=False)
+    assert not unexpected and all("position_ids" in m for m in missing), (missing, unexpected)
+    lens = [5, 30, 64, 12]
+    rng = np.random.default_rng(3)
+    seqs = [rng.integers(2, spec.vocab, size=L) for L in lens]  # id 1 is the pad token
+    ids, mask, _ = enc.pad_batch(seqs, None, pad_id=1)
+    with torch.no_grad():
+        ref = model(input_ids=ids, attention_mask=mask).logits.numpy()
+    got = enc.forward_padded(spec, W, ids, mask)
+    assert np.abs(got - ref).max() < 2e-5
+    # and the ragged driver returns rows in batch order whatever the internal sort
+    out = enc.forward_batch(spec, W, cf.pack(seqs), batch_size=2)
+    assert np.abs(out - ref).max() < 2e-5
