@@ -238,7 +238,9 @@ static constexpr int att_smem_bytes() {
   return (ATT_BQ + 4 * ATT_BKV) * (D + 8) * 2;
 }
 
-int attention_build_tiles(const int32_t* cu, int n_seqs, AttnTile* tiles) {
+int attention_tile_rows(int head_dim, int causal) { return (head_dim == 64 && !causal) ? 128 : ATT_BQ; }
+
+int attention_build_tiles_q(const int32_t* cu, int n_seqs, int bq, AttnTile* tiles) {
   // Longest sequences first, so the most expensive tiles start early and the tail is short.
   std::vector<int> order(n_seqs);
   for (int i = 0; i < n_seqs; ++i) order[i] = i;
@@ -248,7 +250,7 @@ int attention_build_tiles(const int32_t* cu, int n_seqs, AttnTile* tiles) {
   for (int idx = 0; idx < n_seqs; ++idx) {
     const int i = order[idx];
     const int len = cu[i + 1] - cu[i];
-    for (int q = 0; q < len; q += ATT_BQ) {
+    for (int q = 0; q < len; q += bq) {
       if (tiles != nullptr) tiles[n] = AttnTile{cu[i], len, q, 0};
       ++n;
     }

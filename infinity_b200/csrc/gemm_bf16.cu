@@ -6,9 +6,12 @@
 //   warp 1        allocates TMEM and issues tcgen05.mma (128 x BN x 16 per instruction,
 //                 fp32 accumulators in TMEM); two accumulator buffers so the epilogue of
 //                 tile i overlaps the MMAs of tile i+1
-//   warps 2..9    epilogue: tcgen05.ld the accumulator (one TMEM lane = one output row per
-//                 thread), add bias, apply GELU / tanh, round to bf16, store 16-byte vectors
-// M is ragged (token count): TMA zero-fills rows past M, stores are predicated.
+//   warps 2..9    epilogue, two groups of four warps: tcgen05.ld the accumulator (one TMEM lane =
+//                 one output row per thread, 64 columns at a time), release the accumulator,
+//                 add the bias (staged in shared memory), apply GELU / tanh, round to bf16,
+//                 write a 128x64 sub-tile into 128-byte-swizzled shared memory and hand it to
+//                 a TMA store (one staging buffer per group, re-used once its store has read it)
+// M is ragged (token count): TMA zero-fills rows past M on loads and clips them on stores.
 // No cluster launch, no multicast: each CTA issues its own loads; W tiles are re-used
 // out of L2.
 #include <cuda.h>
@@ -35,8 +38,10 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // two accumulator buffers
-  static constexpr int BAR_BYTES = 256;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+  static constexpr int CBUF_BYTES = BM * 64 * 2;  // one 128x64 bf16 output sub-tile
+  static constexpr int BIAS_BYTES = 256 * 4;
+  static constexpr int BAR_BYTES = 128;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * CBUF_BYTES + BIAS_BYTES + BAR_BYTES + 1024;  // + alignment slack
 };
 
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
@@ -51,14 +56,16 @@ __device__ __forceinline__ float apply_epilogue(float v) {
 template <int BN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                         const float* __restrict__ bias, __nv_bfloat16* __restrict__ C, int M, int N, int K,
+                         const __grid_constant__ CUtensorMap tmap_c, const float* __restrict__ bias, int M, int N, int K,
                          int* __restrict__ err_flag) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled tiles must start on a 1024-byte boundary.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint8_t* cstage = smem + STAGES * Cfg::STAGE_BYTES;  // 2 x 16 KB, each 1024-byte aligned
+  float* bias_s = reinterpret_cast<float*>(cstage + 2 * Cfg::CBUF_BYTES);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(cstage + 2 * Cfg::CBUF_BYTES + Cfg::BIAS_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_full_bar = empty_bar + STAGES;  // [2]
   uint64_t* acc_empty_bar = acc_full_bar + 2;   // [2]
@@ -98,6 +105,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     if (lane == 0) {
       tma_prefetch_desc(&tmap_a);
       tma_prefetch_desc(&tmap_w);
+      tma_prefetch_desc(&tmap_c);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -181,62 +189,81 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     }
   } else {
     // ---------------- epilogue ----------------
-    const int ew = warp - 2;                 // 0..7
-    const int quarter = warp & 3;            // TMEM lane quarter this warp may read
-    const int half = ew >> 2;                // which half of the tile's columns
-    constexpr int COLS_PER_WARP = BN / (N_EPI_WARPS / 4);
+    const int et = threadIdx.x - 64;  // 0..255
+    const int ew = warp - 2;          // 0..7
+    const int grp = ew >> 2;          // two groups of four warps
+    const int quarter = warp & 3;     // TMEM lane quarter this warp may read
+    const int row_in_tile = quarter * 32 + lane;
+    constexpr int SUBS = BN / 64;                               // 64-column sub-tiles per tile
+    constexpr int SUBS_PER_GROUP = (SUBS >= 2) ? SUBS / 2 : 1;  // BN = 64: group 1 has none
+    uint8_t* cbuf = cstage + grp * Cfg::CBUF_BYTES;
+    const bool store_thread = (ew & 3) == 0 && lane == 0;
     bool ok = true;
     int local_tile = 0;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local_tile) {
       const int m0 = (tile / n_tiles) * BM;
       const int n0 = (tile % n_tiles) * BN;
       const int acc = local_tile & 1;
       const uint32_t acc_phase = (local_tile >> 1) & 1u;
-      if (!mbar_wait(&acc_full_bar[acc], acc_phase)) {
-        ok = false;
-        break;
-      }
+      named_barrier_sync(1, 32 * N_EPI_WARPS);  // everyone is done with the previous tile's bias
+      if (et < BN) bias_s[et] = (bias != nullptr && n0 + et < N) ? __ldg(bias + n0 + et) : 0.f;
+      const bool ok_local = mbar_wait(&acc_full_bar[acc], acc_phase);
+      // one decision for all epilogue threads (also publishes the bias): leave together or not at all
+      ok = named_barrier_and(1, 32 * N_EPI_WARPS, ok_local);
+      if (!ok) break;
       tc_fence_after_sync();
-      const int row = m0 + quarter * 32 + lane;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + half * COLS_PER_WARP;
-#pragma unroll 1
-      for (int c = 0; c < COLS_PER_WARP; c += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_row + c, r);
-        tmem_ld_wait();
-        const int col0 = n0 + half * COLS_PER_WARP + c;
-        if (row < M && col0 < N) {
-          __nv_bfloat16* dst = C + static_cast<size_t>(row) * N + col0;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            if (col0 + j < N) {  // N % 8 == 0, so a group of 8 is all in or all out
-              float v[8];
+      for (int st = 0; st < SUBS_PER_GROUP; ++st) {
+        const int sub = grp * SUBS_PER_GROUP + st;
+        uint32_t r0[32], r1[32];
+        if (sub < SUBS) {
+          tmem_ld_32x32b_x32(t_row + sub * 64, r0);
+          tmem_ld_32x32b_x32(t_row + sub * 64 + 32, r1);
+          tmem_ld_wait();
+        }
+        if (st == SUBS_PER_GROUP - 1) {
+          // the accumulator is in registers: hand the TMEM buffer back to the MMA warp
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+        }
+        if (sub < SUBS && n0 + sub * 64 < N) {  // uniform within the group
+          if (store_thread) tma_store_wait_read();  // the previous store out of this buffer has read it
+          named_barrier_sync(2 + grp, 128);
+          const float* bsub = bias_s + sub * 64;
+          uint8_t* rowp = cbuf + row_in_tile * 128;
 #pragma unroll
-              for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
-              if (bias != nullptr) {
-                const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + col0 + j));
-                const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias + col0 + j + 4));
-                v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-                v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
-              }
-              uint4 packed;
-              __nv_bfloat162 p0 = __floats2bfloat162_rn(apply_epilogue<EPI>(v[0]), apply_epilogue<EPI>(v[1]));
-              __nv_bfloat162 p1 = __floats2bfloat162_rn(apply_epilogue<EPI>(v[2]), apply_epilogue<EPI>(v[3]));
-              __nv_bfloat162 p2 = __floats2bfloat162_rn(apply_epilogue<EPI>(v[4]), apply_epilogue<EPI>(v[5]));
-              __nv_bfloat162 p3 = __floats2bfloat162_rn(apply_epilogue<EPI>(v[6]), apply_epilogue<EPI>(v[7]));
-              packed.x = *reinterpret_cast<uint32_t*>(&p0);
-              packed.y = *reinterpret_cast<uint32_t*>(&p1);
-              packed.z = *reinterpret_cast<uint32_t*>(&p2);
-              packed.w = *reinterpret_cast<uint32_t*>(&p3);
-              *reinterpret_cast<uint4*>(dst + j) = packed;
-            }
+          for (int c = 0; c < 8; ++c) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(c < 4 ? r0[c * 8 + e] : r1[(c - 4) * 8 + e]);
+            const float4 b0 = *reinterpret_cast<const float4*>(bsub + c * 8);
+            const float4 b1 = *reinterpret_cast<const float4*>(bsub + c * 8 + 4);
+            v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+            v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+            uint4 packed;
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(apply_epilogue<EPI>(v[0]), apply_epilogue<EPI>(v[1]));
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(apply_epilogue<EPI>(v[2]), apply_epilogue<EPI>(v[3]));
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(apply_epilogue<EPI>(v[4]), apply_epilogue<EPI>(v[5]));
+            __nv_bfloat162 p3 = __floats2bfloat162_rn(apply_epilogue<EPI>(v[6]), apply_epilogue<EPI>(v[7]));
+            packed.x = *reinterpret_cast<uint32_t*>(&p0);
+            packed.y = *reinterpret_cast<uint32_t*>(&p1);
+            packed.z = *reinterpret_cast<uint32_t*>(&p2);
+            packed.w = *reinterpret_cast<uint32_t*>(&p3);
+            // 128-byte swizzle: 16-byte chunk c of row r lives at chunk (c ^ (r & 7))
+            *reinterpret_cast<uint4*>(rowp + ((c ^ (row_in_tile & 7)) << 4)) = packed;
+          }
+          fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA (async proxy)
+          named_barrier_sync(2 + grp, 128);
+          if (store_thread) {
+            tma_store_2d(&tmap_c, cbuf, n0 + sub * 64, m0);
+            tma_store_commit();
           }
         }
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
     }
+    if (store_thread) tma_store_wait_read();  // shared memory must outlive the last stores' reads
     if (!ok && lane == 0) atomicExch(err_flag, 3);
   }
 
@@ -267,8 +294,9 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// bf16 row-major [rows, cols] matrix, box = [box_rows, 64 columns], 128-byte swizzle, zero fill.
-int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+// bf16 row-major [rows, cols] matrix, box = [box_rows, 64 columns], 128-byte swizzle; loads zero-fill
+// outside the matrix, stores are clipped.
+int make_tmap_bf16_2d(CUtensorMap_st* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return set_error(B200EMB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
   cuuint64_t dims[2] = {cols, rows};
@@ -283,27 +311,26 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 }
 
 template <int BN, int EPI>
-static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tw, const float* bias, void* C, int M, int N, int K,
-                      int sm_count, int* err_flag, cudaStream_t stream) {
+static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, const float* bias, int M,
+                      int N, int K, int sm_count, int* err_flag, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_bf16_tcgen05_kernel<BN, EPI>;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
   const int tiles = m_tiles * n_tiles;
   const int grid = tiles < sm_count ? tiles : sm_count;
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tw, bias, reinterpret_cast<__nv_bfloat16*>(C), M, N, K,
-                                                        err_flag);
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tw, tc, bias, M, N, K, err_flag);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "gemm launch: %s", cudaGetErrorString(e));
   return B200EMB_OK;
 }
 
 template <int BN>
-static int launch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tw, const float* bias, void* C, int M, int N,
-                      int K, int sm_count, int* err_flag, cudaStream_t stream) {
+static int launch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, const float* bias,
+                      int M, int N, int K, int sm_count, int* err_flag, cudaStream_t stream) {
   switch (epi) {
-    case EPI_BIAS: return launch_cfg<BN, EPI_BIAS>(ta, tw, bias, C, M, N, K, sm_count, err_flag, stream);
-    case EPI_BIAS_GELU: return launch_cfg<BN, EPI_BIAS_GELU>(ta, tw, bias, C, M, N, K, sm_count, err_flag, stream);
-    case EPI_BIAS_TANH: return launch_cfg<BN, EPI_BIAS_TANH>(ta, tw, bias, C, M, N, K, sm_count, err_flag, stream);
+    case EPI_BIAS: return launch_cfg<BN, EPI_BIAS>(ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);
+    case EPI_BIAS_GELU: return launch_cfg<BN, EPI_BIAS_GELU>(ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);
+    case EPI_BIAS_TANH: return launch_cfg<BN, EPI_BIAS_TANH>(ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);
   }
   return set_error(B200EMB_ERR_INVALID, "unknown epilogue %d", epi);
 }
@@ -345,15 +372,17 @@ int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, i
       (reinterpret_cast<uintptr_t>(C) & 15) || (bias && (reinterpret_cast<uintptr_t>(bias) & 15)))
     return set_error(B200EMB_ERR_INVALID, "gemm: pointers must be 16-byte aligned");
   const int bn = force_bn > 0 ? force_bn : gemm_pick_bn(M, N, sm_count);
-  CUtensorMap ta, tw;
+  CUtensorMap ta, tw, tc;
   int rc = make_tmap_bf16_2d(&ta, A, (uint64_t)M, (uint64_t)K, BM);
   if (rc) return rc;
   rc = make_tmap_bf16_2d(&tw, W, (uint64_t)N, (uint64_t)K, (uint32_t)bn);
   if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tc, C, (uint64_t)M, (uint64_t)N, BM);
+  if (rc) return rc;
   switch (bn) {
-    case 256: return launch_epi<256>(epi, ta, tw, bias, C, M, N, K, sm_count, err_flag, stream);
-    case 128: return launch_epi<128>(epi, ta, tw, bias, C, M, N, K, sm_count, err_flag, stream);
-    case 64: return launch_epi<64>(epi, ta, tw, bias, C, M, N, K, sm_count, err_flag, stream);
+    case 256: return launch_epi<256>(epi, ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);
+    case 128: return launch_epi<128>(epi, ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);
+    case 64: return launch_epi<64>(epi, ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);
   }
   return set_error(B200EMB_ERR_INVALID, "gemm: unsupported tile width %d", bn);
 }

@@ -5,6 +5,8 @@
 
 #include "../../include/b200emb.h"
 
+struct CUtensorMap_st;  // the driver API's tensor-map descriptor (cuda.h)
+
 namespace b2 {
 
 enum { EPI_BIAS = B200EMB_EPI_BIAS, EPI_BIAS_GELU = B200EMB_EPI_BIAS_GELU, EPI_BIAS_TANH = B200EMB_EPI_BIAS_TANH };
@@ -27,6 +29,8 @@ int kernels_init_device();
 int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int epi,
                      int sm_count, int* err_flag, cudaStream_t stream, int force_bn);
 int gemm_init_device();
+// TMA descriptor of a bf16 row-major [rows, cols] matrix: box [box_rows x 64 columns], 128-byte swizzle.
+int make_tmap_bf16_2d(::CUtensorMap_st* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 
 // ---- attention (attention.cu) ----
 struct AttnTile {
@@ -35,12 +39,19 @@ struct AttnTile {
   int32_t q_start;    // first query row of this tile, relative to the sequence
   int32_t pad;
 };
-// Builds the tile list on the host: one entry per 64-row query tile, longest sequences first.
+// Builds the tile list on the host: one entry per bq-row query tile, longest sequences first.
 // Returns the number of tiles; `tiles` may be null to only count.
-int attention_build_tiles(const int32_t* h_cu_seqlens, int n_seqs, AttnTile* tiles);
+int attention_build_tiles_q(const int32_t* h_cu_seqlens, int n_seqs, int bq, AttnTile* tiles);
+// Query-tile height of the kernel that serves (head_dim, causal): 128 for the tensor-memory
+// kernel (head_dim 64, bidirectional), 64 for the mma.sync kernel.
+int attention_tile_rows(int head_dim, int causal);
 int launch_attention(const void* qkv, void* out, const AttnTile* d_tiles, int n_tiles, int n_heads, int n_kv_heads,
                      int head_dim, int causal, cudaStream_t stream);
 int attention_init_device();
+// tensor-memory (tcgen05) kernel, head_dim 64, bidirectional (attention_tc.cu)
+int launch_attention_tc(const void* qkv, void* out, const AttnTile* d_tiles, int n_tiles, int n_tokens, int n_heads,
+                        int n_kv_heads, int head_dim, int* err_flag, cudaStream_t stream);
+int attention_tc_init_device();
 
 // ---- row kernels (rowops.cu) ----
 int launch_embed_ln(const int32_t* ids, const int32_t* types, const int32_t* d_cu, int n_seqs, int n_tokens,

@@ -90,6 +90,36 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, ui
       : "memory");
 }
 
+// 2-D tiled store shared -> global (bulk async-group completion). Elements outside the
+// tensor are clipped. The start coordinates must not be negative.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, const void* smem_src, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until the bulk groups committed by this thread have finished READING shared memory.
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t n_threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n_threads) : "memory");
+}
+// Barrier over n_threads that also ANDs a predicate across them.
+__device__ __forceinline__ bool named_barrier_and(uint32_t id, uint32_t n_threads, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n"
+      " .reg .pred p, q;\n"
+      " setp.ne.u32 q, %3, 0;\n"
+      " bar.red.and.pred p, %1, %2, q;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(out)
+      : "r"(id), "r"(n_threads), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return out != 0;
+}
+
 // ---- tcgen05 / TMEM -------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {  // whole warp
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
@@ -138,6 +168,29 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
       : "r"(taddr)
       : "memory");
 }
+// D[tmem] (+)= A[tmem] * B[smem desc]: the A operand (16-bit elements, two per 32-bit column,
+// one row per lane) is read from tensor memory.
+__device__ __forceinline__ void tc_mma_f16_tmem_a(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns, registers -> tensor memory.
+__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor for a K-major bf16 tile whose rows are 128 bytes
@@ -154,6 +207,20 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
   return d;
 }
 
+// Shared-memory matrix descriptor for an MN-major bf16 tile written by TMA with the 128-byte
+// swizzle as rows of 64 elements (the MN dimension is contiguous, 128 bytes wide; consecutive
+// K indices are consecutive 128-byte rows): 8-row K groups are 1024 bytes apart (stride byte
+// offset); lbo_bytes = distance between 64-element blocks along MN (unused when MN == 64).
+__device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
 // Instruction descriptor for kind::f16, bf16 x bf16 -> fp32, both operands K-major.
 __host__ __device__ constexpr uint32_t make_idesc_bf16_f32(int m, int n) {
   return (1u << 4)                               // accumulator format fp32
@@ -161,6 +228,10 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16_f32(int m, int n) {
          | (1u << 10)                            // B = bf16
          | (static_cast<uint32_t>(n >> 3) << 17) // N / 8
          | (static_cast<uint32_t>(m >> 4) << 24);  // M / 16
+}
+// Same with the B operand MN-major (bit 16).
+__host__ __device__ constexpr uint32_t make_idesc_bf16_f32_b_mn(int m, int n) {
+  return make_idesc_bf16_f32(m, n) | (1u << 16);
 }
 
 }  // namespace b2

@@ -41,6 +41,7 @@ int kernels_init_device() {
   if (dev >= 0 && dev < 64 && g_dev_inited[dev]) return B200EMB_OK;
   int rc = gemm_init_device();
   if (!rc) rc = attention_init_device();
+  if (!rc) rc = attention_tc_init_device();
   if (rc) return rc;
   if (dev >= 0 && dev < 64) g_dev_inited[dev] = true;
   return B200EMB_OK;
@@ -365,7 +366,11 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
     if (rc) return rc;
     {
       KernelScope ks(c, B200EMB_KCLASS_ATTN);
-      rc = launch_attention(c->qkv, c->ctx, c->d_tiles, n_tiles, d.n_heads, d.n_kv_heads, d.head_dim, 0, c->stream);
+      if (attention_tile_rows(d.head_dim, 0) == 128)
+        rc = launch_attention_tc(c->qkv, c->ctx, c->d_tiles, n_tiles, T, d.n_heads, d.n_kv_heads, d.head_dim, c->d_err,
+                                 c->stream);
+      else
+        rc = launch_attention(c->qkv, c->ctx, c->d_tiles, n_tiles, d.n_heads, d.n_kv_heads, d.head_dim, 0, c->stream);
       if (rc) return rc;
     }
     rc = gemm(c, c->ctx, L.o_w, L.o_b, c->y, T, H, d.n_heads * d.head_dim, EPI_BIAS);
@@ -463,10 +468,11 @@ static void run_shard(b200emb_handle* h, DeviceCtx* c, const int32_t* ids, const
   c->per_kernel = per_kernel;
   c->kev_used = 0;
   if (n_seqs == 0) return;
-  const int n_tiles = attention_build_tiles(cu, n_seqs, nullptr);
+  const int bq = attention_tile_rows(h->desc.head_dim, 0);
+  const int n_tiles = attention_build_tiles_q(cu, n_seqs, bq, nullptr);
   int rc = ensure_capacity(h, c, n_tokens, n_seqs, n_tiles);
   if (rc) return fail(rc);
-  attention_build_tiles(cu, n_seqs, c->h_tiles);
+  attention_build_tiles_q(cu, n_seqs, bq, c->h_tiles);
   cudaStream_t s = c->stream;
   const bool use_types = types != nullptr && h->desc.type_vocab > 0;
 #define B2_TRY(expr)                                                                              \
@@ -733,10 +739,11 @@ int b200emb_forward_device(b200emb_handle* h, const int32_t* d_input_ids, const 
   c->gemm_flops = 0;
   c->per_kernel = timing != nullptr && timing->per_kernel != 0;
   c->kev_used = 0;
-  const int n_tiles = attention_build_tiles(h_cu_seqlens, n_seqs, nullptr);
+  const int bq = attention_tile_rows(h->desc.head_dim, 0);
+  const int n_tiles = attention_build_tiles_q(h_cu_seqlens, n_seqs, bq, nullptr);
   int rc = ensure_capacity(h, c, n_tokens, n_seqs, n_tiles);
   if (rc) return rc;
-  attention_build_tiles(h_cu_seqlens, n_seqs, c->h_tiles);
+  attention_build_tiles_q(h_cu_seqlens, n_seqs, bq, c->h_tiles);
   cudaStream_t s = c->stream;
   B2_CUDA_CHECK(cudaEventRecord(c->ev[0], s));
   B2_CUDA_CHECK(cudaMemcpyAsync(c->d_tiles, c->h_tiles, sizeof(AttnTile) * n_tiles, cudaMemcpyHostToDevice, s));
@@ -773,6 +780,22 @@ int b200emb_forward_device(b200emb_handle* h, const int32_t* d_input_ids, const 
 
 // ---- single kernels ---------------------------------------------------------------------
 
+// One error word per device for the single-kernel entry points, allocated on first use and kept.
+static int op_error_word(int** out) {
+  static std::mutex mu;
+  static int* words[64] = {};
+  int dev = 0;
+  B2_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return set_error(B200EMB_ERR_UNSUPPORTED, "device index %d too large", dev);
+  std::lock_guard<std::mutex> lk(mu);
+  if (words[dev] == nullptr) {
+    B2_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&words[dev]), sizeof(int)));
+    B2_CUDA_CHECK(cudaMemset(words[dev], 0, sizeof(int)));
+  }
+  *out = words[dev];
+  return B200EMB_OK;
+}
+
 static int current_sm_count(int* out) {
   int dev = 0;
   B2_CUDA_CHECK(cudaGetDevice(&dev));
@@ -790,18 +813,20 @@ int b200emb_op_gemm_bf16(const void* A, const void* W, const float* bias, void* 
   if (rc) return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   int* d_err = nullptr;
-  B2_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&d_err), sizeof(int)));
-  cudaMemsetAsync(d_err, 0, sizeof(int), s);
+  rc = op_error_word(&d_err);
+  if (rc) return rc;
   // epilogue values >= 0x100 select the tile width in the upper bits (tests only): (bn << 8) | epi
   const int force_bn = epilogue >> 8;
   rc = launch_gemm_bf16(A, W, bias, C, M, N, K, epilogue & 0xff, sms, d_err, s, force_bn);
   int herr = 0;
   cudaError_t e = cudaMemcpyAsync(&herr, d_err, sizeof(int), cudaMemcpyDeviceToHost, s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
-  cudaFree(d_err);
   if (rc) return rc;
   if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "gemm: %s", cudaGetErrorString(e));
-  if (herr != 0) return set_error(B200EMB_ERR_DEVICE_WAIT, "gemm: a device-side wait gave up (role %d)", herr);
+  if (herr != 0) {
+    cudaMemset(d_err, 0, sizeof(int));
+    return set_error(B200EMB_ERR_DEVICE_WAIT, "gemm: a device-side wait gave up (role %d)", herr);
+  }
   return B200EMB_OK;
 }
 
@@ -818,17 +843,30 @@ int b200emb_op_attention(const void* qkv, void* out, const int32_t* d_cu_seqlens
   int rc = kernels_init_device();
   if (rc) return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const int n_tiles = attention_build_tiles(h_cu_seqlens, n_seqs, nullptr);
+  const int force_legacy = (causal >> 8) & 1;  // bit 8: use the mma.sync kernel whatever the shape (tests)
+  causal &= 1;
+  const bool use_tc = !force_legacy && attention_tile_rows(head_dim, causal) == 128;
+  const int bq = use_tc ? 128 : 64;
+  const int n_tiles = attention_build_tiles_q(h_cu_seqlens, n_seqs, bq, nullptr);
   std::vector<AttnTile> tiles(n_tiles);
-  attention_build_tiles(h_cu_seqlens, n_seqs, tiles.data());
+  attention_build_tiles_q(h_cu_seqlens, n_seqs, bq, tiles.data());
   AttnTile* d_tiles = nullptr;
-  B2_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&d_tiles), sizeof(AttnTile) * n_tiles));
+  int* d_err = nullptr;
+  B2_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&d_tiles), sizeof(AttnTile) * n_tiles + sizeof(int)));
+  d_err = reinterpret_cast<int*>(d_tiles + n_tiles);
+  cudaMemsetAsync(d_err, 0, sizeof(int), s);
   cudaMemcpyAsync(d_tiles, tiles.data(), sizeof(AttnTile) * n_tiles, cudaMemcpyHostToDevice, s);
-  rc = launch_attention(qkv, out, d_tiles, n_tiles, n_heads, n_kv_heads, head_dim, causal, s);
-  cudaError_t e = cudaStreamSynchronize(s);
+  if (use_tc)
+    rc = launch_attention_tc(qkv, out, d_tiles, n_tiles, n_tokens, n_heads, n_kv_heads, head_dim, d_err, s);
+  else
+    rc = launch_attention(qkv, out, d_tiles, n_tiles, n_heads, n_kv_heads, head_dim, causal, s);
+  int herr = 0;
+  cudaError_t e = cudaMemcpyAsync(&herr, d_err, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   cudaFree(d_tiles);
   if (rc) return rc;
   if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "attention: %s", cudaGetErrorString(e));
+  if (herr != 0) return set_error(B200EMB_ERR_DEVICE_WAIT, "attention: a device-side wait gave up (role %d)", herr);
   return B200EMB_OK;
 }
 

@@ -97,9 +97,9 @@ def _attention_ref(qkv, cu, nh, nkv, d, causal):
 
 
 @pytest.mark.parametrize("d,nh,nkv", [(32, 12, 12), (64, 16, 16), (64, 4, 4), (128, 8, 2), (128, 4, 4)])
-@pytest.mark.parametrize("causal", [0, 1])
+@pytest.mark.parametrize("causal", [0, 1, 0x100])  # 0x100: bidirectional on the mma.sync kernel
 def test_attention_varlen(lib, d, nh, nkv, causal):
-    lens = [1, 7, 64, 65, 128, 200, 63, 512, 33, 300]
+    lens = [1, 7, 64, 65, 128, 200, 63, 512, 33, 300, 129, 16, 17, 384]
     cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
     T = int(cu[-1])
     g = torch.Generator(device="cuda").manual_seed(d + nh + causal)
@@ -109,7 +109,7 @@ def test_attention_varlen(lib, d, nh, nkv, causal):
     torch.cuda.synchronize()
     _lib.check(lib.b200emb_op_attention(qkv.data_ptr(), out.data_ptr(), d_cu.data_ptr(), cu.ctypes.data, len(lens), T,
                                         nh, nkv, d, causal, _stream()))
-    ref = _attention_ref(qkv, cu, nh, nkv, d, causal)
+    ref = _attention_ref(qkv, cu, nh, nkv, d, causal & 1)
     assert not torch.isnan(out.float()).any()
     err = (out.float() - ref).abs().max().item()
     assert err < 2e-2, err  # P and the output are rounded to bf16 (values are O(1))
