@@ -50,7 +50,7 @@ int launch_attention(const void* qkv, void* out, const AttnTile* d_tiles, int n_
 int attention_init_device();
 // tensor-memory (tcgen05) kernel, head_dim 64, bidirectional (attention_tc.cu)
 int launch_attention_tc(const void* qkv, void* out, const AttnTile* d_tiles, int n_tiles, int n_tokens, int n_heads,
-                        int n_kv_heads, int head_dim, int* err_flag, cudaStream_t stream);
+                        int n_kv_heads, int head_dim, int sm_count, int* err_flag, cudaStream_t stream);
 int attention_tc_init_device();
 
 // ---- row kernels (rowops.cu) ----

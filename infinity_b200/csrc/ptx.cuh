@@ -50,16 +50,19 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+// One probe of the barrier. The hardware may park the thread for up to `suspend_ns` while the
+// phase is pending (it resumes as soon as the phase completes), which keeps waiting warps from
+// burning issue slots that co-resident warps need.
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t suspend_ns = 1000) {
   uint32_t ok;
   asm volatile(
       "{\n"
       " .reg .pred p;\n"
-      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
       " selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(suspend_ns)
       : "memory");
   return ok != 0;
 }
@@ -71,7 +74,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   uint32_t polls = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++polls & 0xffu) == 0u) {
+    if ((++polls & 0x3fu) == 0u) {
       if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) return false;
     }
   }

@@ -367,8 +367,8 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
     {
       KernelScope ks(c, B200EMB_KCLASS_ATTN);
       if (attention_tile_rows(d.head_dim, 0) == 128)
-        rc = launch_attention_tc(c->qkv, c->ctx, c->d_tiles, n_tiles, T, d.n_heads, d.n_kv_heads, d.head_dim, c->d_err,
-                                 c->stream);
+        rc = launch_attention_tc(c->qkv, c->ctx, c->d_tiles, n_tiles, T, d.n_heads, d.n_kv_heads, d.head_dim, c->sm_count,
+                                 c->d_err, c->stream);
       else
         rc = launch_attention(c->qkv, c->ctx, c->d_tiles, n_tiles, d.n_heads, d.n_kv_heads, d.head_dim, 0, c->stream);
       if (rc) return rc;
@@ -857,7 +857,11 @@ int b200emb_op_attention(const void* qkv, void* out, const int32_t* d_cu_seqlens
   cudaMemsetAsync(d_err, 0, sizeof(int), s);
   cudaMemcpyAsync(d_tiles, tiles.data(), sizeof(AttnTile) * n_tiles, cudaMemcpyHostToDevice, s);
   if (use_tc)
-    rc = launch_attention_tc(qkv, out, d_tiles, n_tiles, n_tokens, n_heads, n_kv_heads, head_dim, d_err, s);
+  {
+    int sms = 0;
+    rc = current_sm_count(&sms);
+    if (!rc) rc = launch_attention_tc(qkv, out, d_tiles, n_tiles, n_tokens, n_heads, n_kv_heads, head_dim, sms, d_err, s);
+  }
   else
     rc = launch_attention(qkv, out, d_tiles, n_tiles, n_heads, n_kv_heads, head_dim, causal, s);
   int herr = 0;
