@@ -192,6 +192,24 @@ int b200emb_op_attention(const void* qkv, void* out, const int32_t* d_cu_seqlens
                          int32_t n_seqs, int32_t n_tokens, int32_t n_heads, int32_t n_kv_heads,
                          int32_t head_dim, int32_t causal, void* stream);
 
+/* The same attention for callers that must not allocate device memory. No counterpart in the
+ * reference: it exists for processes whose framework pool already holds nearly all GPU memory
+ * (so a cudaMalloc inside a library call may fail) and for latency-critical threads that
+ * cannot afford cudaMalloc / cudaFree, which synchronise the whole device.
+ * Same arguments and result as b200emb_op_attention (without its 0x100 flag), but the
+ * query-tile list and the error word live in a fixed array inside the library
+ * (B200EMB_STATIC_ATTN_MAX_TILES tile records, about 256 KB, present on every GPU that loads
+ * the library until the process exits) and the list is built by a kernel from d_cu_seqlens.
+ * The call makes no cudaMalloc, cudaFree or other allocating call. A batch that needs more
+ * query tiles (128 rows each for head_dim 64 bidirectional, else 64 rows) is rejected with
+ * B200EMB_ERR_UNSUPPORTED. The first call on each device looks up the array's device address;
+ * make that first call before any stream capture. All calls on a device share the array:
+ * two calls whose kernels overlap on the GPU (different streams or threads) race on it. */
+#define B200EMB_STATIC_ATTN_MAX_TILES 16384
+int b200emb_op_attention_static(const void* qkv, void* out, const int32_t* d_cu_seqlens,
+                                const int32_t* h_cu_seqlens, int32_t n_seqs, int32_t n_tokens, int32_t n_heads,
+                                int32_t n_kv_heads, int32_t head_dim, int32_t causal, void* stream);
+
 /* x[t,:] = LayerNorm(word[ids[t]] + pos[pos_offset + t - cu_seqlens[seq(t)]] + type[types[t]]) -> bf16.
  * Tables are bf16, gamma/beta fp32. type_table / types nullable. With
  * gamma == NULL the sum is written without normalisation (decoder gather). */
