@@ -66,10 +66,10 @@ __device__ __forceinline__ void layernorm_store(float (&v)[NCH][8], int lane, in
   for (int i = 0; i < NCH; ++i) {
     const int c = lane + 32 * i;
     if (c < n_chunks) {
-      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + c * 8));
-      const float4 g1 = __ldg(reinterpret_cast<const float4*>(gamma + c * 8 + 4));
-      const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta + c * 8));
-      const float4 b1 = __ldg(reinterpret_cast<const float4*>(beta + c * 8 + 4));
+      const float4 g0 = *reinterpret_cast<const float4*>(gamma + c * 8);
+      const float4 g1 = *reinterpret_cast<const float4*>(gamma + c * 8 + 4);
+      const float4 b0 = *reinterpret_cast<const float4*>(beta + c * 8);
+      const float4 b1 = *reinterpret_cast<const float4*>(beta + c * 8 + 4);
       float o[8];
       o[0] = (v[i][0] - mean) * rstd * g0.x + b0.x;
       o[1] = (v[i][1] - mean) * rstd * g0.y + b0.y;
@@ -140,32 +140,61 @@ embed_ln_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ typ
   layernorm_store<NCH>(v, lane, n_chunks, hidden, gamma, beta, eps, dst);
 }
 
+// Persistent: every warp walks rows warp_id, warp_id + n_warps, ...; gamma and beta are staged once
+// per CTA in shared memory, and the loads of the next row are issued before the current row is
+// reduced, so each warp keeps two rows of loads in flight.
 template <int NCH>
 __global__ void __launch_bounds__(ROW_WARPS * 32)
 add_ln_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ y,
               const float* __restrict__ gamma, const float* __restrict__ beta, int n_rows, int hidden, float eps,
               __nv_bfloat16* __restrict__ out) {
-  const int row = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
-  if (row >= n_rows) return;
+  extern __shared__ float ln_smem[];  // gamma[hidden], beta[hidden]
+  float* g_s = ln_smem;
+  float* b_s = ln_smem + hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    g_s[i] = gamma[i];
+    b_s[i] = beta[i];
+  }
+  __syncthreads();
   const int lane = threadIdx.x & 31;
   const int n_chunks = hidden >> 3;
-  const __nv_bfloat16* xr = x + static_cast<size_t>(row) * hidden;
-  const __nv_bfloat16* yr = y != nullptr ? y + static_cast<size_t>(row) * hidden : nullptr;
-  float v[NCH][8];
+  const int warps_total = gridDim.x * ROW_WARPS;
+  int row = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  uint4 xn[NCH], yn[NCH];
+  auto load_row = [&](int r) {
+    const __nv_bfloat16* xr = x + static_cast<size_t>(r) * hidden;
+    const __nv_bfloat16* yr = y != nullptr ? y + static_cast<size_t>(r) * hidden : nullptr;
 #pragma unroll
-  for (int i = 0; i < NCH; ++i) {
-    const int c = lane + 32 * i;
-    if (c < n_chunks) {
-      unpack8(*reinterpret_cast<const uint4*>(xr + c * 8), v[i]);
-      if (yr != nullptr) {
-        float a[8];
-        unpack8(*reinterpret_cast<const uint4*>(yr + c * 8), a);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) v[i][e] += a[e];
+    for (int i = 0; i < NCH; ++i) {
+      const int c = lane + 32 * i;
+      if (c < n_chunks) {
+        xn[i] = *reinterpret_cast<const uint4*>(xr + c * 8);
+        if (yr != nullptr) yn[i] = *reinterpret_cast<const uint4*>(yr + c * 8);
       }
     }
+  };
+  load_row(row);
+  while (row < n_rows) {
+    float v[NCH][8];
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const int c = lane + 32 * i;
+      if (c < n_chunks) {
+        unpack8(xn[i], v[i]);
+        if (y != nullptr) {
+          float a[8];
+          unpack8(yn[i], a);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[i][e] += a[e];
+        }
+      }
+    }
+    const int next = row + warps_total;
+    if (next < n_rows) load_row(next);  // in flight while this row is reduced and stored
+    layernorm_store<NCH>(v, lane, n_chunks, hidden, g_s, b_s, eps, out + static_cast<size_t>(row) * hidden);
+    row = next;
   }
-  layernorm_store<NCH>(v, lane, n_chunks, hidden, gamma, beta, eps, out + static_cast<size_t>(row) * hidden);
 }
 
 // One CTA per sequence. Threads tile the hidden dimension in 16-byte chunks; when the block
@@ -318,8 +347,13 @@ int launch_add_ln(const void* x, const void* y, const float* gamma, const float*
   int rc = check_hidden(hidden, 16);
   if (rc) return rc;
   const int nch = ((hidden >> 3) + 31) / 32;
-  const int grid = (n_rows + ROW_WARPS - 1) / ROW_WARPS;
-  B2_DISPATCH_NCH(nch, (add_ln_kernel<NCH><<<grid, ROW_WARPS * 32, 0, stream>>>(
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int full = (n_rows + ROW_WARPS - 1) / ROW_WARPS;
+  const int grid = full < sms * 4 ? full : sms * 4;  // persistent: a few CTAs per SM walk all rows
+  const size_t ln_smem = 2 * static_cast<size_t>(hidden) * sizeof(float);
+  B2_DISPATCH_NCH(nch, (add_ln_kernel<NCH><<<grid, ROW_WARPS * 32, ln_smem, stream>>>(
                            reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(y),
                            gamma, beta, n_rows, hidden, eps, reinterpret_cast<__nv_bfloat16*>(out))));
   cudaError_t e = cudaGetLastError();
