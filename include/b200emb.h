@@ -71,6 +71,9 @@ extern "C" {
 #define B200EMB_EPI_BIAS 0
 #define B200EMB_EPI_BIAS_GELU 1 /* exact (erf) GELU */
 #define B200EMB_EPI_BIAS_TANH 2
+/* SwiGLU: W is [2F, K] in blocks of 256 rows = 128 gate rows followed by the 128 up rows of the same
+ * output columns; C is [M, F] with C[:, j] = silu(gate_j) * up_j. N passed to the call is 2F. */
+#define B200EMB_EPI_BIAS_SWIGLU 3
 
 typedef struct b200emb_model_desc {
   int32_t abi_version; /* B200EMB_ABI_VERSION */
@@ -176,7 +179,7 @@ int b200emb_device_count(void);
  * each is one step of the third-party torch forward the reference calls at
  * sentence_transformer.py:124. */
 
-/* C[M,N] (bf16) = epilogue(A[M,K] (bf16, row-major) * W[N,K]^T (bf16, row-major) + bias[N] (fp32, nullable)).
+/* C[M,N] (bf16; [M, N/2] for the SwiGLU epilogue) = epilogue(A[M,K] (bf16, row-major) * W[N,K]^T (bf16, row-major) + bias[N] (fp32, nullable)).
  * K % 8 == 0, N % 8 == 0. tcgen05 / TMEM kernel fed by TMA. Synchronises the
  * stream before returning and reports a device-side wait that gave up. */
 int b200emb_op_gemm_bf16(const void* A, const void* W, const float* bias, void* C, int32_t M, int32_t N,

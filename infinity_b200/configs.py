@@ -57,8 +57,12 @@ XLMR_LARGE_RERANK = ModelSpec(name="xlmr-large-reranker-shape", arch="xlmr", n_l
                               pos_offset=2, norm_eps=1e-5, pooling="cls", normalize=False, head="classifier",
                               n_labels=1)
 
-SPECS: Dict[str, ModelSpec] = {"c1": BGE_SMALL, "c2": BERT_LARGE, "c3": XLMR_LARGE_RERANK}
-SEEDS = {"c1": (1001, 2001, 3001), "c2": (1002, 2002, 3002), "c3": (1003, 2003, 3003)}
+QWEN2_7B = ModelSpec(name="qwen2-7b-shape", arch="decoder", n_layers=28, hidden=3584, n_heads=28, n_kv_heads=4,
+                     head_dim=128, ffn=18944, vocab=151646, max_pos=2048, type_vocab=0, norm_eps=1e-6,
+                     rope_theta=1e6, pooling="last", max_len=2048)
+
+SPECS: Dict[str, ModelSpec] = {"c1": BGE_SMALL, "c2": BERT_LARGE, "c3": XLMR_LARGE_RERANK, "c5": QWEN2_7B}
+SEEDS = {"c1": (1001, 2001, 3001), "c2": (1002, 2002, 3002), "c3": (1003, 2003, 3003), "c5": (1005, 2005, 3005)}
 
 
 def tiny_spec(arch: str = "bert", **kw) -> ModelSpec:
@@ -68,6 +72,9 @@ def tiny_spec(arch: str = "bert", **kw) -> ModelSpec:
     if arch == "xlmr":
         base.update(type_vocab=1, pos_offset=2, norm_eps=1e-5, pooling="cls", normalize=False, head="classifier",
                     n_labels=1)
+    if arch == "decoder":
+        base.update(hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=384, type_vocab=0, norm_eps=1e-6,
+                    rope_theta=1e6, pooling="last", max_pos=320, max_len=320)
     base.update(kw)
     return ModelSpec(**base)
 
@@ -95,6 +102,18 @@ def init_weights(spec: ModelSpec, seed: int, perturb: bool = False) -> Dict[str,
 
     w: Dict[str, torch.Tensor] = {}
     w["emb.word"] = mat(spec.vocab, H)
+    if spec.arch == "decoder":
+        # Qwen2 layout: q/k/v carry biases, o / gate / up / down do not; RMSNorm gains only
+        for l in range(spec.n_layers):
+            p = f"layer.{l}."
+            w[p + "ln1.g"] = gain(H)
+            w[p + "qkv.w"], w[p + "qkv.b"] = mat(QKV, H), bias(QKV)
+            w[p + "o.w"] = mat(H, spec.n_heads * spec.head_dim)
+            w[p + "ln2.g"] = gain(H)
+            w[p + "gate.w"], w[p + "up.w"] = mat(F, H), mat(F, H)
+            w[p + "down.w"] = mat(H, F)
+        w["norm.g"] = gain(H)
+        return w
     w["emb.pos"] = mat(spec.max_pos, H)
     if spec.type_vocab > 0:
         w["emb.type"] = mat(spec.type_vocab, H)
@@ -117,9 +136,28 @@ def is_matrix(name: str) -> bool:
     return name.endswith(".w") or name in ("emb.word", "emb.pos", "emb.type")
 
 
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, block: int = 128) -> torch.Tensor:
+    """[F, H] gate and up matrices -> one [2F, H] matrix in blocks of ``block`` gate rows followed by
+    the ``block`` up rows of the same output columns (the layout the fused SwiGLU epilogue reads)."""
+    F, H = gate.shape
+    assert F % block == 0 and up.shape == gate.shape
+    g = gate.reshape(F // block, block, H)
+    u = up.reshape(F // block, block, H)
+    return torch.stack([g, u], dim=1).reshape(2 * F, H).contiguous()
+
+
 def runtime_tensors(master: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
-    """What the CUDA runtime loads: matrices and tables in bf16, vectors in fp32."""
-    return {k: (v.to(torch.bfloat16) if is_matrix(k) else v.float()) for k, v in master.items()}
+    """What the CUDA runtime loads: matrices and tables in bf16, vectors in fp32; the decoder's
+    gate and up projections fused block-interleaved into ``gu.w``."""
+    out: Dict[str, torch.Tensor] = {}
+    for k, v in master.items():
+        if k.endswith("gate.w"):
+            out[k[:-6] + "gu.w"] = interleave_gate_up(v, master[k[:-6] + "up.w"]).to(torch.bfloat16)
+        elif k.endswith("up.w"):
+            continue
+        else:
+            out[k] = v.to(torch.bfloat16) if is_matrix(k) else v.float()
+    return out
 
 
 def oracle_tensors(spec: ModelSpec, master: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
@@ -189,6 +227,10 @@ def synth_batch(cfg: str, n_seqs: Optional[int] = None, seed_offset: int = 0) ->
             s[0] = 101  # CLS
             seqs.append(s)
         return pack(seqs)
+    if cfg == "c5":
+        n = n_seqs if n_seqs is not None else 512
+        lens = np.random.default_rng(len_seed).integers(32, 2049, size=n)
+        return pack([rng.integers(1000, 151646, size=int(L)) for L in lens])
     if cfg == "c3":
         n = n_seqs if n_seqs is not None else 2048
         lrng = np.random.default_rng(len_seed)

@@ -46,6 +46,8 @@ struct GemmCfg {
 
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
 
+__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
 template <int EPI>
 __device__ __forceinline__ float apply_epilogue(float v) {
   if (EPI == EPI_BIAS_GELU) return gelu_erf(v);
@@ -213,6 +215,57 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      if constexpr (EPI == EPI_BIAS_SWIGLU) {
+        // The tile's accumulator columns are [gate block | up block] (BN/2 each): output column j of
+        // this tile = silu(gate_j) * up_j. Group g owns output columns [64 g, 64 g + 64).
+        const int out_col0 = (n0 >> 1) + grp * 64;
+        const bool have = (grp * 64 < BN / 2) && out_col0 < (N >> 1);  // uniform within the group
+        if (have) {
+          if (store_thread) tma_store_wait_read();
+          named_barrier_sync(2 + grp, 128);
+        }
+        uint8_t* rowp = cbuf + row_in_tile * 128;
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+          uint32_t g[32], u[32];
+          if (grp * 64 < BN / 2) {
+            tmem_ld_32x32b_x32(t_row + grp * 64 + p * 32, g);
+            tmem_ld_32x32b_x32(t_row + BN / 2 + grp * 64 + p * 32, u);
+            tmem_ld_wait();
+          }
+          if (p == 1) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+          }
+          if (have) {
+            const float* bg = bias_s + grp * 64 + p * 32;
+            const float* bu = bias_s + BN / 2 + grp * 64 + p * 32;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 8; e += 2) {
+                const float a0 = silu_f(__uint_as_float(g[c * 8 + e]) + bg[c * 8 + e]) * (__uint_as_float(u[c * 8 + e]) + bu[c * 8 + e]);
+                const float a1 = silu_f(__uint_as_float(g[c * 8 + e + 1]) + bg[c * 8 + e + 1]) *
+                                 (__uint_as_float(u[c * 8 + e + 1]) + bu[c * 8 + e + 1]);
+                __nv_bfloat162 pr = __floats2bfloat162_rn(a0, a1);
+                w[e >> 1] = *reinterpret_cast<uint32_t*>(&pr);
+              }
+              const int chunk = p * 4 + c;
+              *reinterpret_cast<uint4*>(rowp + ((chunk ^ (row_in_tile & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+        if (have) {
+          fence_proxy_async_smem();
+          named_barrier_sync(2 + grp, 128);
+          if (store_thread) {
+            tma_store_2d(&tmap_c, cbuf, out_col0, m0);
+            tma_store_commit();
+          }
+        }
+      } else {
 #pragma unroll
       for (int st = 0; st < SUBS_PER_GROUP; ++st) {
         const int sub = grp * SUBS_PER_GROUP + st;
@@ -261,6 +314,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             tma_store_commit();
           }
         }
+      }
       }
     }
     if (store_thread) tma_store_wait_read();  // shared memory must outlive the last stores' reads
@@ -331,6 +385,9 @@ static int launch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tw, con
     case EPI_BIAS: return launch_cfg<BN, EPI_BIAS>(ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);
     case EPI_BIAS_GELU: return launch_cfg<BN, EPI_BIAS_GELU>(ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);
     case EPI_BIAS_TANH: return launch_cfg<BN, EPI_BIAS_TANH>(ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);
+    case EPI_BIAS_SWIGLU:
+      if constexpr (BN == 256) return launch_cfg<BN, EPI_BIAS_SWIGLU>(ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);
+      break;
   }
   return set_error(B200EMB_ERR_INVALID, "unknown epilogue %d", epi);
 }
@@ -346,6 +403,9 @@ static int init_bn() {
   int rc = init_one<BN, EPI_BIAS>();
   if (!rc) rc = init_one<BN, EPI_BIAS_GELU>();
   if (!rc) rc = init_one<BN, EPI_BIAS_TANH>();
+  if constexpr (BN == 256) {
+    if (!rc) rc = init_one<BN, EPI_BIAS_SWIGLU>();
+  }
   return rc;
 }
 int gemm_init_device() {
@@ -371,13 +431,20 @@ int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, i
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) ||
       (reinterpret_cast<uintptr_t>(C) & 15) || (bias && (reinterpret_cast<uintptr_t>(bias) & 15)))
     return set_error(B200EMB_ERR_INVALID, "gemm: pointers must be 16-byte aligned");
-  const int bn = force_bn > 0 ? force_bn : gemm_pick_bn(M, N, sm_count);
+  int bn = force_bn > 0 ? force_bn : gemm_pick_bn(M, N, sm_count);
+  int n_out = N;
+  if (epi == EPI_BIAS_SWIGLU) {
+    // W holds 128-row blocks [gate rows | up rows]; a 256-wide tile yields 128 output columns
+    if (N % 256 != 0) return set_error(B200EMB_ERR_INVALID, "gemm: the SwiGLU epilogue needs N %% 256 == 0 (N=%d)", N);
+    bn = 256;
+    n_out = N / 2;
+  }
   CUtensorMap ta, tw, tc;
   int rc = make_tmap_bf16_2d(&ta, A, (uint64_t)M, (uint64_t)K, BM);
   if (rc) return rc;
   rc = make_tmap_bf16_2d(&tw, W, (uint64_t)N, (uint64_t)K, (uint32_t)bn);
   if (rc) return rc;
-  rc = make_tmap_bf16_2d(&tc, C, (uint64_t)M, (uint64_t)N, BM);
+  rc = make_tmap_bf16_2d(&tc, C, (uint64_t)M, (uint64_t)n_out, BM);
   if (rc) return rc;
   switch (bn) {
     case 256: return launch_epi<256>(epi, ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);

@@ -9,7 +9,12 @@ struct CUtensorMap_st;  // the driver API's tensor-map descriptor (cuda.h)
 
 namespace b2 {
 
-enum { EPI_BIAS = B200EMB_EPI_BIAS, EPI_BIAS_GELU = B200EMB_EPI_BIAS_GELU, EPI_BIAS_TANH = B200EMB_EPI_BIAS_TANH };
+enum {
+  EPI_BIAS = B200EMB_EPI_BIAS,
+  EPI_BIAS_GELU = B200EMB_EPI_BIAS_GELU,
+  EPI_BIAS_TANH = B200EMB_EPI_BIAS_TANH,
+  EPI_BIAS_SWIGLU = B200EMB_EPI_BIAS_SWIGLU
+};
 
 // Records a thread-local error message and returns `code`.
 int set_error(int code, const char* fmt, ...);
@@ -59,6 +64,13 @@ int launch_embed_ln(const int32_t* ids, const int32_t* types, const int32_t* d_c
                     int hidden, int pos_offset, float eps, void* out, cudaStream_t stream);
 int launch_add_ln(const void* x, const void* y, const float* gamma, const float* beta, int n_rows, int hidden,
                   float eps, void* out, cudaStream_t stream);
+// h (fp32) += y (bf16, nullable); out = RMSNorm(h) * gamma (bf16)
+int launch_add_rmsnorm(float* h, const void* y, const float* gamma, int n_rows, int hidden, float eps, void* out,
+                       cudaStream_t stream);
+int launch_widen(const void* x, float* out, size_t n_elems, cudaStream_t stream);
+// rotates the first n_rot_heads heads (queries then keys) of every qkv row in place; cos_sin = [max_pos, head_dim/2] (cos, sin) pairs
+int launch_rope(void* qkv, const int32_t* d_cu, int n_seqs, int n_tokens, int n_rot_heads, int row_width,
+                int head_dim, const float* cos_sin, cudaStream_t stream);
 int launch_pool(const void* x, const int32_t* d_cu, int n_seqs, int hidden, int pooling, int normalize, void* out,
                 int64_t out_row_stride, int out_bf16, cudaStream_t stream);
 // logits[i, l] = dot(x[i, :], W[l, :]) + b[l]; x bf16 [n, hidden], W bf16 [n_labels, hidden], out fp32.

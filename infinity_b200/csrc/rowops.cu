@@ -197,6 +197,109 @@ add_ln_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   }
 }
 
+// Pre-norm residual step of decoder blocks: h (fp32 residual stream) += y (bf16 sub-layer output,
+// nullable), then out = h / sqrt(mean(h^2) + eps) * gamma in bf16. Persistent warps, gamma in
+// shared memory. The residual stream stays fp32 so that 2 x n_layers additions do not
+// accumulate bf16 rounding.
+template <int NCH>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+add_rmsnorm_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ y, const float* __restrict__ gamma,
+                   int n_rows, int hidden, float eps, __nv_bfloat16* __restrict__ out) {
+  extern __shared__ float ln_smem[];
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) ln_smem[i] = gamma[i];
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int n_chunks = hidden >> 3;
+  const int warps_total = gridDim.x * ROW_WARPS;
+  for (int row = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5); row < n_rows; row += warps_total) {
+    float* hr = h + static_cast<size_t>(row) * hidden;
+    const __nv_bfloat16* yr = y != nullptr ? y + static_cast<size_t>(row) * hidden : nullptr;
+    float v[NCH][8];
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const int c = lane + 32 * i;
+      if (c < n_chunks) {
+        const float4 a0 = *reinterpret_cast<const float4*>(hr + c * 8);
+        const float4 a1 = *reinterpret_cast<const float4*>(hr + c * 8 + 4);
+        v[i][0] = a0.x; v[i][1] = a0.y; v[i][2] = a0.z; v[i][3] = a0.w;
+        v[i][4] = a1.x; v[i][5] = a1.y; v[i][6] = a1.z; v[i][7] = a1.w;
+        if (yr != nullptr) {
+          float b[8];
+          unpack8(*reinterpret_cast<const uint4*>(yr + c * 8), b);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[i][e] += b[e];
+          *reinterpret_cast<float4*>(hr + c * 8) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+          *reinterpret_cast<float4*>(hr + c * 8 + 4) = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sq += v[i][e] * v[i][e];
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(sq) / hidden + eps);
+    __nv_bfloat16* dst = out + static_cast<size_t>(row) * hidden;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const int c = lane + 32 * i;
+      if (c < n_chunks) {
+        const float4 g0 = *reinterpret_cast<const float4*>(ln_smem + c * 8);
+        const float4 g1 = *reinterpret_cast<const float4*>(ln_smem + c * 8 + 4);
+        float o[8];
+        o[0] = v[i][0] * rstd * g0.x; o[1] = v[i][1] * rstd * g0.y; o[2] = v[i][2] * rstd * g0.z; o[3] = v[i][3] * rstd * g0.w;
+        o[4] = v[i][4] * rstd * g1.x; o[5] = v[i][5] * rstd * g1.y; o[6] = v[i][6] * rstd * g1.z; o[7] = v[i][7] * rstd * g1.w;
+        *reinterpret_cast<uint4*>(dst + c * 8) = pack8(o);
+      }
+    }
+  }
+}
+
+// bf16 rows -> fp32 rows (starts the fp32 residual stream from the embedding gather).
+__global__ void widen_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, size_t n_chunks) {
+  for (size_t c = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; c < n_chunks;
+       c += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float v[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + c * 8), v);
+    *reinterpret_cast<float4*>(out + c * 8) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(out + c * 8 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+}
+
+// Rotary position embedding, in place on the query and key heads of the packed qkv buffer
+// (rotate-half convention: element i pairs with i + d/2; angle = position * theta^(-2i/d)).
+// Positions restart at every sequence. cs holds (cos, sin) per (position, i), fp32.
+__global__ void __launch_bounds__(256)
+rope_kernel(__nv_bfloat16* __restrict__ qkv, const int32_t* __restrict__ cu, int n_seqs, int n_tokens, int n_rot_heads,
+            int row_width, int head_dim, const float2* __restrict__ cs) {
+  const int t = blockIdx.x;
+  if (t >= n_tokens) return;
+  int lo = 0, hi = n_seqs;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(cu + mid) <= t) lo = mid; else hi = mid;
+  }
+  const int pos = t - __ldg(cu + lo);
+  const int half = head_dim >> 1;
+  const int per_head = half >> 3;  // 16-byte groups of 8 pairs
+  const float2* cst = cs + static_cast<size_t>(pos) * half;
+  __nv_bfloat16* row = qkv + static_cast<size_t>(t) * row_width;
+  for (int w = threadIdx.x; w < n_rot_heads * per_head; w += blockDim.x) {
+    const int head = w / per_head, g = w % per_head;
+    __nv_bfloat16* p1 = row + head * head_dim + g * 8;
+    __nv_bfloat16* p2 = p1 + half;
+    float a[8], b[8], o1[8], o2[8];
+    unpack8(*reinterpret_cast<const uint4*>(p1), a);
+    unpack8(*reinterpret_cast<const uint4*>(p2), b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float2 c = __ldg(cst + g * 8 + e);
+      o1[e] = a[e] * c.x - b[e] * c.y;
+      o2[e] = b[e] * c.x + a[e] * c.y;
+    }
+    *reinterpret_cast<uint4*>(p1) = pack8(o1);
+    *reinterpret_cast<uint4*>(p2) = pack8(o2);
+  }
+}
+
 // One CTA per sequence. Threads tile the hidden dimension in 16-byte chunks; when the block
 // has more threads than chunks the spare threads split the rows (mean pooling) and the
 // partial sums meet in shared memory.
@@ -358,6 +461,48 @@ int launch_add_ln(const void* x, const void* y, const float* gamma, const float*
                            gamma, beta, n_rows, hidden, eps, reinterpret_cast<__nv_bfloat16*>(out))));
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "add_ln launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
+int launch_add_rmsnorm(float* h, const void* y, const float* gamma, int n_rows, int hidden, float eps, void* out,
+                       cudaStream_t stream) {
+  if (n_rows <= 0) return B200EMB_OK;
+  int rc = check_hidden(hidden, 16);
+  if (rc) return rc;
+  const int nch = ((hidden >> 3) + 31) / 32;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int full = (n_rows + ROW_WARPS - 1) / ROW_WARPS;
+  const int grid = full < sms * 4 ? full : sms * 4;
+  const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
+  B2_DISPATCH_NCH(nch, (add_rmsnorm_kernel<NCH><<<grid, ROW_WARPS * 32, smem, stream>>>(
+                           h, reinterpret_cast<const __nv_bfloat16*>(y), gamma, n_rows, hidden, eps,
+                           reinterpret_cast<__nv_bfloat16*>(out))));
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "add_rmsnorm launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
+int launch_widen(const void* x, float* out, size_t n_elems, cudaStream_t stream) {
+  if (n_elems == 0) return B200EMB_OK;
+  if (n_elems % 8) return set_error(B200EMB_ERR_INVALID, "widen: element count must be a multiple of 8");
+  const size_t chunks = n_elems / 8;
+  const int grid = static_cast<int>(chunks / 256 + 1 < 148 * 16 ? chunks / 256 + 1 : 148 * 16);
+  widen_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), out, chunks);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "widen launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
+int launch_rope(void* qkv, const int32_t* d_cu, int n_seqs, int n_tokens, int n_rot_heads, int row_width,
+                int head_dim, const float* cos_sin, cudaStream_t stream) {
+  if (n_tokens <= 0) return B200EMB_OK;
+  if (head_dim % 16 != 0) return set_error(B200EMB_ERR_UNSUPPORTED, "rope: head_dim %d not a multiple of 16", head_dim);
+  rope_kernel<<<n_tokens, 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(qkv), d_cu, n_seqs, n_tokens, n_rot_heads,
+                                           row_width, head_dim, reinterpret_cast<const float2*>(cos_sin));
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "rope launch: %s", cudaGetErrorString(e));
   return B200EMB_OK;
 }
 

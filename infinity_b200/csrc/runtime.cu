@@ -3,6 +3,7 @@
 // single-kernel entry points used by the parity tests.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <math.h>
 #include <stdarg.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -103,7 +104,7 @@ static int read_weight_file(const char* path, WeightFile* wf) {
 
 // ---- model --------------------------------------------------------------------------
 struct LayerW {
-  const __nv_bfloat16 *qkv_w, *o_w, *ffn1_w, *ffn2_w;
+  const __nv_bfloat16 *qkv_w, *o_w, *ffn1_w, *ffn2_w;  // decoder: ffn1_w = block-interleaved gate/up [2F, H], ffn2_w = down
   const float *qkv_b, *o_b, *ffn1_b, *ffn2_b;
   const float *ln1_g, *ln1_b, *ln2_g, *ln2_b;
 };
@@ -114,6 +115,7 @@ struct ModelW {
   std::vector<LayerW> layers;
   const __nv_bfloat16 *head_dense_w, *head_out_w;
   const float *head_dense_b, *head_out_b;
+  const float* final_norm_g;  // decoder
 };
 
 struct EventPair {
@@ -133,6 +135,8 @@ struct DeviceCtx {
   AttnTile* d_tiles = nullptr;
   __nv_bfloat16 *x = nullptr, *x2 = nullptr, *qkv = nullptr, *ctx = nullptr, *y = nullptr, *ffn = nullptr;
   __nv_bfloat16 *pooled = nullptr, *head_h = nullptr;
+  float* hres = nullptr;     // decoder: fp32 residual stream [T, H]
+  float* rope_cs = nullptr;  // decoder: (cos, sin) table [max_pos, head_dim / 2]
   float* d_out = nullptr;
   int* d_err = nullptr;
   // pinned host staging
@@ -190,7 +194,8 @@ static int ensure_capacity(b200emb_handle* h, DeviceCtx* c, int n_tokens, int n_
     if (!rc) rc = dev_alloc(&c->d_ids, T);
     if (!rc) rc = dev_alloc(&c->d_types, T);
     if (!rc) rc = dev_alloc(&c->x, T * H);
-    if (!rc) rc = dev_alloc(&c->x2, T * H);
+    if (!rc && d.arch == B200EMB_ARCH_DECODER) rc = dev_alloc(&c->hres, T * H);
+    if (!rc && d.arch != B200EMB_ARCH_DECODER) rc = dev_alloc(&c->x2, T * H);
     if (!rc) rc = dev_alloc(&c->y, T * H);
     if (!rc) rc = dev_alloc(&c->ctx, T * (size_t)d.n_heads * d.head_dim);
     if (!rc) rc = dev_alloc(&c->qkv, T * QKV);
@@ -246,6 +251,32 @@ static int bind_weights(const b200emb_model_desc& d, const WeightFile& wf, Devic
   const uint8_t* b = c->blob;
   ModelW& w = c->w;
   int rc = lookup(wf, b, "emb.word", 1, (uint64_t)d.vocab * H, &w.word);
+  if (d.arch == B200EMB_ARCH_DECODER) {
+    w.pos = nullptr;
+    w.type = nullptr;
+    w.emb_ln_g = w.emb_ln_b = nullptr;
+    w.layers.resize(d.n_layers);
+    char nm[96];
+    for (int l = 0; l < d.n_layers && !rc; ++l) {
+      LayerW& L = w.layers[l];
+      memset(&L, 0, sizeof(L));
+#define B2_LK(field, suffix, dt, n)                         \
+  if (!rc) {                                                \
+    snprintf(nm, sizeof(nm), "layer.%d." suffix, l);        \
+    rc = lookup(wf, b, nm, dt, n, &L.field);                \
+  }
+      B2_LK(ln1_g, "ln1.g", 0, H)
+      B2_LK(qkv_w, "qkv.w", 1, QKV * H)
+      B2_LK(qkv_b, "qkv.b", 0, QKV)
+      B2_LK(o_w, "o.w", 1, H * HQ)
+      B2_LK(ln2_g, "ln2.g", 0, H)
+      B2_LK(ffn1_w, "gu.w", 1, 2 * F * H)
+      B2_LK(ffn2_w, "down.w", 1, H * F)
+#undef B2_LK
+    }
+    if (!rc) rc = lookup(wf, b, "norm.g", 0, H, &w.final_norm_g);
+    return rc;
+  }
   if (!rc) rc = lookup(wf, b, "emb.pos", 1, (uint64_t)d.max_pos * H, &w.pos);
   if (!rc && d.type_vocab > 0) rc = lookup(wf, b, "emb.type", 1, (uint64_t)d.type_vocab * H, &w.type);
   if (d.type_vocab <= 0) w.type = nullptr;
@@ -291,6 +322,7 @@ static void destroy_ctx(DeviceCtx* c) {
   cudaFree(c->d_ids); cudaFree(c->d_types); cudaFree(c->d_cu); cudaFree(c->d_tiles);
   cudaFree(c->x); cudaFree(c->x2); cudaFree(c->qkv); cudaFree(c->ctx); cudaFree(c->y); cudaFree(c->ffn);
   cudaFree(c->pooled); cudaFree(c->head_h); cudaFree(c->d_out); cudaFree(c->d_err);
+  cudaFree(c->hres); cudaFree(c->rope_cs);
   cudaFreeHost(c->h_ids); cudaFreeHost(c->h_types); cudaFreeHost(c->h_cu); cudaFreeHost(c->h_tiles);
   cudaFreeHost(c->h_out); cudaFreeHost(c->h_err);
   for (auto& e : c->ev) if (e) cudaEventDestroy(e);
@@ -301,12 +333,19 @@ static void destroy_ctx(DeviceCtx* c) {
 
 static int validate_desc(const b200emb_model_desc& d) {
   if (d.abi_version != B200EMB_ABI_VERSION) return set_error(B200EMB_ERR_INVALID, "abi_version %d != %d", d.abi_version, B200EMB_ABI_VERSION);
-  if (d.arch != B200EMB_ARCH_BERT && d.arch != B200EMB_ARCH_XLMR)
-    return set_error(B200EMB_ERR_UNSUPPORTED, "arch %d: only the post-LayerNorm encoders (BERT, XLM-R) are built", d.arch);
+  if (d.arch != B200EMB_ARCH_BERT && d.arch != B200EMB_ARCH_XLMR && d.arch != B200EMB_ARCH_DECODER)
+    return set_error(B200EMB_ERR_UNSUPPORTED, "arch %d: the mixture-of-experts encoder is not built", d.arch);
   if (d.weight_format != B200EMB_WFMT_BF16) return set_error(B200EMB_ERR_UNSUPPORTED, "weight_format %d: only bf16 is built", d.weight_format);
   if (d.n_layers <= 0 || d.hidden <= 0 || d.n_heads <= 0 || d.ffn <= 0 || d.vocab <= 0 || d.max_pos <= 0)
     return set_error(B200EMB_ERR_INVALID, "model dimensions must be positive");
-  if (d.n_kv_heads != d.n_heads) return set_error(B200EMB_ERR_UNSUPPORTED, "grouped-query attention needs the decoder arch");
+  if (d.arch == B200EMB_ARCH_DECODER) {
+    if (d.n_kv_heads <= 0 || d.n_heads % d.n_kv_heads != 0) return set_error(B200EMB_ERR_INVALID, "n_heads must be a multiple of n_kv_heads");
+    if (d.ffn % 128 != 0) return set_error(B200EMB_ERR_UNSUPPORTED, "decoder ffn width must be a multiple of 128");
+    if (!(d.rope_theta > 0.f)) return set_error(B200EMB_ERR_INVALID, "decoder needs rope_theta > 0");
+    if (d.head != B200EMB_HEAD_NONE) return set_error(B200EMB_ERR_UNSUPPORTED, "decoder with a classifier head is not built");
+  } else if (d.n_kv_heads != d.n_heads) {
+    return set_error(B200EMB_ERR_UNSUPPORTED, "grouped-query attention needs the decoder arch");
+  }
   if (d.head_dim != 32 && d.head_dim != 64 && d.head_dim != 128) return set_error(B200EMB_ERR_UNSUPPORTED, "head_dim %d not in {32, 64, 128}", d.head_dim);
   if (d.n_heads * d.head_dim != d.hidden) return set_error(B200EMB_ERR_INVALID, "n_heads * head_dim must equal hidden");
   if (d.hidden % 8 || d.ffn % 8) return set_error(B200EMB_ERR_UNSUPPORTED, "hidden and ffn must be multiples of 8");
@@ -354,6 +393,58 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
   const int H = d.hidden, F = d.ffn, T = n_tokens;
   const int QKV = (d.n_heads + 2 * d.n_kv_heads) * d.head_dim;
   int rc;
+  if (d.arch == B200EMB_ARCH_DECODER) {
+    // pre-RMSNorm decoder block (Qwen2): h is the fp32 residual stream
+    {
+      KernelScope ks(c, B200EMB_KCLASS_EMBED);
+      rc = launch_embed_ln(d_ids, nullptr, d_cu, n_seqs, T, w.word, nullptr, nullptr, nullptr, nullptr, H, 0, d.norm_eps,
+                           c->y, c->stream);
+      if (rc) return rc;
+    }
+    {
+      KernelScope ks(c, B200EMB_KCLASS_OTHER);
+      rc = launch_widen(c->y, c->hres, (size_t)T * H, c->stream);
+      if (rc) return rc;
+    }
+    for (int l = 0; l < d.n_layers; ++l) {
+      const LayerW& L = w.layers[l];
+      {
+        KernelScope ks(c, B200EMB_KCLASS_NORM);
+        rc = launch_add_rmsnorm(c->hres, l == 0 ? nullptr : c->y, L.ln1_g, T, H, d.norm_eps, c->x, c->stream);
+        if (rc) return rc;
+      }
+      rc = gemm(c, c->x, L.qkv_w, L.qkv_b, c->qkv, T, QKV, H, EPI_BIAS);
+      if (rc) return rc;
+      {
+        KernelScope ks(c, B200EMB_KCLASS_OTHER);
+        rc = launch_rope(c->qkv, d_cu, n_seqs, T, d.n_heads + d.n_kv_heads, QKV, d.head_dim, c->rope_cs, c->stream);
+        if (rc) return rc;
+      }
+      {
+        KernelScope ks(c, B200EMB_KCLASS_ATTN);
+        rc = launch_attention(c->qkv, c->ctx, c->d_tiles, n_tiles, d.n_heads, d.n_kv_heads, d.head_dim, 1, c->stream);
+        if (rc) return rc;
+      }
+      rc = gemm(c, c->ctx, L.o_w, nullptr, c->y, T, H, d.n_heads * d.head_dim, EPI_BIAS);
+      if (rc) return rc;
+      {
+        KernelScope ks(c, B200EMB_KCLASS_NORM);
+        rc = launch_add_rmsnorm(c->hres, c->y, L.ln2_g, T, H, d.norm_eps, c->x, c->stream);
+        if (rc) return rc;
+      }
+      rc = gemm(c, c->x, L.ffn1_w, nullptr, c->ffn, T, 2 * F, H, EPI_BIAS_SWIGLU);  // silu(gate) * up fused
+      if (rc) return rc;
+      rc = gemm(c, c->ffn, L.ffn2_w, nullptr, c->y, T, H, F, EPI_BIAS);
+      if (rc) return rc;
+    }
+    {
+      KernelScope ks(c, B200EMB_KCLASS_NORM);
+      rc = launch_add_rmsnorm(c->hres, c->y, w.final_norm_g, T, H, d.norm_eps, c->x, c->stream);
+      if (rc) return rc;
+    }
+    KernelScope ks(c, B200EMB_KCLASS_POOL);
+    return launch_pool(c->x, d_cu, n_seqs, H, d.pooling, d.normalize, d_out, out_row_stride, 0, c->stream);
+  }
   {
     KernelScope ks(c, B200EMB_KCLASS_EMBED);
     rc = launch_embed_ln(d_ids, w.type != nullptr ? d_types : nullptr, d_cu, n_seqs, T, w.word, w.pos, w.type,
@@ -468,7 +559,7 @@ static void run_shard(b200emb_handle* h, DeviceCtx* c, const int32_t* ids, const
   c->per_kernel = per_kernel;
   c->kev_used = 0;
   if (n_seqs == 0) return;
-  const int bq = attention_tile_rows(h->desc.head_dim, 0);
+  const int bq = attention_tile_rows(h->desc.head_dim, h->desc.arch == B200EMB_ARCH_DECODER);
   const int n_tiles = attention_build_tiles_q(cu, n_seqs, bq, nullptr);
   int rc = ensure_capacity(h, c, n_tokens, n_seqs, n_tiles);
   if (rc) return fail(rc);
@@ -575,8 +666,9 @@ int b200emb_create(const b200emb_model_desc* desc, const char* weight_path, cons
   {
     const double H = desc->hidden, F = desc->ffn;
     const double QKV = (double)(desc->n_heads + 2 * desc->n_kv_heads) * desc->head_dim;
-    h->cost_a = 2.0 * H * QKV + 2.0 * H * H + 4.0 * H * F;  // GEMM flops per token per layer
-    h->cost_b = 4.0 * H;                                     // attention flops per token pair per layer
+    const bool dec = desc->arch == B200EMB_ARCH_DECODER;
+    h->cost_a = 2.0 * H * QKV + 2.0 * H * H + (dec ? 6.0 : 4.0) * H * F;  // GEMM flops per token per layer
+    h->cost_b = (dec ? 2.0 : 4.0) * H;                                     // attention flops per token pair per layer
   }
   for (int i = 0; i < n_devices && !rc; ++i) {
     DeviceCtx* c = new DeviceCtx();
@@ -609,8 +701,23 @@ int b200emb_create(const b200emb_model_desc* desc, const char* weight_path, cons
     B2_CR(cudaMalloc(reinterpret_cast<void**>(&c->d_err), sizeof(int)));
     B2_CR(cudaMemset(c->d_err, 0, sizeof(int)));
     B2_CR(cudaMallocHost(reinterpret_cast<void**>(&c->h_err), sizeof(int)));
-#undef B2_CR
     if (!rc) rc = bind_weights(*desc, wf, c);
+    if (!rc && desc->arch == B200EMB_ARCH_DECODER) {
+      // (cos, sin) of position * theta^(-2i/d), computed in fp32 the way the torch reference does
+      const int half = desc->head_dim / 2;
+      std::vector<float> cs((size_t)desc->max_pos * half * 2);
+      for (int i = 0; i < half; ++i) {
+        const float inv_freq = 1.0f / powf(desc->rope_theta, (float)(2 * i) / (float)desc->head_dim);
+        for (int p = 0; p < desc->max_pos; ++p) {
+          const float ang = (float)p * inv_freq;
+          cs[((size_t)p * half + i) * 2] = cosf(ang);
+          cs[((size_t)p * half + i) * 2 + 1] = sinf(ang);
+        }
+      }
+      B2_CR(cudaMalloc(reinterpret_cast<void**>(&c->rope_cs), cs.size() * sizeof(float)));
+      B2_CR(cudaMemcpy(c->rope_cs, cs.data(), cs.size() * sizeof(float), cudaMemcpyHostToDevice));
+    }
+#undef B2_CR
     if (!rc) rc = ensure_capacity(h, c, std::max(desc->max_tokens, 1), 256, 1024);
   }
   if (rc) {
@@ -739,7 +846,7 @@ int b200emb_forward_device(b200emb_handle* h, const int32_t* d_input_ids, const 
   c->gemm_flops = 0;
   c->per_kernel = timing != nullptr && timing->per_kernel != 0;
   c->kev_used = 0;
-  const int bq = attention_tile_rows(h->desc.head_dim, 0);
+  const int bq = attention_tile_rows(h->desc.head_dim, h->desc.arch == B200EMB_ARCH_DECODER);
   const int n_tiles = attention_build_tiles_q(h_cu_seqlens, n_seqs, bq, nullptr);
   int rc = ensure_capacity(h, c, n_tokens, n_seqs, n_tiles);
   if (rc) return rc;

@@ -57,6 +57,42 @@ def test_tiny_reranker_matches_oracle(tmp_path):
     model.close()
 
 
+def _oracle_forward(spec, W, batch):
+    if spec.arch == "decoder":
+        from oracle import decoder as dec
+        return dec.forward_batch(spec, W, batch)
+    return enc.forward_batch(spec, W, batch)
+
+
+@pytest.mark.parametrize("kw", [dict(), dict(hidden=512, n_heads=4, n_kv_heads=1, head_dim=128, ffn=1024),
+                                dict(pooling="mean", n_kv_heads=4)])
+def test_tiny_decoder_matches_oracle(tmp_path, kw):
+    """Pre-RMSNorm decoder: RoPE, causal grouped-query attention, fused SwiGLU, fp32 residual stream."""
+    spec = cf.tiny_spec("decoder", **kw)
+    model, W = build_model(tmp_path, spec, 21, perturb=True)
+    batch = cf.random_batch(spec, [1, 2, 9, 64, 65, 127, 128, 300, 33, 77], 5)
+    got = model.forward(batch)
+    ref = _oracle_forward(spec, W, batch)
+    cos = cosines(got, ref)
+    assert cos.min() >= COS_TOL, cos
+    model.close()
+
+
+def test_qwen2_7b_layer_shapes(tmp_path):
+    """Two layers with the exact Qwen2-7B matrix shapes (hidden 3584, 28/4 heads of 128, FFN 18944)
+    and a reduced vocabulary: exercises the real GEMM / attention / SwiGLU tile shapes."""
+    from dataclasses import replace
+    spec = replace(cf.QWEN2_7B, n_layers=2, vocab=4096, name="qwen2-7b-2layer")
+    model, W = build_model(tmp_path, spec, cf.SEEDS["c5"][2], perturb=False)
+    batch = cf.random_batch(spec, [32, 700, 2048, 129, 1024, 63], 6)
+    got = model.forward(batch)
+    ref = _oracle_forward(spec, W, batch)
+    cos = cosines(got, ref)
+    print("qwen2 shape cosine", cos)
+    assert cos.min() >= COS_TOL
+    model.close()
+
+
 def test_order_and_batch_independence(tmp_path):
     """Row i belongs to sequence i whatever the order, and a sequence's embedding does not
     depend on its neighbours in the batch (bit-exact: same kernels, same per-row math)."""

@@ -60,6 +60,26 @@ def test_gemm_bf16(lib, M, N, K, epi):
         assert err <= tol, f"bn={bn}: max abs err {err} > {tol}"
 
 
+@pytest.mark.parametrize("M,F,K", [(300, 128, 256), (1000, 384, 512), (4100, 18944, 3584)])
+def test_gemm_swiglu_epilogue(lib, M, F, K):
+    from infinity_b200.configs import interleave_gate_up
+    g = torch.Generator(device="cuda").manual_seed(M + F)
+    a = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    wg = (torch.randn(F, K, generator=g, device="cuda") / math.sqrt(K)).to(torch.bfloat16)
+    wu = (torch.randn(F, K, generator=g, device="cuda") / math.sqrt(K)).to(torch.bfloat16)
+    w = interleave_gate_up(wg, wu)
+    c = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()
+    _lib.check(lib.b200emb_op_gemm_bf16(a.data_ptr(), w.data_ptr(), None, c.data_ptr(), M, 2 * F, K, _lib.EPI["swiglu"],
+                                        _stream()))
+    rows = slice(0, min(M, 1024))
+    ref = torch.nn.functional.silu(a[rows].float() @ wg.float().t()) * (a[rows].float() @ wu.float().t())
+    err = (c[rows].float() - ref).abs().max().item()
+    assert err <= 2.0 ** -8 * max(1.0, ref.abs().max().item()) + 2e-3, err
+    st = lib.b200emb_op_gemm_bf16(a.data_ptr(), w.data_ptr(), None, c.data_ptr(), M, 2 * F - 8, K, _lib.EPI["swiglu"], _stream())
+    assert st == -1
+
+
 def test_gemm_no_bias_and_identity(lib):
     # W = I picks out A exactly: checks the K-slice / swizzle addressing bit for bit.
     K = N = 256

@@ -129,3 +129,42 @@ def test_reranker_matches_transformers_xlmr():
     # and the ragged driver returns rows in batch order whatever the internal sort
     out = enc.forward_batch(spec, W, cf.pack(seqs), batch_size=2)
     assert np.abs(out - ref).max() < 2e-5
+
+
+def test_decoder_matches_transformers_qwen2():
+    """The decoder restatement against ``transformers.Qwen2Model`` with identical weights."""
+    from transformers import Qwen2Config, Qwen2Model
+    from oracle import decoder as dec
+    spec = cf.tiny_spec("decoder", hidden=64, n_heads=4, n_kv_heads=2, head_dim=16, ffn=128, vocab=300, max_pos=64)
+    W = cf.oracle_tensors(spec, cf.init_weights(spec, 8, perturb=True))
+    cfg = Qwen2Config(vocab_size=spec.vocab, hidden_size=spec.hidden, intermediate_size=spec.ffn,
+                      num_hidden_layers=spec.n_layers, num_attention_heads=spec.n_heads,
+                      num_key_value_heads=spec.n_kv_heads, max_position_embeddings=spec.max_pos,
+                      rms_norm_eps=spec.norm_eps, rope_theta=spec.rope_theta, attention_dropout=0.0,
+                      use_sliding_window=False, tie_word_embeddings=False)
+    cfg._attn_implementation = "eager"
+    model = Qwen2Model(cfg).eval()
+    nh, nkv, d = spec.n_heads, spec.n_kv_heads, spec.head_dim
+    sd = {"embed_tokens.weight": W["emb.word"], "norm.weight": W["norm.g"]}
+    for l in range(spec.n_layers):
+        p, q = f"layer.{l}.", f"layers.{l}."
+        wq, wk, wv = W[p + "qkv.w"].split([nh * d, nkv * d, nkv * d], 0)
+        bq, bk, bv = W[p + "qkv.b"].split([nh * d, nkv * d, nkv * d], 0)
+        sd.update({q + "self_attn.q_proj.weight": wq, q + "self_attn.q_proj.bias": bq,
+                   q + "self_attn.k_proj.weight": wk, q + "self_attn.k_proj.bias": bk,
+                   q + "self_attn.v_proj.weight": wv, q + "self_attn.v_proj.bias": bv,
+                   q + "self_attn.o_proj.weight": W[p + "o.w"],
+                   q + "mlp.gate_proj.weight": W[p + "gate.w"], q + "mlp.up_proj.weight": W[p + "up.w"],
+                   q + "mlp.down_proj.weight": W[p + "down.w"],
+                   q + "input_layernorm.weight": W[p + "ln1.g"], q + "post_attention_layernorm.weight": W[p + "ln2.g"]})
+    missing, unexpected = model.load_state_dict(sd, strict=False)
+    assert not unexpected and not [m for m in missing if "rotary" not in m], (missing, unexpected)
+    rope = getattr(cfg, "rope_parameters", None) or {}
+    assert float(rope.get("rope_theta", getattr(cfg, "rope_theta", 0))) == spec.rope_theta
+    batch = cf.random_batch(spec, [3, 17, 64, 40], 9)
+    ids, mask, _ = enc.pad_batch(batch.sequences())
+    with torch.no_grad():
+        ref = model(input_ids=ids, attention_mask=mask).last_hidden_state
+    got = dec.decoder_hidden(spec, W, ids, mask)
+    m = mask.bool()
+    assert (got[m] - ref[m]).abs().max().item() < 5e-5
