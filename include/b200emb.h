@@ -195,6 +195,22 @@ int b200emb_op_attention(const void* qkv, void* out, const int32_t* d_cu_seqlens
                          int32_t n_seqs, int32_t n_tokens, int32_t n_heads, int32_t n_kv_heads,
                          int32_t head_dim, int32_t causal, void* stream);
 
+/* Weight quantisers (the reference's hook for them is quant_interface,
+ * infinity_emb/transformer/quantization/interface.py:28-70; it has int8 / fp8 only).
+ * w_bf16 [rows, cols] row-major, blocks along cols (K):
+ *   B200EMB_WFMT_NVFP4: q_out = rows*cols/2 bytes (two e2m1 per byte, even element in the low
+ *     nibble), scales_out = rows*cols/16 e4m3 bytes, *tensor_scale_out (device fp32) = gs with
+ *     gs = 2688 / amax(tensor); block scale = e4m3(amax(block) / 6 * gs); x^ = q * scale / gs.
+ *   B200EMB_WFMT_MXFP8: q_out = rows*cols e4m3 bytes, scales_out = rows*cols/32 e8m0 bytes
+ *     (biased exponent e + 127, e = floor(log2(amax(block))) - 8); x^ = q * 2^e.
+ * Round to nearest even, saturating. Synchronises the stream. */
+int b200emb_op_quantize(const void* w_bf16, int64_t rows, int64_t cols, int32_t format, void* q_out,
+                        void* scales_out, float* tensor_scale_out, void* stream);
+/* Inverse: bf16 [rows, cols]; for NVFP4 the result is q * block scale, WITHOUT the 1 / gs factor
+ * (exact in bf16; the GEMM applies 1 / gs to its accumulator). Asynchronous on the stream. */
+int b200emb_op_dequantize(const void* q, const void* scales, int64_t rows, int64_t cols, int32_t format,
+                          void* out_bf16, void* stream);
+
 /* The same attention for callers that must not allocate device memory. No counterpart in the
  * reference: it exists for processes whose framework pool already holds nearly all GPU memory
  * (so a cudaMalloc inside a library call may fail) and for latency-critical threads that

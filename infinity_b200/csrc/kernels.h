@@ -58,6 +58,15 @@ int launch_attention_tc(const void* qkv, void* out, const AttnTile* d_tiles, int
                         int n_kv_heads, int head_dim, int sm_count, int* err_flag, cudaStream_t stream);
 int attention_tc_init_device();
 
+// ---- block-format weight quantisers (quant.cu) ----
+// w bf16 [rows, cols] -> q (packed elements), scales (one byte per block, row-major [rows, cols / block]);
+// NVFP4 also writes the tensor scale gs to d_gs and needs a 4-byte device scratch word.
+int launch_quantize(const void* w, int64_t rows, int64_t cols, int fmt, void* q, void* scales, float* d_gs,
+                    unsigned int* d_amax_scratch, cudaStream_t stream);
+// q, scales -> bf16 [rows, cols]; for NVFP4 the result is q * block_scale (the consumer multiplies by 1 / gs)
+int launch_dequantize(const void* q, const void* scales, int64_t rows, int64_t cols, int fmt, void* out,
+                      cudaStream_t stream);
+
 // ---- row kernels (rowops.cu) ----
 int launch_embed_ln(const int32_t* ids, const int32_t* types, const int32_t* d_cu, int n_seqs, int n_tokens,
                     const void* word, const void* pos, const void* type_table, const float* gamma, const float* beta,

@@ -1,0 +1,259 @@
+// Weight quantisers and dequantisers for the two block formats (memory-bound kernels).
+//
+//   NVFP4  elements e2m1 (two per byte, element 2j in the low nibble), 16-element blocks along
+//          K, one e4m3 scale per block, one fp32 scale per tensor:
+//            gs      = 2688 / amax(tensor)                 (2688 = 448 * 6; gs = 1 if amax == 0)
+//            s_q     = e4m3_rn(min(amax(block) / 6 * gs, 448))
+//            q       = e2m1_rn_even_satfinite(x / (float(s_q) / gs))      (0 if s_q == 0)
+//            x^      = q * float(s_q) / gs
+//   MXFP8  elements e4m3, 32-element blocks along K, one e8m0 (power-of-two) scale per block:
+//            e       = clamp(floor(log2(amax(block))) - 8, -127, 127)   (-127 if amax == 0)
+//            q       = e4m3_rn_even_satfinite(x * 2^-e),   x^ = q * 2^e,   scale byte = e + 127
+// Scales are stored row-major [rows, K / block]. The numpy statement of the same rules lives
+// in the test oracle; the two must agree bit for bit.
+#include <cuda_bf16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "kernels.h"
+
+namespace b2 {
+
+__device__ __forceinline__ void unpack8q(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(p[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+// amax over the whole tensor: bit pattern of |x| as an unsigned (monotone for non-negative floats)
+__global__ void amax_kernel(const __nv_bfloat16* __restrict__ w, size_t n_chunks, unsigned int* __restrict__ out) {
+  float m = 0.f;
+  for (size_t c = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; c < n_chunks;
+       c += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float v[8];
+    unpack8q(__ldg(reinterpret_cast<const uint4*>(w + c * 8)), v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(v[e]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(out, __float_as_uint(m));
+}
+
+__global__ void nvfp4_global_scale_kernel(const unsigned int* __restrict__ amax_bits, float* __restrict__ gs) {
+  const float amax = __uint_as_float(*amax_bits);
+  *gs = amax > 0.f ? 2688.0f / amax : 1.0f;
+}
+
+// one thread per 16-element block
+__global__ void __launch_bounds__(256)
+quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ w, size_t n_blocks, const float* __restrict__ gs_ptr,
+                   uint8_t* __restrict__ q, uint8_t* __restrict__ scales) {
+  const size_t b = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (b >= n_blocks) return;
+  const float gs = *gs_ptr;
+  float v[16];
+  unpack8q(__ldg(reinterpret_cast<const uint4*>(w + b * 16)), reinterpret_cast<float(&)[8]>(v[0]));
+  unpack8q(__ldg(reinterpret_cast<const uint4*>(w + b * 16 + 8)), reinterpret_cast<float(&)[8]>(v[8]));
+  float amax = 0.f;
+#pragma unroll
+  for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(v[e]));
+  const float s_enc = fminf(__fmul_rn(__fdiv_rn(amax, 6.0f), gs), 448.0f);
+  const __nv_fp8_storage_t s_q = __nv_cvt_float_to_fp8(s_enc, __NV_SATFINITE, __NV_E4M3);
+  const float s_f = __half2float(__half(__nv_cvt_fp8_to_halfraw(s_q, __NV_E4M3)));
+  const float s_dec = __fdiv_rn(s_f, gs);
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int e = 0; e < 16; e += 2) {
+    float2 p = make_float2(0.f, 0.f);
+    if (s_dec > 0.f) p = make_float2(__fdiv_rn(v[e], s_dec), __fdiv_rn(v[e + 1], s_dec));
+    const uint32_t byte = __nv_cvt_float2_to_fp4x2(p, __NV_E2M1, cudaRoundNearest) & 0xffu;
+    if (e < 8) lo |= byte << (4 * e); else hi |= byte << (4 * (e - 8));
+  }
+  *reinterpret_cast<uint2*>(q + b * 8) = make_uint2(lo, hi);
+  scales[b] = s_q;
+}
+
+// one thread per 32-element block
+__global__ void __launch_bounds__(256)
+quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ w, size_t n_blocks, uint8_t* __restrict__ q,
+                   uint8_t* __restrict__ scales) {
+  const size_t b = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (b >= n_blocks) return;
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    unpack8q(__ldg(reinterpret_cast<const uint4*>(w + b * 32 + i * 8)), reinterpret_cast<float(&)[8]>(v[i * 8]));
+  float amax = 0.f;
+#pragma unroll
+  for (int e = 0; e < 32; ++e) amax = fmaxf(amax, fabsf(v[e]));
+  int ex = -127;
+  if (amax > 0.f) {
+    ex = ilogbf(amax) - 8;
+    ex = ex < -127 ? -127 : (ex > 127 ? 127 : ex);
+  }
+  const float inv = ex == -127 ? 0.f : exp2f(static_cast<float>(-ex));  // amax == 0 (or far below range): all zeros
+  uint32_t out[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int j = 0; j < 4; j += 2) {
+      const float2 p = make_float2(v[i * 4 + j] * inv, v[i * 4 + j + 1] * inv);
+      const uint32_t two = __nv_cvt_float2_to_fp8x2(p, __NV_SATFINITE, __NV_E4M3);
+      word |= (two & 0xffffu) << (8 * j);
+    }
+    out[i] = word;
+  }
+  uint4* dst = reinterpret_cast<uint4*>(q + b * 32);
+  dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
+  dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
+  scales[b] = static_cast<uint8_t>(ex + 127);
+}
+
+__device__ __forceinline__ float e2m1_value(uint32_t nib) {
+  const float mag[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  const float m = mag[nib & 7];
+  return (nib & 8) ? -m : m;
+}
+
+// q * float(s_q) in bf16 (exact: at most 5 significant bits); the tensor scale 1/gs is applied by the consumer
+__global__ void __launch_bounds__(256)
+dequant_nvfp4_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ scales, size_t n_blocks,
+                     __nv_bfloat16* __restrict__ out) {
+  const size_t b = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (b >= n_blocks) return;
+  const uint2 packed = __ldg(reinterpret_cast<const uint2*>(q + b * 8));
+  const float s = __half2float(__half(__nv_cvt_fp8_to_halfraw(scales[b], __NV_E4M3)));
+  __nv_bfloat162 o[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const uint32_t word = e < 4 ? packed.x : packed.y;
+    const uint32_t byte = (word >> (8 * (e & 3))) & 0xffu;
+    o[e] = __floats2bfloat162_rn(e2m1_value(byte & 15) * s, e2m1_value(byte >> 4) * s);
+  }
+  uint4* dst = reinterpret_cast<uint4*>(out + b * 16);
+  dst[0] = *reinterpret_cast<uint4*>(&o[0]);
+  dst[1] = *reinterpret_cast<uint4*>(&o[4]);
+}
+
+__global__ void __launch_bounds__(256)
+dequant_mxfp8_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ scales, size_t n_blocks,
+                     __nv_bfloat16* __restrict__ out) {
+  const size_t b = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (b >= n_blocks) return;
+  const float s = exp2f(static_cast<float>(static_cast<int>(scales[b]) - 127));
+  const uint4* src = reinterpret_cast<const uint4*>(q + b * 32);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint4 u = __ldg(src + h);
+    const uint32_t words[4] = {u.x, u.y, u.z, u.w};
+    __nv_bfloat162 o[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>((words[i] >> (16 * j)) & 0xffffu), __NV_E4M3);
+        const float2 f = __half22float2(__half2(hr));
+        o[i * 2 + j] = __floats2bfloat162_rn(f.x * s, f.y * s);
+      }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + b * 32 + h * 16);
+    dst[0] = *reinterpret_cast<uint4*>(&o[0]);
+    dst[1] = *reinterpret_cast<uint4*>(&o[4]);
+  }
+}
+
+static int check_shape(int64_t rows, int64_t cols, int block) {
+  if (rows <= 0 || cols <= 0 || cols % block != 0)
+    return set_error(B200EMB_ERR_INVALID, "quantise: K = %lld must be a positive multiple of the block size %d",
+                     (long long)cols, block);
+  return B200EMB_OK;
+}
+
+int launch_quantize(const void* w, int64_t rows, int64_t cols, int fmt, void* q, void* scales, float* d_gs,
+                    unsigned int* d_amax_scratch, cudaStream_t stream) {
+  const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(w);
+  if (fmt == B200EMB_WFMT_NVFP4) {
+    int rc = check_shape(rows, cols, 16);
+    if (rc) return rc;
+    if (d_gs == nullptr || d_amax_scratch == nullptr) return set_error(B200EMB_ERR_INVALID, "nvfp4 needs a tensor-scale output");
+    const size_t n = static_cast<size_t>(rows) * cols;
+    B2_CUDA_CHECK(cudaMemsetAsync(d_amax_scratch, 0, sizeof(unsigned int), stream));
+    const size_t chunks = n / 8;
+    const int grid = static_cast<int>(chunks / 256 + 1 < 148 * 8 ? chunks / 256 + 1 : 148 * 8);
+    amax_kernel<<<grid, 256, 0, stream>>>(wp, chunks, d_amax_scratch);
+    nvfp4_global_scale_kernel<<<1, 1, 0, stream>>>(d_amax_scratch, d_gs);
+    const size_t blocks = n / 16;
+    quant_nvfp4_kernel<<<static_cast<unsigned int>((blocks + 255) / 256), 256, 0, stream>>>(
+        wp, blocks, d_gs, reinterpret_cast<uint8_t*>(q), reinterpret_cast<uint8_t*>(scales));
+  } else if (fmt == B200EMB_WFMT_MXFP8) {
+    int rc = check_shape(rows, cols, 32);
+    if (rc) return rc;
+    const size_t blocks = static_cast<size_t>(rows) * cols / 32;
+    quant_mxfp8_kernel<<<static_cast<unsigned int>((blocks + 255) / 256), 256, 0, stream>>>(
+        wp, blocks, reinterpret_cast<uint8_t*>(q), reinterpret_cast<uint8_t*>(scales));
+  } else {
+    return set_error(B200EMB_ERR_INVALID, "quantise: unknown format %d", fmt);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "quantise launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
+int launch_dequantize(const void* q, const void* scales, int64_t rows, int64_t cols, int fmt, void* out,
+                      cudaStream_t stream) {
+  if (fmt == B200EMB_WFMT_NVFP4) {
+    int rc = check_shape(rows, cols, 16);
+    if (rc) return rc;
+    const size_t blocks = static_cast<size_t>(rows) * cols / 16;
+    dequant_nvfp4_kernel<<<static_cast<unsigned int>((blocks + 255) / 256), 256, 0, stream>>>(
+        reinterpret_cast<const uint8_t*>(q), reinterpret_cast<const uint8_t*>(scales), blocks,
+        reinterpret_cast<__nv_bfloat16*>(out));
+  } else if (fmt == B200EMB_WFMT_MXFP8) {
+    int rc = check_shape(rows, cols, 32);
+    if (rc) return rc;
+    const size_t blocks = static_cast<size_t>(rows) * cols / 32;
+    dequant_mxfp8_kernel<<<static_cast<unsigned int>((blocks + 255) / 256), 256, 0, stream>>>(
+        reinterpret_cast<const uint8_t*>(q), reinterpret_cast<const uint8_t*>(scales), blocks,
+        reinterpret_cast<__nv_bfloat16*>(out));
+  } else {
+    return set_error(B200EMB_ERR_INVALID, "dequantise: unknown format %d", fmt);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "dequantise launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
+}  // namespace b2
+
+using namespace b2;
+
+extern "C" int b200emb_op_quantize(const void* w_bf16, int64_t rows, int64_t cols, int32_t format, void* q_out,
+                                   void* scales_out, float* tensor_scale_out, void* stream) {
+  if (w_bf16 == nullptr || q_out == nullptr || scales_out == nullptr)
+    return set_error(B200EMB_ERR_INVALID, "quantise: null pointer");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  unsigned int* scratch = nullptr;
+  if (format == B200EMB_WFMT_NVFP4) B2_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&scratch), sizeof(unsigned int)));
+  int rc = launch_quantize(w_bf16, rows, cols, format, q_out, scales_out, tensor_scale_out, scratch, s);
+  cudaError_t e = cudaStreamSynchronize(s);
+  if (scratch) cudaFree(scratch);
+  if (rc) return rc;
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "quantise: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
+extern "C" int b200emb_op_dequantize(const void* q, const void* scales, int64_t rows, int64_t cols, int32_t format,
+                                     void* out_bf16, void* stream) {
+  if (q == nullptr || scales == nullptr || out_bf16 == nullptr)
+    return set_error(B200EMB_ERR_INVALID, "dequantise: null pointer");
+  return launch_dequantize(q, scales, rows, cols, format, out_bf16, reinterpret_cast<cudaStream_t>(stream));
+}
