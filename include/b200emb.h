@@ -136,6 +136,13 @@ int b200emb_create(const b200emb_model_desc* desc, const char* weight_path, cons
                    int32_t n_devices, b200emb_handle** out);
 int b200emb_destroy(b200emb_handle* h);
 
+/* Offline weight quantisation: reads a bf16 weight file, replaces every layer matrix
+ * ("layer.<l>.<...>.w"; only the expert matrices when the model has experts) by name.q / name.s
+ * (/ name.gs) in the given block format using the quantiser kernels on device_id, and writes
+ * out_path. Load the result with weight_format set to the same format. The reference's
+ * counterpart is the load-time hook quant_interface (quantization/interface.py:28-70). */
+int b200emb_quantize_weights(const char* in_path, const char* out_path, int32_t format, int32_t device_id);
+
 /* ---- the hot path -----------------------------------------------------------
  * Replaces encode_core (+ the pooling / normalise part of encode_post):
  *   sentence_transformer.py:117-133 + :142-145, crossencoder/torch.py:100-108,

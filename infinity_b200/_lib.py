@@ -54,6 +54,7 @@ _I32P = C.POINTER(C.c_int32)
 SIGNATURES = {
     "b200emb_create": (C.c_int, [C.POINTER(ModelDesc), C.c_char_p, _I32P, C.c_int32, C.POINTER(_P)]),
     "b200emb_destroy": (C.c_int, [_P]),
+    "b200emb_quantize_weights": (C.c_int, [C.c_char_p, C.c_char_p, C.c_int32, C.c_int32]),
     "b200emb_forward": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_int32, _P, C.c_int64, C.POINTER(Timing)]),
     "b200emb_forward_device": (C.c_int, [_P, _P, _P, _P, _P, C.c_int32, C.c_int32, _P, C.c_int64, C.POINTER(Timing)]),
     "b200emb_partition": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_double, C.c_double, _P]),

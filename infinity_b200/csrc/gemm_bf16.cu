@@ -58,8 +58,8 @@ __device__ __forceinline__ float apply_epilogue(float v) {
 template <int BN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                         const __grid_constant__ CUtensorMap tmap_c, const float* __restrict__ bias, int M, int N, int K,
-                         int* __restrict__ err_flag) {
+                         const __grid_constant__ CUtensorMap tmap_c, const float* __restrict__ bias, float alpha, int M, int N,
+                         int K, int* __restrict__ err_flag) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -246,9 +246,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
               uint32_t w[4];
 #pragma unroll
               for (int e = 0; e < 8; e += 2) {
-                const float a0 = silu_f(__uint_as_float(g[c * 8 + e]) + bg[c * 8 + e]) * (__uint_as_float(u[c * 8 + e]) + bu[c * 8 + e]);
-                const float a1 = silu_f(__uint_as_float(g[c * 8 + e + 1]) + bg[c * 8 + e + 1]) *
-                                 (__uint_as_float(u[c * 8 + e + 1]) + bu[c * 8 + e + 1]);
+                const float a0 = silu_f(fmaf(__uint_as_float(g[c * 8 + e]), alpha, bg[c * 8 + e])) *
+                                 fmaf(__uint_as_float(u[c * 8 + e]), alpha, bu[c * 8 + e]);
+                const float a1 = silu_f(fmaf(__uint_as_float(g[c * 8 + e + 1]), alpha, bg[c * 8 + e + 1])) *
+                                 fmaf(__uint_as_float(u[c * 8 + e + 1]), alpha, bu[c * 8 + e + 1]);
                 __nv_bfloat162 pr = __floats2bfloat162_rn(a0, a1);
                 w[e >> 1] = *reinterpret_cast<uint32_t*>(&pr);
               }
@@ -293,8 +294,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(c < 4 ? r0[c * 8 + e] : r1[(c - 4) * 8 + e]);
             const float4 b0 = *reinterpret_cast<const float4*>(bsub + c * 8);
             const float4 b1 = *reinterpret_cast<const float4*>(bsub + c * 8 + 4);
-            v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-            v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+            v[0] = fmaf(v[0], alpha, b0.x); v[1] = fmaf(v[1], alpha, b0.y);
+            v[2] = fmaf(v[2], alpha, b0.z); v[3] = fmaf(v[3], alpha, b0.w);
+            v[4] = fmaf(v[4], alpha, b1.x); v[5] = fmaf(v[5], alpha, b1.y);
+            v[6] = fmaf(v[6], alpha, b1.z); v[7] = fmaf(v[7], alpha, b1.w);
             uint4 packed;
             __nv_bfloat162 p0 = __floats2bfloat162_rn(apply_epilogue<EPI>(v[0]), apply_epilogue<EPI>(v[1]));
             __nv_bfloat162 p1 = __floats2bfloat162_rn(apply_epilogue<EPI>(v[2]), apply_epilogue<EPI>(v[3]));
@@ -365,14 +368,14 @@ int make_tmap_bf16_2d(CUtensorMap_st* out, const void* base, uint64_t rows, uint
 }
 
 template <int BN, int EPI>
-static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, const float* bias, int M,
-                      int N, int K, int sm_count, int* err_flag, cudaStream_t stream) {
+static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, const float* bias, float alpha,
+                      int M, int N, int K, int sm_count, int* err_flag, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_bf16_tcgen05_kernel<BN, EPI>;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
   const int tiles = m_tiles * n_tiles;
   const int grid = tiles < sm_count ? tiles : sm_count;
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tw, tc, bias, M, N, K, err_flag);
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tw, tc, bias, alpha, M, N, K, err_flag);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "gemm launch: %s", cudaGetErrorString(e));
   return B200EMB_OK;
@@ -380,13 +383,13 @@ static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tw, const CUtens
 
 template <int BN>
 static int launch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, const float* bias,
-                      int M, int N, int K, int sm_count, int* err_flag, cudaStream_t stream) {
+                      float alpha, int M, int N, int K, int sm_count, int* err_flag, cudaStream_t stream) {
   switch (epi) {
-    case EPI_BIAS: return launch_cfg<BN, EPI_BIAS>(ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);
-    case EPI_BIAS_GELU: return launch_cfg<BN, EPI_BIAS_GELU>(ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);
-    case EPI_BIAS_TANH: return launch_cfg<BN, EPI_BIAS_TANH>(ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);
+    case EPI_BIAS: return launch_cfg<BN, EPI_BIAS>(ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
+    case EPI_BIAS_GELU: return launch_cfg<BN, EPI_BIAS_GELU>(ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
+    case EPI_BIAS_TANH: return launch_cfg<BN, EPI_BIAS_TANH>(ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
     case EPI_BIAS_SWIGLU:
-      if constexpr (BN == 256) return launch_cfg<BN, EPI_BIAS_SWIGLU>(ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);
+      if constexpr (BN == 256) return launch_cfg<BN, EPI_BIAS_SWIGLU>(ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
       break;
   }
   return set_error(B200EMB_ERR_INVALID, "unknown epilogue %d", epi);
@@ -424,7 +427,7 @@ int gemm_pick_bn(int M, int N, int sm_count) {
 }
 
 int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int epi,
-                     int sm_count, int* err_flag, cudaStream_t stream, int force_bn) {
+                     int sm_count, int* err_flag, cudaStream_t stream, int force_bn, float alpha) {
   if (M <= 0) return B200EMB_OK;
   if (N <= 0 || K <= 0 || (K % 8) != 0 || (N % 8) != 0)
     return set_error(B200EMB_ERR_INVALID, "gemm: need N, K > 0 and multiples of 8 (N=%d K=%d)", N, K);
@@ -447,9 +450,9 @@ int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, i
   rc = make_tmap_bf16_2d(&tc, C, (uint64_t)M, (uint64_t)n_out, BM);
   if (rc) return rc;
   switch (bn) {
-    case 256: return launch_epi<256>(epi, ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);
-    case 128: return launch_epi<128>(epi, ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);
-    case 64: return launch_epi<64>(epi, ta, tw, tc, bias, M, N, K, sm_count, err_flag, stream);
+    case 256: return launch_epi<256>(epi, ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
+    case 128: return launch_epi<128>(epi, ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
+    case 64: return launch_epi<64>(epi, ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
   }
   return set_error(B200EMB_ERR_INVALID, "gemm: unsupported tile width %d", bn);
 }

@@ -31,8 +31,9 @@ int kernels_init_device();
 // ---- GEMM (gemm_bf16.cu) ----
 // err_flag: device int the kernel sets non-zero when a bounded wait gave up.
 // force_bn: 0 = choose the tile width from the problem size, else 64 / 128 / 256.
+// alpha scales the accumulator before the bias (1 / tensor scale of NVFP4 weights; 1 otherwise).
 int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int epi,
-                     int sm_count, int* err_flag, cudaStream_t stream, int force_bn);
+                     int sm_count, int* err_flag, cudaStream_t stream, int force_bn, float alpha = 1.0f);
 int gemm_init_device();
 // TMA descriptor of a bf16 row-major [rows, cols] matrix: box [box_rows x 64 columns], 128-byte swizzle.
 int make_tmap_bf16_2d(::CUtensorMap_st* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);

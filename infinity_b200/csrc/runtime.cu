@@ -103,8 +103,18 @@ static int read_weight_file(const char* path, WeightFile* wf) {
 }
 
 // ---- model --------------------------------------------------------------------------
+// One GEMM weight: bf16 as stored, or a block-quantised tensor that is expanded into the
+// per-device scratch right before its GEMM (alpha = 1 / tensor scale for NVFP4).
+struct Mat {
+  const __nv_bfloat16* w = nullptr;
+  const uint8_t* q = nullptr;
+  const uint8_t* s = nullptr;
+  float alpha = 1.0f;
+  int64_t rows = 0, cols = 0;
+};
+
 struct LayerW {
-  const __nv_bfloat16 *qkv_w, *o_w, *ffn1_w, *ffn2_w;  // decoder: ffn1_w = block-interleaved gate/up [2F, H], ffn2_w = down
+  Mat qkv_w, o_w, ffn1_w, ffn2_w;  // decoder: ffn1_w = block-interleaved gate/up [2F, H], ffn2_w = down
   const float *qkv_b, *o_b, *ffn1_b, *ffn2_b;
   const float *ln1_g, *ln1_b, *ln2_g, *ln2_b;
 };
@@ -135,6 +145,8 @@ struct DeviceCtx {
   AttnTile* d_tiles = nullptr;
   __nv_bfloat16 *x = nullptr, *x2 = nullptr, *qkv = nullptr, *ctx = nullptr, *y = nullptr, *ffn = nullptr;
   __nv_bfloat16 *pooled = nullptr, *head_h = nullptr;
+  __nv_bfloat16* wscratch = nullptr;  // expanded copy of the quantised matrix in use
+  size_t wscratch_elems = 0;
   float* hres = nullptr;     // decoder: fp32 residual stream [T, H]
   float* rope_cs = nullptr;  // decoder: (cos, sin) table [max_pos, head_dim / 2]
   float* d_out = nullptr;
@@ -245,6 +257,36 @@ static int lookup(const WeightFile& wf, const uint8_t* blob, const char* name, u
   return B200EMB_OK;
 }
 
+// A GEMM weight by name: the bf16 tensor, or (block formats) name.q / name.s / name.gs.
+static int lookup_mat(const b200emb_model_desc& d, const WeightFile& wf, DeviceCtx* c, const char* name, uint64_t rows,
+                      uint64_t cols, Mat* m) {
+  m->rows = (int64_t)rows;
+  m->cols = (int64_t)cols;
+  char nm[112];
+  snprintf(nm, sizeof(nm), "%s.q", name);
+  if (d.weight_format == B200EMB_WFMT_BF16 || wf.index.find(nm) == wf.index.end())
+    return lookup(wf, c->blob, name, 1, rows * cols, &m->w);
+  const bool fp4 = d.weight_format == B200EMB_WFMT_NVFP4;
+  const uint64_t block = fp4 ? 16 : 32;
+  if (cols % block) return set_error(B200EMB_ERR_IO, "tensor %s: K = %llu not a multiple of %llu", name, (unsigned long long)cols, (unsigned long long)block);
+  int rc = lookup(wf, c->blob, nm, 2, fp4 ? rows * cols / 2 : rows * cols, &m->q);
+  snprintf(nm, sizeof(nm), "%s.s", name);
+  if (!rc) rc = lookup(wf, c->blob, nm, 2, rows * cols / block, &m->s);
+  if (!rc && fp4) {
+    snprintf(nm, sizeof(nm), "%s.gs", name);
+    auto it = wf.index.find(nm);
+    if (it == wf.index.end()) return set_error(B200EMB_ERR_IO, "weight file lacks tensor %s", nm);
+    const TensorEntry& e = wf.entries[it->second];
+    if (e.dtype != 0 || e.nbytes < 4) return set_error(B200EMB_ERR_IO, "tensor %s must be one fp32", nm);
+    float gs = 1.f;
+    memcpy(&gs, wf.data.data() + e.offset, 4);
+    if (!(gs > 0.f)) return set_error(B200EMB_ERR_IO, "tensor %s: tensor scale must be positive", nm);
+    m->alpha = 1.0f / gs;
+  }
+  if (!rc) c->wscratch_elems = std::max(c->wscratch_elems, (size_t)(rows * cols));
+  return rc;
+}
+
 static int bind_weights(const b200emb_model_desc& d, const WeightFile& wf, DeviceCtx* c) {
   const uint64_t H = d.hidden, F = d.ffn, QKV = (uint64_t)(d.n_heads + 2 * d.n_kv_heads) * d.head_dim;
   const uint64_t HQ = (uint64_t)d.n_heads * d.head_dim;
@@ -259,19 +301,25 @@ static int bind_weights(const b200emb_model_desc& d, const WeightFile& wf, Devic
     char nm[96];
     for (int l = 0; l < d.n_layers && !rc; ++l) {
       LayerW& L = w.layers[l];
-      memset(&L, 0, sizeof(L));
+      L = LayerW();
 #define B2_LK(field, suffix, dt, n)                         \
   if (!rc) {                                                \
     snprintf(nm, sizeof(nm), "layer.%d." suffix, l);        \
     rc = lookup(wf, b, nm, dt, n, &L.field);                \
   }
+#define B2_LM(field, suffix, r, k)                          \
+  if (!rc) {                                                \
+    snprintf(nm, sizeof(nm), "layer.%d." suffix, l);        \
+    rc = lookup_mat(d, wf, c, nm, r, k, &L.field);          \
+  }
       B2_LK(ln1_g, "ln1.g", 0, H)
-      B2_LK(qkv_w, "qkv.w", 1, QKV * H)
+      B2_LM(qkv_w, "qkv.w", QKV, H)
       B2_LK(qkv_b, "qkv.b", 0, QKV)
-      B2_LK(o_w, "o.w", 1, H * HQ)
+      B2_LM(o_w, "o.w", H, HQ)
       B2_LK(ln2_g, "ln2.g", 0, H)
-      B2_LK(ffn1_w, "gu.w", 1, 2 * F * H)
-      B2_LK(ffn2_w, "down.w", 1, H * F)
+      B2_LM(ffn1_w, "gu.w", 2 * F, H)
+      B2_LM(ffn2_w, "down.w", H, F)
+#undef B2_LM
 #undef B2_LK
     }
     if (!rc) rc = lookup(wf, b, "norm.g", 0, H, &w.final_norm_g);
@@ -291,16 +339,22 @@ static int bind_weights(const b200emb_model_desc& d, const WeightFile& wf, Devic
     snprintf(nm, sizeof(nm), "layer.%d." suffix, l);        \
     rc = lookup(wf, b, nm, dt, n, &L.field);                \
   }
-    B2_LK(qkv_w, "qkv.w", 1, QKV * H)
+#define B2_LM(field, suffix, r, k)                          \
+  if (!rc) {                                                \
+    snprintf(nm, sizeof(nm), "layer.%d." suffix, l);        \
+    rc = lookup_mat(d, wf, c, nm, r, k, &L.field);          \
+  }
+    B2_LM(qkv_w, "qkv.w", QKV, H)
     B2_LK(qkv_b, "qkv.b", 0, QKV)
-    B2_LK(o_w, "o.w", 1, H * HQ)
+    B2_LM(o_w, "o.w", H, HQ)
     B2_LK(o_b, "o.b", 0, H)
     B2_LK(ln1_g, "ln1.g", 0, H)
     B2_LK(ln1_b, "ln1.b", 0, H)
-    B2_LK(ffn1_w, "ffn1.w", 1, F * H)
+    B2_LM(ffn1_w, "ffn1.w", F, H)
     B2_LK(ffn1_b, "ffn1.b", 0, F)
-    B2_LK(ffn2_w, "ffn2.w", 1, H * F)
+    B2_LM(ffn2_w, "ffn2.w", H, F)
     B2_LK(ffn2_b, "ffn2.b", 0, H)
+#undef B2_LM
     B2_LK(ln2_g, "ln2.g", 0, H)
     B2_LK(ln2_b, "ln2.b", 0, H)
 #undef B2_LK
@@ -322,7 +376,7 @@ static void destroy_ctx(DeviceCtx* c) {
   cudaFree(c->d_ids); cudaFree(c->d_types); cudaFree(c->d_cu); cudaFree(c->d_tiles);
   cudaFree(c->x); cudaFree(c->x2); cudaFree(c->qkv); cudaFree(c->ctx); cudaFree(c->y); cudaFree(c->ffn);
   cudaFree(c->pooled); cudaFree(c->head_h); cudaFree(c->d_out); cudaFree(c->d_err);
-  cudaFree(c->hres); cudaFree(c->rope_cs);
+  cudaFree(c->hres); cudaFree(c->rope_cs); cudaFree(c->wscratch);
   cudaFreeHost(c->h_ids); cudaFreeHost(c->h_types); cudaFreeHost(c->h_cu); cudaFreeHost(c->h_tiles);
   cudaFreeHost(c->h_out); cudaFreeHost(c->h_err);
   for (auto& e : c->ev) if (e) cudaEventDestroy(e);
@@ -335,7 +389,8 @@ static int validate_desc(const b200emb_model_desc& d) {
   if (d.abi_version != B200EMB_ABI_VERSION) return set_error(B200EMB_ERR_INVALID, "abi_version %d != %d", d.abi_version, B200EMB_ABI_VERSION);
   if (d.arch != B200EMB_ARCH_BERT && d.arch != B200EMB_ARCH_XLMR && d.arch != B200EMB_ARCH_DECODER)
     return set_error(B200EMB_ERR_UNSUPPORTED, "arch %d: the mixture-of-experts encoder is not built", d.arch);
-  if (d.weight_format != B200EMB_WFMT_BF16) return set_error(B200EMB_ERR_UNSUPPORTED, "weight_format %d: only bf16 is built", d.weight_format);
+  if (d.weight_format < B200EMB_WFMT_BF16 || d.weight_format > B200EMB_WFMT_NVFP4)
+    return set_error(B200EMB_ERR_INVALID, "unknown weight_format %d", d.weight_format);
   if (d.n_layers <= 0 || d.hidden <= 0 || d.n_heads <= 0 || d.ffn <= 0 || d.vocab <= 0 || d.max_pos <= 0)
     return set_error(B200EMB_ERR_INVALID, "model dimensions must be positive");
   if (d.arch == B200EMB_ARCH_DECODER) {
@@ -384,6 +439,21 @@ static int gemm(DeviceCtx* c, const void* A, const void* W, const float* bias, v
   return launch_gemm_bf16(A, W, bias, C, M, N, K, epi, c->sm_count, c->d_err, c->stream, 0);
 }
 
+// GEMM against a model weight; a block-quantised weight is expanded into the scratch first.
+static int gemm(DeviceCtx* c, int wfmt, const void* A, const Mat& W, const float* bias, void* C, int M, int N, int K,
+                int epi) {
+  const void* w = W.w;
+  if (W.q != nullptr) {
+    KernelScope ks(c, B200EMB_KCLASS_OTHER);
+    int rc = launch_dequantize(W.q, W.s, W.rows, W.cols, wfmt, c->wscratch, c->stream);
+    if (rc) return rc;
+    w = c->wscratch;
+  }
+  KernelScope ks(c, B200EMB_KCLASS_GEMM);
+  c->gemm_flops += 2.0 * M * N * K;
+  return launch_gemm_bf16(A, w, bias, C, M, N, K, epi, c->sm_count, c->d_err, c->stream, 0, W.alpha);
+}
+
 // Enqueues every kernel of one forward on c->stream. Inputs are on the device.
 static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids, const int32_t* d_types,
                            const int32_t* d_cu, int n_seqs, int n_tokens, int n_tiles, float* d_out,
@@ -413,7 +483,7 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
         rc = launch_add_rmsnorm(c->hres, l == 0 ? nullptr : c->y, L.ln1_g, T, H, d.norm_eps, c->x, c->stream);
         if (rc) return rc;
       }
-      rc = gemm(c, c->x, L.qkv_w, L.qkv_b, c->qkv, T, QKV, H, EPI_BIAS);
+      rc = gemm(c, d.weight_format, c->x, L.qkv_w, L.qkv_b, c->qkv, T, QKV, H, EPI_BIAS);
       if (rc) return rc;
       {
         KernelScope ks(c, B200EMB_KCLASS_OTHER);
@@ -425,16 +495,16 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
         rc = launch_attention(c->qkv, c->ctx, c->d_tiles, n_tiles, d.n_heads, d.n_kv_heads, d.head_dim, 1, c->stream);
         if (rc) return rc;
       }
-      rc = gemm(c, c->ctx, L.o_w, nullptr, c->y, T, H, d.n_heads * d.head_dim, EPI_BIAS);
+      rc = gemm(c, d.weight_format, c->ctx, L.o_w, nullptr, c->y, T, H, d.n_heads * d.head_dim, EPI_BIAS);
       if (rc) return rc;
       {
         KernelScope ks(c, B200EMB_KCLASS_NORM);
         rc = launch_add_rmsnorm(c->hres, c->y, L.ln2_g, T, H, d.norm_eps, c->x, c->stream);
         if (rc) return rc;
       }
-      rc = gemm(c, c->x, L.ffn1_w, nullptr, c->ffn, T, 2 * F, H, EPI_BIAS_SWIGLU);  // silu(gate) * up fused
+      rc = gemm(c, d.weight_format, c->x, L.ffn1_w, nullptr, c->ffn, T, 2 * F, H, EPI_BIAS_SWIGLU);  // silu(gate) * up fused
       if (rc) return rc;
-      rc = gemm(c, c->ffn, L.ffn2_w, nullptr, c->y, T, H, F, EPI_BIAS);
+      rc = gemm(c, d.weight_format, c->ffn, L.ffn2_w, nullptr, c->y, T, H, F, EPI_BIAS);
       if (rc) return rc;
     }
     {
@@ -453,7 +523,7 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
   }
   for (int l = 0; l < d.n_layers; ++l) {
     const LayerW& L = w.layers[l];
-    rc = gemm(c, c->x, L.qkv_w, L.qkv_b, c->qkv, T, QKV, H, EPI_BIAS);
+    rc = gemm(c, d.weight_format, c->x, L.qkv_w, L.qkv_b, c->qkv, T, QKV, H, EPI_BIAS);
     if (rc) return rc;
     {
       KernelScope ks(c, B200EMB_KCLASS_ATTN);
@@ -464,16 +534,16 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
         rc = launch_attention(c->qkv, c->ctx, c->d_tiles, n_tiles, d.n_heads, d.n_kv_heads, d.head_dim, 0, c->stream);
       if (rc) return rc;
     }
-    rc = gemm(c, c->ctx, L.o_w, L.o_b, c->y, T, H, d.n_heads * d.head_dim, EPI_BIAS);
+    rc = gemm(c, d.weight_format, c->ctx, L.o_w, L.o_b, c->y, T, H, d.n_heads * d.head_dim, EPI_BIAS);
     if (rc) return rc;
     {
       KernelScope ks(c, B200EMB_KCLASS_NORM);
       rc = launch_add_ln(c->x, c->y, L.ln1_g, L.ln1_b, T, H, d.norm_eps, c->x2, c->stream);
       if (rc) return rc;
     }
-    rc = gemm(c, c->x2, L.ffn1_w, L.ffn1_b, c->ffn, T, F, H, EPI_BIAS_GELU);
+    rc = gemm(c, d.weight_format, c->x2, L.ffn1_w, L.ffn1_b, c->ffn, T, F, H, EPI_BIAS_GELU);
     if (rc) return rc;
-    rc = gemm(c, c->ffn, L.ffn2_w, L.ffn2_b, c->y, T, H, F, EPI_BIAS);
+    rc = gemm(c, d.weight_format, c->ffn, L.ffn2_w, L.ffn2_b, c->y, T, H, F, EPI_BIAS);
     if (rc) return rc;
     {
       KernelScope ks(c, B200EMB_KCLASS_NORM);
@@ -702,6 +772,9 @@ int b200emb_create(const b200emb_model_desc* desc, const char* weight_path, cons
     B2_CR(cudaMemset(c->d_err, 0, sizeof(int)));
     B2_CR(cudaMallocHost(reinterpret_cast<void**>(&c->h_err), sizeof(int)));
     if (!rc) rc = bind_weights(*desc, wf, c);
+    if (!rc && c->wscratch_elems > 0) {
+      B2_CR(cudaMalloc(reinterpret_cast<void**>(&c->wscratch), c->wscratch_elems * sizeof(__nv_bfloat16)));
+    }
     if (!rc && desc->arch == B200EMB_ARCH_DECODER) {
       // (cos, sin) of position * theta^(-2i/d), computed in fp32 the way the torch reference does
       const int half = desc->head_dim / 2;
@@ -727,6 +800,113 @@ int b200emb_create(const b200emb_model_desc* desc, const char* weight_path, cons
     return rc;
   }
   *out = h;
+  return B200EMB_OK;
+}
+
+// Reads a bf16 weight file, replaces every layer matrix ("layer.*.w", or only the expert
+// matrices when the file has any) by its block-quantised form and writes a new file:
+// name.q (packed elements), name.s (block scales), name.gs (NVFP4 tensor scale).
+int b200emb_quantize_weights(const char* in_path, const char* out_path, int32_t format, int32_t device_id) {
+  if (in_path == nullptr || out_path == nullptr) return set_error(B200EMB_ERR_INVALID, "quantize_weights: null path");
+  if (format != B200EMB_WFMT_NVFP4 && format != B200EMB_WFMT_MXFP8)
+    return set_error(B200EMB_ERR_INVALID, "quantize_weights: format must be MXFP8 or NVFP4");
+  WeightFile wf;
+  int rc = read_weight_file(in_path, &wf);
+  if (rc) return rc;
+  B2_CUDA_CHECK(cudaSetDevice(device_id));
+  const uint64_t block = format == B200EMB_WFMT_NVFP4 ? 16 : 32;
+  bool has_experts = false;
+  for (const TensorEntry& e : wf.entries)
+    if (strstr(e.name, ".expert.") != nullptr) has_experts = true;
+  struct OutTensor {
+    TensorEntry e;
+    std::vector<uint8_t> data;
+  };
+  std::vector<OutTensor> outs;
+  auto add = [&](const char* name, uint32_t dtype, uint32_t ndim, uint64_t d0, uint64_t d1, std::vector<uint8_t>&& data) {
+    OutTensor t;
+    memset(&t.e, 0, sizeof(t.e));
+    snprintf(t.e.name, sizeof(t.e.name), "%.63s", name);
+    t.e.dtype = dtype;
+    t.e.ndim = ndim;
+    t.e.dims[0] = d0; t.e.dims[1] = d1; t.e.dims[2] = 1; t.e.dims[3] = 1;
+    t.e.nbytes = data.size();
+    t.data = std::move(data);
+    outs.push_back(std::move(t));
+  };
+  unsigned int* d_amax = nullptr;
+  float* d_gs = nullptr;
+  B2_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&d_amax), sizeof(unsigned int)));
+  B2_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&d_gs), sizeof(float)));
+  for (const TensorEntry& e : wf.entries) {
+    const size_t len = strlen(e.name);
+    const bool is_layer_mat = e.dtype == 1 && e.ndim == 2 && strncmp(e.name, "layer.", 6) == 0 && len > 2 &&
+                              strcmp(e.name + len - 2, ".w") == 0 && e.dims[1] % block == 0 && len < 60;
+    const bool selected = is_layer_mat && (!has_experts || strstr(e.name, ".expert.") != nullptr);
+    if (!selected) {
+      std::vector<uint8_t> copy(wf.data.begin() + e.offset, wf.data.begin() + e.offset + e.nbytes);
+      OutTensor t;
+      t.e = e;
+      t.data = std::move(copy);
+      outs.push_back(std::move(t));
+      continue;
+    }
+    const uint64_t rows = e.dims[0], cols = e.dims[1];
+    const size_t q_bytes = format == B200EMB_WFMT_NVFP4 ? rows * cols / 2 : rows * cols;
+    const size_t s_bytes = rows * cols / block;
+    void *d_w = nullptr, *d_q = nullptr, *d_s = nullptr;
+    cudaError_t ce = cudaMalloc(&d_w, e.nbytes);
+    if (ce == cudaSuccess) ce = cudaMalloc(&d_q, q_bytes);
+    if (ce == cudaSuccess) ce = cudaMalloc(&d_s, s_bytes);
+    if (ce == cudaSuccess) ce = cudaMemcpy(d_w, wf.data.data() + e.offset, e.nbytes, cudaMemcpyHostToDevice);
+    if (ce == cudaSuccess) {
+      rc = launch_quantize(d_w, (int64_t)rows, (int64_t)cols, format, d_q, d_s, d_gs, d_amax, nullptr);
+      if (!rc) ce = cudaDeviceSynchronize();
+    }
+    std::vector<uint8_t> q(q_bytes), sc(s_bytes), gs(4);
+    if (ce == cudaSuccess && !rc) ce = cudaMemcpy(q.data(), d_q, q_bytes, cudaMemcpyDeviceToHost);
+    if (ce == cudaSuccess && !rc) ce = cudaMemcpy(sc.data(), d_s, s_bytes, cudaMemcpyDeviceToHost);
+    if (ce == cudaSuccess && !rc && format == B200EMB_WFMT_NVFP4) ce = cudaMemcpy(gs.data(), d_gs, 4, cudaMemcpyDeviceToHost);
+    cudaFree(d_w); cudaFree(d_q); cudaFree(d_s);
+    if (ce != cudaSuccess && !rc) rc = set_error(B200EMB_ERR_CUDA, "quantize_weights(%s): %s", e.name, cudaGetErrorString(ce));
+    if (rc) break;
+    char nm[64];
+    snprintf(nm, sizeof(nm), "%.59s.q", e.name);
+    add(nm, 2, 2, rows, q_bytes / rows, std::move(q));
+    snprintf(nm, sizeof(nm), "%.59s.s", e.name);
+    add(nm, 2, 2, rows, cols / block, std::move(sc));
+    if (format == B200EMB_WFMT_NVFP4) {
+      snprintf(nm, sizeof(nm), "%.59s.gs", e.name);
+      add(nm, 0, 1, 1, 1, std::move(gs));
+    }
+  }
+  cudaFree(d_amax);
+  cudaFree(d_gs);
+  if (rc) return rc;
+  // write
+  const uint64_t header = 8 + 4 + 4 + 8 + sizeof(TensorEntry) * outs.size();
+  const uint64_t data_offset = (header + 255) / 256 * 256;
+  uint64_t off = 0;
+  for (OutTensor& t : outs) {
+    t.e.offset = off;
+    off = (off + t.e.nbytes + 255) / 256 * 256;
+  }
+  FILE* f = fopen(out_path, "wb");
+  if (f == nullptr) return set_error(B200EMB_ERR_IO, "cannot write %s", out_path);
+  const uint32_t n = (uint32_t)outs.size(), zero = 0;
+  bool ok = fwrite("B2EW0001", 1, 8, f) == 8 && fwrite(&n, 4, 1, f) == 1 && fwrite(&zero, 4, 1, f) == 1 &&
+            fwrite(&data_offset, 8, 1, f) == 1;
+  for (const OutTensor& t : outs) ok = ok && fwrite(&t.e, sizeof(TensorEntry), 1, f) == 1;
+  std::vector<uint8_t> pad(256, 0);
+  ok = ok && fwrite(pad.data(), 1, data_offset - header, f) == data_offset - header;
+  uint64_t pos = 0;
+  for (const OutTensor& t : outs) {
+    if (t.e.offset > pos) ok = ok && fwrite(pad.data(), 1, t.e.offset - pos, f) == t.e.offset - pos;
+    ok = ok && (t.data.empty() || fwrite(t.data.data(), 1, t.data.size(), f) == t.data.size());
+    pos = t.e.offset + t.data.size();
+  }
+  ok = (fclose(f) == 0) && ok;
+  if (!ok) return set_error(B200EMB_ERR_IO, "short write to %s", out_path);
   return B200EMB_OK;
 }
 

