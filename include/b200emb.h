@@ -218,6 +218,14 @@ int b200emb_op_quantize(const void* w_bf16, int64_t rows, int64_t cols, int32_t 
 int b200emb_op_dequantize(const void* q, const void* scales, int64_t rows, int64_t cols, int32_t format,
                           void* out_bf16, void* stream);
 
+/* Mixture-of-experts router: fp32 logits x[t,:] (bf16) . router_w[e,:] (fp32) + router_b[e]
+ * (nullable), softmax over the n_experts (<= 16) experts, top_k (<= 4) experts per token with
+ * ties going to the lower expert index; topk_weight = softmax probability of the chosen expert
+ * (not renormalised). counts (nullable, [n_experts]) receives tokens per expert. Asynchronous. */
+int b200emb_op_moe_router(const void* x, const float* router_w, const float* router_b, int32_t n_tokens,
+                          int32_t hidden, int32_t n_experts, int32_t top_k, int32_t* topk_idx, float* topk_weight,
+                          int32_t* counts, void* stream);
+
 /* The same attention for callers that must not allocate device memory. No counterpart in the
  * reference: it exists for processes whose framework pool already holds nearly all GPU memory
  * (so a cudaMalloc inside a library call may fail) and for latency-critical threads that

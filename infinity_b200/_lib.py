@@ -65,6 +65,7 @@ SIGNATURES = {
     "b200emb_op_attention_static": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P]),
     "b200emb_op_quantize": (C.c_int, [_P, C.c_int64, C.c_int64, C.c_int32, _P, _P, _P, _P]),
     "b200emb_op_dequantize": (C.c_int, [_P, _P, C.c_int64, C.c_int64, C.c_int32, _P, _P]),
+    "b200emb_op_moe_router": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P]),
     "b200emb_op_embed_ln": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, C.c_int32, C.c_int32, C.c_float, _P, _P]),
     "b200emb_op_add_ln": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_int32, C.c_float, _P, _P]),
     "b200emb_op_pool": (C.c_int, [_P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, C.c_int64, C.c_int32, _P]),

@@ -57,12 +57,21 @@ XLMR_LARGE_RERANK = ModelSpec(name="xlmr-large-reranker-shape", arch="xlmr", n_l
                               pos_offset=2, norm_eps=1e-5, pooling="cls", normalize=False, head="classifier",
                               n_labels=1)
 
+MOE_ENCODER = ModelSpec(name="moe-encoder-shape", arch="moe", n_layers=12, hidden=768, n_heads=12, n_kv_heads=12,
+                        head_dim=64, ffn=3072, vocab=250048, max_pos=512, type_vocab=1, pooling="mean",
+                        n_experts=8, top_k=2, moe_every=2, weight_format="mxfp8")
 QWEN2_7B = ModelSpec(name="qwen2-7b-shape", arch="decoder", n_layers=28, hidden=3584, n_heads=28, n_kv_heads=4,
                      head_dim=128, ffn=18944, vocab=151646, max_pos=2048, type_vocab=0, norm_eps=1e-6,
                      rope_theta=1e6, pooling="last", max_len=2048)
 
-SPECS: Dict[str, ModelSpec] = {"c1": BGE_SMALL, "c2": BERT_LARGE, "c3": XLMR_LARGE_RERANK, "c5": QWEN2_7B}
-SEEDS = {"c1": (1001, 2001, 3001), "c2": (1002, 2002, 3002), "c3": (1003, 2003, 3003), "c5": (1005, 2005, 3005)}
+SPECS: Dict[str, ModelSpec] = {"c1": BGE_SMALL, "c2": BERT_LARGE, "c3": XLMR_LARGE_RERANK, "c4": MOE_ENCODER,
+                               "c5": QWEN2_7B}
+SEEDS = {"c1": (1001, 2001, 3001), "c2": (1002, 2002, 3002), "c3": (1003, 2003, 3003), "c4": (1004, 2004, 3004),
+         "c5": (1005, 2005, 3005)}
+
+
+def is_moe_layer(spec: "ModelSpec", l: int) -> bool:
+    return spec.arch == "moe" and spec.moe_every > 0 and l % spec.moe_every == spec.moe_every - 1
 
 
 def tiny_spec(arch: str = "bert", **kw) -> ModelSpec:
@@ -72,6 +81,9 @@ def tiny_spec(arch: str = "bert", **kw) -> ModelSpec:
     if arch == "xlmr":
         base.update(type_vocab=1, pos_offset=2, norm_eps=1e-5, pooling="cls", normalize=False, head="classifier",
                     n_labels=1)
+    if arch == "moe":
+        base.update(hidden=128, n_heads=2, n_kv_heads=2, head_dim=64, ffn=256, type_vocab=1, n_experts=8, top_k=2,
+                    moe_every=2, n_layers=4)
     if arch == "decoder":
         base.update(hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=384, type_vocab=0, norm_eps=1e-6,
                     rope_theta=1e6, pooling="last", max_pos=320, max_len=320)
@@ -123,8 +135,15 @@ def init_weights(spec: ModelSpec, seed: int, perturb: bool = False) -> Dict[str,
         w[p + "qkv.w"], w[p + "qkv.b"] = mat(QKV, H), bias(QKV)
         w[p + "o.w"], w[p + "o.b"] = mat(H, spec.n_heads * spec.head_dim), bias(H)
         w[p + "ln1.g"], w[p + "ln1.b"] = gain(H), bias(H)
-        w[p + "ffn1.w"], w[p + "ffn1.b"] = mat(F, H), bias(F)
-        w[p + "ffn2.w"], w[p + "ffn2.b"] = mat(H, F), bias(H)
+        if is_moe_layer(spec, l):
+            # router in fp32; the experts' matrices stacked along the rows: expert e owns rows [e*F, (e+1)*F)
+            E = spec.n_experts
+            w[p + "router.w"], w[p + "router.b"] = mat(E, H), bias(E)
+            w[p + "experts.ffn1.w"], w[p + "experts.ffn1.b"] = mat(E * F, H), bias(E * F)
+            w[p + "experts.ffn2.w"], w[p + "experts.ffn2.b"] = mat(E * H, F), bias(E * H)
+        else:
+            w[p + "ffn1.w"], w[p + "ffn1.b"] = mat(F, H), bias(F)
+            w[p + "ffn2.w"], w[p + "ffn2.b"] = mat(H, F), bias(H)
         w[p + "ln2.g"], w[p + "ln2.b"] = gain(H), bias(H)
     if spec.head == "classifier":
         w["head.dense.w"], w["head.dense.b"] = mat(H, H), bias(H)
@@ -133,6 +152,9 @@ def init_weights(spec: ModelSpec, seed: int, perturb: bool = False) -> Dict[str,
 
 
 def is_matrix(name: str) -> bool:
+    """Stored in bf16 by the runtime (the router stays fp32)."""
+    if name.endswith("router.w"):
+        return False
     return name.endswith(".w") or name in ("emb.word", "emb.pos", "emb.type")
 
 
@@ -227,6 +249,10 @@ def synth_batch(cfg: str, n_seqs: Optional[int] = None, seed_offset: int = 0) ->
             s[0] = 101  # CLS
             seqs.append(s)
         return pack(seqs)
+    if cfg == "c4":
+        n = n_seqs if n_seqs is not None else 8192
+        lens = np.random.default_rng(len_seed).integers(16, 513, size=n)
+        return pack([rng.integers(1000, 250048, size=int(L)) for L in lens])
     if cfg == "c5":
         n = n_seqs if n_seqs is not None else 512
         lens = np.random.default_rng(len_seed).integers(32, 2049, size=n)

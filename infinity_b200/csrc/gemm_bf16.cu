@@ -59,7 +59,7 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                          const __grid_constant__ CUtensorMap tmap_c, const float* __restrict__ bias, float alpha, int M, int N,
-                         int K, int* __restrict__ err_flag) {
+                         int K, const int32_t* __restrict__ tile_expert, int* __restrict__ err_flag) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -115,6 +115,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile / n_tiles) * BM;
         const int n0 = (tile % n_tiles) * BN;
+        // grouped mode: row block m0/BM belongs to expert e (its weights are rows [e*N, e*N + N) of W);
+        // e < 0 marks an unused row block, skipped by every role alike
+        const int expert = tile_expert != nullptr ? __ldg(tile_expert + tile / n_tiles) : 0;
+        if (expert < 0) continue;
+        const int w_row0 = expert * N + n0;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u)) {
             ok = false;
@@ -124,7 +129,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           uint8_t* b_dst = a_dst + Cfg::A_BYTES;
           mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
           tma_load_2d(a_dst, &tmap_a, &full_bar[stage], kb * BK, m0);
-          tma_load_2d(b_dst, &tmap_w, &full_bar[stage], kb * BK, n0);
+          tma_load_2d(b_dst, &tmap_w, &full_bar[stage], kb * BK, w_row0);
           ++issued;
           if (++stage == STAGES) {
             stage = 0;
@@ -151,9 +156,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       uint32_t phase = 0;
       bool ok = true;
       int local_tile = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
-        const int acc = local_tile & 1;
-        const uint32_t acc_phase = (local_tile >> 1) & 1u;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        if (tile_expert != nullptr && __ldg(tile_expert + tile / n_tiles) < 0) continue;
+        const int lt = local_tile++;
+        const int acc = lt & 1;
+        const uint32_t acc_phase = (lt >> 1) & 1u;
         if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1u)) {
           ok = false;
           break;
@@ -202,13 +209,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const bool store_thread = (ew & 3) == 0 && lane == 0;
     bool ok = true;
     int local_tile = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local_tile) {
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const int expert = tile_expert != nullptr ? __ldg(tile_expert + tile / n_tiles) : 0;
+      if (expert < 0) continue;
+      const int lt = local_tile++;
       const int m0 = (tile / n_tiles) * BM;
       const int n0 = (tile % n_tiles) * BN;
-      const int acc = local_tile & 1;
-      const uint32_t acc_phase = (local_tile >> 1) & 1u;
+      const int acc = lt & 1;
+      const uint32_t acc_phase = (lt >> 1) & 1u;
       named_barrier_sync(1, 32 * N_EPI_WARPS);  // everyone is done with the previous tile's bias
-      if (et < BN) bias_s[et] = (bias != nullptr && n0 + et < N) ? __ldg(bias + n0 + et) : 0.f;
+      if (et < BN) bias_s[et] = (bias != nullptr && n0 + et < N) ? __ldg(bias + expert * N + n0 + et) : 0.f;
       const bool ok_local = mbar_wait(&acc_full_bar[acc], acc_phase);
       // one decision for all epilogue threads (also publishes the bias): leave together or not at all
       ok = named_barrier_and(1, 32 * N_EPI_WARPS, ok_local);
@@ -369,13 +379,13 @@ int make_tmap_bf16_2d(CUtensorMap_st* out, const void* base, uint64_t rows, uint
 
 template <int BN, int EPI>
 static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, const float* bias, float alpha,
-                      int M, int N, int K, int sm_count, int* err_flag, cudaStream_t stream) {
+                      int M, int N, int K, const int32_t* tile_expert, int sm_count, int* err_flag, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_bf16_tcgen05_kernel<BN, EPI>;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
   const int tiles = m_tiles * n_tiles;
   const int grid = tiles < sm_count ? tiles : sm_count;
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tw, tc, bias, alpha, M, N, K, err_flag);
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tw, tc, bias, alpha, M, N, K, tile_expert, err_flag);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "gemm launch: %s", cudaGetErrorString(e));
   return B200EMB_OK;
@@ -383,13 +393,14 @@ static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tw, const CUtens
 
 template <int BN>
 static int launch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, const float* bias,
-                      float alpha, int M, int N, int K, int sm_count, int* err_flag, cudaStream_t stream) {
+                      float alpha, int M, int N, int K, const int32_t* tile_expert, int sm_count, int* err_flag,
+                      cudaStream_t stream) {
   switch (epi) {
-    case EPI_BIAS: return launch_cfg<BN, EPI_BIAS>(ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
-    case EPI_BIAS_GELU: return launch_cfg<BN, EPI_BIAS_GELU>(ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
-    case EPI_BIAS_TANH: return launch_cfg<BN, EPI_BIAS_TANH>(ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
+    case EPI_BIAS: return launch_cfg<BN, EPI_BIAS>(ta, tw, tc, bias, alpha, M, N, K, tile_expert, sm_count, err_flag, stream);
+    case EPI_BIAS_GELU: return launch_cfg<BN, EPI_BIAS_GELU>(ta, tw, tc, bias, alpha, M, N, K, tile_expert, sm_count, err_flag, stream);
+    case EPI_BIAS_TANH: return launch_cfg<BN, EPI_BIAS_TANH>(ta, tw, tc, bias, alpha, M, N, K, tile_expert, sm_count, err_flag, stream);
     case EPI_BIAS_SWIGLU:
-      if constexpr (BN == 256) return launch_cfg<BN, EPI_BIAS_SWIGLU>(ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
+      if constexpr (BN == 256) return launch_cfg<BN, EPI_BIAS_SWIGLU>(ta, tw, tc, bias, alpha, M, N, K, tile_expert, sm_count, err_flag, stream);
       break;
   }
   return set_error(B200EMB_ERR_INVALID, "unknown epilogue %d", epi);
@@ -427,7 +438,8 @@ int gemm_pick_bn(int M, int N, int sm_count) {
 }
 
 int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int epi,
-                     int sm_count, int* err_flag, cudaStream_t stream, int force_bn, float alpha) {
+                     int sm_count, int* err_flag, cudaStream_t stream, int force_bn, float alpha,
+                     const int32_t* tile_expert, int n_experts) {
   if (M <= 0) return B200EMB_OK;
   if (N <= 0 || K <= 0 || (K % 8) != 0 || (N % 8) != 0)
     return set_error(B200EMB_ERR_INVALID, "gemm: need N, K > 0 and multiples of 8 (N=%d K=%d)", N, K);
@@ -445,14 +457,16 @@ int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, i
   CUtensorMap ta, tw, tc;
   int rc = make_tmap_bf16_2d(&ta, A, (uint64_t)M, (uint64_t)K, BM);
   if (rc) return rc;
-  rc = make_tmap_bf16_2d(&tw, W, (uint64_t)N, (uint64_t)K, (uint32_t)bn);
+  if (tile_expert != nullptr && (N % bn) != 0)
+    return set_error(B200EMB_ERR_INVALID, "grouped gemm: N = %d must be a multiple of the tile width %d", N, bn);
+  rc = make_tmap_bf16_2d(&tw, W, (uint64_t)N * (tile_expert != nullptr ? n_experts : 1), (uint64_t)K, (uint32_t)bn);
   if (rc) return rc;
   rc = make_tmap_bf16_2d(&tc, C, (uint64_t)M, (uint64_t)n_out, BM);
   if (rc) return rc;
   switch (bn) {
-    case 256: return launch_epi<256>(epi, ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
-    case 128: return launch_epi<128>(epi, ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
-    case 64: return launch_epi<64>(epi, ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
+    case 256: return launch_epi<256>(epi, ta, tw, tc, bias, alpha, M, N, K, tile_expert, sm_count, err_flag, stream);
+    case 128: return launch_epi<128>(epi, ta, tw, tc, bias, alpha, M, N, K, tile_expert, sm_count, err_flag, stream);
+    case 64: return launch_epi<64>(epi, ta, tw, tc, bias, alpha, M, N, K, tile_expert, sm_count, err_flag, stream);
   }
   return set_error(B200EMB_ERR_INVALID, "gemm: unsupported tile width %d", bn);
 }

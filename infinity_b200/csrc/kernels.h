@@ -32,8 +32,12 @@ int kernels_init_device();
 // err_flag: device int the kernel sets non-zero when a bounded wait gave up.
 // force_bn: 0 = choose the tile width from the problem size, else 64 / 128 / 256.
 // alpha scales the accumulator before the bias (1 / tensor scale of NVFP4 weights; 1 otherwise).
+// Grouped mode (tile_expert != null): A is [M, K] with rows grouped by expert in 128-row blocks,
+// tile_expert[m / 128] = expert of that row block (< 0: unused block, skipped), W is the stack
+// [n_experts * N, K], bias [n_experts * N]; one launch covers every expert.
 int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int epi,
-                     int sm_count, int* err_flag, cudaStream_t stream, int force_bn, float alpha = 1.0f);
+                     int sm_count, int* err_flag, cudaStream_t stream, int force_bn, float alpha = 1.0f,
+                     const int32_t* tile_expert = nullptr, int n_experts = 1);
 int gemm_init_device();
 // TMA descriptor of a bf16 row-major [rows, cols] matrix: box [box_rows x 64 columns], 128-byte swizzle.
 int make_tmap_bf16_2d(::CUtensorMap_st* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
@@ -67,6 +71,18 @@ int launch_quantize(const void* w, int64_t rows, int64_t cols, int fmt, void* q,
 // q, scales -> bf16 [rows, cols]; for NVFP4 the result is q * block_scale (the consumer multiplies by 1 / gs)
 int launch_dequantize(const void* q, const void* scales, int64_t rows, int64_t cols, int fmt, void* out,
                       cudaStream_t stream);
+
+// ---- mixture of experts (moe.cu) ----
+int launch_moe_router(const void* x, const float* wr, const float* br, int n_tokens, int hidden, int n_experts,
+                      int top_k, int32_t* topk_idx, float* topk_w, int32_t* counts, cudaStream_t stream);
+// upper bound of 128-row blocks of the expert-contiguous layout (segments padded to 128 rows)
+int moe_max_row_blocks(int n_tokens, int top_k, int n_experts);
+int launch_moe_scatter(const void* x, const int32_t* topk_idx, const int32_t* counts, int n_tokens, int top_k,
+                       int hidden, int n_experts, int32_t* cursor, int32_t* tile_expert, int32_t* row_of, void* xperm,
+                       cudaStream_t stream);
+int launch_moe_combine_ln(const void* x, const void* yperm, const int32_t* row_of, const float* topk_w, int top_k,
+                          const float* gamma, const float* beta, int n_tokens, int hidden, float eps, void* out,
+                          cudaStream_t stream);
 
 // ---- row kernels (rowops.cu) ----
 int launch_embed_ln(const int32_t* ids, const int32_t* types, const int32_t* d_cu, int n_seqs, int n_tokens,

@@ -1,0 +1,304 @@
+// Mixture-of-experts feed-forward around the grouped GEMM (memory-bound kernels):
+//   router      fp32 logits x W_r^T + b_r, softmax over the experts, top-k (ties -> lower expert
+//               index), gate weights = the softmax probabilities of the chosen experts (not
+//               renormalised); also counts tokens per expert
+//   offsets     exclusive scan of the counts rounded up to 128 rows per expert (so a GEMM row
+//               block never straddles two experts) and the row-block -> expert table
+//   scatter     copies every token row to its slot(s) in expert-contiguous order
+//   combine+LN  out = LayerNorm(x + sum_k gate_k * y[slot_k])
+// The slot a token gets inside its expert's segment depends on atomics and may differ from run
+// to run; results do not, because every GEMM row is computed independently of its position.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "kernels.h"
+
+namespace b2 {
+
+static constexpr int MOE_MAX_E = 16;
+static constexpr int MOE_MAX_K = 4;
+static constexpr int MOE_WARPS = 8;
+
+__device__ __forceinline__ void unpack8m(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(p[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8m(const float (&f)[8]) {
+  uint4 u;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+__device__ __forceinline__ float warp_sum_m(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__global__ void __launch_bounds__(MOE_WARPS * 32)
+moe_router_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wr, const float* __restrict__ br,
+                  int n_tokens, int hidden, int n_experts, int top_k, int32_t* __restrict__ topk_idx,
+                  float* __restrict__ topk_w, int32_t* __restrict__ counts) {
+  extern __shared__ float wr_s[];  // [n_experts, hidden]
+  for (int i = threadIdx.x; i < n_experts * hidden; i += blockDim.x) wr_s[i] = wr[i];
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int n_chunks = hidden >> 3;
+  const int warps_total = gridDim.x * MOE_WARPS;
+  for (int t = blockIdx.x * MOE_WARPS + (threadIdx.x >> 5); t < n_tokens; t += warps_total) {
+    const __nv_bfloat16* xr = x + static_cast<size_t>(t) * hidden;
+    float acc[MOE_MAX_E];
+#pragma unroll
+    for (int e = 0; e < MOE_MAX_E; ++e) acc[e] = 0.f;
+    for (int c = lane; c < n_chunks; c += 32) {
+      float v[8];
+      unpack8m(*reinterpret_cast<const uint4*>(xr + c * 8), v);
+#pragma unroll
+      for (int e = 0; e < MOE_MAX_E; ++e) {
+        if (e < n_experts) {
+          const float4 w0 = *reinterpret_cast<const float4*>(wr_s + e * hidden + c * 8);
+          const float4 w1 = *reinterpret_cast<const float4*>(wr_s + e * hidden + c * 8 + 4);
+          acc[e] += v[0] * w0.x + v[1] * w0.y + v[2] * w0.z + v[3] * w0.w + v[4] * w1.x + v[5] * w1.y + v[6] * w1.z +
+                    v[7] * w1.w;
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < MOE_MAX_E; ++e)
+      if (e < n_experts) acc[e] = warp_sum_m(acc[e]);
+    if (lane == 0) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < MOE_MAX_E; ++e)
+        if (e < n_experts) {
+          acc[e] += br != nullptr ? br[e] : 0.f;
+          mx = fmaxf(mx, acc[e]);
+        }
+      float den = 0.f;
+#pragma unroll
+      for (int e = 0; e < MOE_MAX_E; ++e)
+        if (e < n_experts) {
+          acc[e] = expf(acc[e] - mx);
+          den += acc[e];
+        }
+      uint32_t taken = 0;
+      for (int k = 0; k < top_k; ++k) {
+        int best = -1;
+        float bv = -1.f;
+#pragma unroll
+        for (int e = 0; e < MOE_MAX_E; ++e)
+          if (e < n_experts && !((taken >> e) & 1u) && acc[e] > bv) {  // strict >: a tie keeps the lower index
+            bv = acc[e];
+            best = e;
+          }
+        taken |= 1u << best;
+        topk_idx[static_cast<size_t>(t) * top_k + k] = best;
+        topk_w[static_cast<size_t>(t) * top_k + k] = bv / den;
+        if (counts != nullptr) atomicAdd(counts + best, 1);
+      }
+    }
+  }
+}
+
+// counts[e] -> seg_off[e] (row offset of expert e's segment, multiples of 128), cursor[e] = seg_off[e],
+// tile_expert[row block] = expert or -1.
+__global__ void moe_offsets_kernel(const int32_t* __restrict__ counts, int n_experts, int max_blocks,
+                                   int32_t* __restrict__ cursor, int32_t* __restrict__ tile_expert) {
+  __shared__ int32_t off[MOE_MAX_E + 1];
+  if (threadIdx.x == 0) {
+    int o = 0;
+    for (int e = 0; e < n_experts; ++e) {
+      off[e] = o;
+      cursor[e] = o;
+      o += (counts[e] + 127) / 128 * 128;
+    }
+    off[n_experts] = o;
+  }
+  __syncthreads();
+  for (int b = threadIdx.x; b < max_blocks; b += blockDim.x) {
+    const int row = b * 128;
+    int owner = -1;
+    for (int e = 0; e < n_experts; ++e)
+      if (row >= off[e] && row < off[e] + (counts[e] + 127) / 128 * 128) owner = e;
+    tile_expert[b] = owner;
+  }
+}
+
+__global__ void __launch_bounds__(MOE_WARPS * 32)
+moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ topk_idx, int n_slots, int top_k,
+                   int hidden, int32_t* __restrict__ cursor, int32_t* __restrict__ row_of,
+                   __nv_bfloat16* __restrict__ xperm) {
+  const int lane = threadIdx.x & 31;
+  const int warps_total = gridDim.x * MOE_WARPS;
+  for (int s = blockIdx.x * MOE_WARPS + (threadIdx.x >> 5); s < n_slots; s += warps_total) {
+    int row = 0;
+    if (lane == 0) {
+      row = atomicAdd(cursor + topk_idx[s], 1);
+      row_of[s] = row;
+    }
+    row = __shfl_sync(0xffffffffu, row, 0);
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(s / top_k) * hidden);
+    uint4* dst = reinterpret_cast<uint4*>(xperm + static_cast<size_t>(row) * hidden);
+    for (int c = lane; c < (hidden >> 3); c += 32) dst[c] = src[c];
+  }
+}
+
+template <int NCH>
+__global__ void __launch_bounds__(MOE_WARPS * 32)
+moe_combine_ln_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ yperm,
+                      const int32_t* __restrict__ row_of, const float* __restrict__ topk_w, int top_k,
+                      const float* __restrict__ gamma, const float* __restrict__ beta, int n_tokens, int hidden,
+                      float eps, __nv_bfloat16* __restrict__ out) {
+  extern __shared__ float ln_s[];  // gamma[hidden], beta[hidden]
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    ln_s[i] = gamma[i];
+    ln_s[hidden + i] = beta[i];
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int n_chunks = hidden >> 3;
+  const int warps_total = gridDim.x * MOE_WARPS;
+  for (int t = blockIdx.x * MOE_WARPS + (threadIdx.x >> 5); t < n_tokens; t += warps_total) {
+    float v[NCH][8];
+    const __nv_bfloat16* xr = x + static_cast<size_t>(t) * hidden;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const int c = lane + 32 * i;
+      if (c < n_chunks) unpack8m(*reinterpret_cast<const uint4*>(xr + c * 8), v[i]);
+    }
+    for (int k = 0; k < top_k; ++k) {
+      const float g = topk_w[static_cast<size_t>(t) * top_k + k];
+      const __nv_bfloat16* yr = yperm + static_cast<size_t>(row_of[static_cast<size_t>(t) * top_k + k]) * hidden;
+#pragma unroll
+      for (int i = 0; i < NCH; ++i) {
+        const int c = lane + 32 * i;
+        if (c < n_chunks) {
+          float a[8];
+          unpack8m(*reinterpret_cast<const uint4*>(yr + c * 8), a);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[i][e] = fmaf(g, a[e], v[i][e]);
+        }
+      }
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i)
+      if (lane + 32 * i < n_chunks) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum += v[i][e];
+      }
+    const float mean = warp_sum_m(sum) / hidden;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i)
+      if (lane + 32 * i < n_chunks) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float d = v[i][e] - mean;
+          sq += d * d;
+        }
+      }
+    const float rstd = rsqrtf(warp_sum_m(sq) / hidden + eps);
+    __nv_bfloat16* dst = out + static_cast<size_t>(t) * hidden;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const int c = lane + 32 * i;
+      if (c < n_chunks) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = (v[i][e] - mean) * rstd * ln_s[c * 8 + e] + ln_s[hidden + c * 8 + e];
+        *reinterpret_cast<uint4*>(dst + c * 8) = pack8m(o);
+      }
+    }
+  }
+}
+
+static int persistent_grid(int n_rows) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int full = (n_rows + MOE_WARPS - 1) / MOE_WARPS;
+  return full < sms * 4 ? (full > 0 ? full : 1) : sms * 4;
+}
+
+int launch_moe_router(const void* x, const float* wr, const float* br, int n_tokens, int hidden, int n_experts,
+                      int top_k, int32_t* topk_idx, float* topk_w, int32_t* counts, cudaStream_t stream) {
+  if (n_tokens <= 0) return B200EMB_OK;
+  if (n_experts < 1 || n_experts > MOE_MAX_E || top_k < 1 || top_k > MOE_MAX_K || top_k > n_experts)
+    return set_error(B200EMB_ERR_UNSUPPORTED, "router: need 1 <= top_k <= min(%d, n_experts) and n_experts <= %d", MOE_MAX_K, MOE_MAX_E);
+  if (hidden % 8) return set_error(B200EMB_ERR_UNSUPPORTED, "router: hidden %d not a multiple of 8", hidden);
+  const size_t smem = static_cast<size_t>(n_experts) * hidden * sizeof(float);
+  if (smem > 96 * 1024) return set_error(B200EMB_ERR_UNSUPPORTED, "router: n_experts * hidden too large for shared memory");
+  static bool attr = false;
+  if (!attr || smem > 48 * 1024) {
+    cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    attr = true;
+  }
+  if (counts != nullptr) B2_CUDA_CHECK(cudaMemsetAsync(counts, 0, sizeof(int32_t) * n_experts, stream));
+  moe_router_kernel<<<persistent_grid(n_tokens), MOE_WARPS * 32, smem, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), wr, br, n_tokens, hidden, n_experts, top_k, topk_idx, topk_w, counts);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "router launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
+int moe_max_row_blocks(int n_tokens, int top_k, int n_experts) {
+  return (n_tokens * top_k + n_experts * 127 + 127) / 128;
+}
+
+int launch_moe_scatter(const void* x, const int32_t* topk_idx, const int32_t* counts, int n_tokens, int top_k,
+                       int hidden, int n_experts, int32_t* cursor, int32_t* tile_expert, int32_t* row_of, void* xperm,
+                       cudaStream_t stream) {
+  if (n_tokens <= 0) return B200EMB_OK;
+  const int max_blocks = moe_max_row_blocks(n_tokens, top_k, n_experts);
+  moe_offsets_kernel<<<1, 256, 0, stream>>>(counts, n_experts, max_blocks, cursor, tile_expert);
+  moe_scatter_kernel<<<persistent_grid(n_tokens * top_k), MOE_WARPS * 32, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), topk_idx, n_tokens * top_k, top_k, hidden, cursor, row_of,
+      reinterpret_cast<__nv_bfloat16*>(xperm));
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "moe scatter launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
+int launch_moe_combine_ln(const void* x, const void* yperm, const int32_t* row_of, const float* topk_w, int top_k,
+                          const float* gamma, const float* beta, int n_tokens, int hidden, float eps, void* out,
+                          cudaStream_t stream) {
+  if (n_tokens <= 0) return B200EMB_OK;
+  if (hidden % 8 || (hidden >> 3) > 32 * 4)
+    return set_error(B200EMB_ERR_UNSUPPORTED, "moe combine: hidden %d unsupported (multiple of 8, at most 1024)", hidden);
+  const int nch = ((hidden >> 3) + 31) / 32;
+  const size_t smem = 2 * static_cast<size_t>(hidden) * sizeof(float);
+  const int grid = persistent_grid(n_tokens);
+  const __nv_bfloat16* xp = reinterpret_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* yp = reinterpret_cast<const __nv_bfloat16*>(yperm);
+  __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(out);
+  switch (nch) {
+    case 1: moe_combine_ln_kernel<1><<<grid, MOE_WARPS * 32, smem, stream>>>(xp, yp, row_of, topk_w, top_k, gamma, beta, n_tokens, hidden, eps, op); break;
+    case 2: moe_combine_ln_kernel<2><<<grid, MOE_WARPS * 32, smem, stream>>>(xp, yp, row_of, topk_w, top_k, gamma, beta, n_tokens, hidden, eps, op); break;
+    case 3: moe_combine_ln_kernel<3><<<grid, MOE_WARPS * 32, smem, stream>>>(xp, yp, row_of, topk_w, top_k, gamma, beta, n_tokens, hidden, eps, op); break;
+    default: moe_combine_ln_kernel<4><<<grid, MOE_WARPS * 32, smem, stream>>>(xp, yp, row_of, topk_w, top_k, gamma, beta, n_tokens, hidden, eps, op); break;
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "moe combine launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
+}  // namespace b2
+
+using namespace b2;
+
+extern "C" int b200emb_op_moe_router(const void* x, const float* router_w, const float* router_b, int32_t n_tokens,
+                                     int32_t hidden, int32_t n_experts, int32_t top_k, int32_t* topk_idx,
+                                     float* topk_weight, int32_t* counts, void* stream) {
+  if (x == nullptr || router_w == nullptr || topk_idx == nullptr || topk_weight == nullptr)
+    return set_error(B200EMB_ERR_INVALID, "moe_router: null pointer");
+  return launch_moe_router(x, router_w, router_b, n_tokens, hidden, n_experts, top_k, topk_idx, topk_weight, counts,
+                           reinterpret_cast<cudaStream_t>(stream));
+}

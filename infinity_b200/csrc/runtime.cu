@@ -115,6 +115,9 @@ struct Mat {
 
 struct LayerW {
   Mat qkv_w, o_w, ffn1_w, ffn2_w;  // decoder: ffn1_w = block-interleaved gate/up [2F, H], ffn2_w = down
+  // mixture-of-experts layers: router (fp32) and the experts' matrices stacked along the rows
+  bool is_moe = false;
+  const float *router_w = nullptr, *router_b = nullptr;
   const float *qkv_b, *o_b, *ffn1_b, *ffn2_b;
   const float *ln1_g, *ln1_b, *ln2_g, *ln2_b;
 };
@@ -145,6 +148,10 @@ struct DeviceCtx {
   AttnTile* d_tiles = nullptr;
   __nv_bfloat16 *x = nullptr, *x2 = nullptr, *qkv = nullptr, *ctx = nullptr, *y = nullptr, *ffn = nullptr;
   __nv_bfloat16 *pooled = nullptr, *head_h = nullptr;
+  // mixture of experts: routing tables and the expert-contiguous copies of the activations
+  int32_t *topk_idx = nullptr, *row_of = nullptr, *moe_counts = nullptr, *moe_cursor = nullptr, *tile_expert = nullptr;
+  float* topk_w = nullptr;
+  __nv_bfloat16 *xperm = nullptr, *hperm = nullptr, *yperm = nullptr;
   __nv_bfloat16* wscratch = nullptr;  // expanded copy of the quantised matrix in use
   size_t wscratch_elems = 0;
   float* hres = nullptr;     // decoder: fp32 residual stream [T, H]
@@ -212,6 +219,19 @@ static int ensure_capacity(b200emb_handle* h, DeviceCtx* c, int n_tokens, int n_
     if (!rc) rc = dev_alloc(&c->ctx, T * (size_t)d.n_heads * d.head_dim);
     if (!rc) rc = dev_alloc(&c->qkv, T * QKV);
     if (!rc) rc = dev_alloc(&c->ffn, T * (size_t)d.ffn);
+    if (!rc && d.arch == B200EMB_ARCH_MOE) {
+      const size_t K = d.top_k, E = d.n_experts;
+      const size_t Mp = (size_t)moe_max_row_blocks((int)T, d.top_k, d.n_experts) * 128;
+      rc = dev_alloc(&c->topk_idx, T * K);
+      if (!rc) rc = dev_alloc(&c->row_of, T * K);
+      if (!rc) rc = dev_alloc(&c->topk_w, T * K);
+      if (!rc) rc = dev_alloc(&c->moe_counts, E);
+      if (!rc) rc = dev_alloc(&c->moe_cursor, E);
+      if (!rc) rc = dev_alloc(&c->tile_expert, Mp / 128);
+      if (!rc) rc = dev_alloc(&c->xperm, Mp * H);
+      if (!rc) rc = dev_alloc(&c->hperm, Mp * (size_t)d.ffn);
+      if (!rc) rc = dev_alloc(&c->yperm, Mp * H);
+    }
     if (!rc) rc = host_alloc(&c->h_ids, T);
     if (!rc) rc = host_alloc(&c->h_types, T);
     if (rc) return rc;
@@ -350,10 +370,21 @@ static int bind_weights(const b200emb_model_desc& d, const WeightFile& wf, Devic
     B2_LK(o_b, "o.b", 0, H)
     B2_LK(ln1_g, "ln1.g", 0, H)
     B2_LK(ln1_b, "ln1.b", 0, H)
-    B2_LM(ffn1_w, "ffn1.w", F, H)
-    B2_LK(ffn1_b, "ffn1.b", 0, F)
-    B2_LM(ffn2_w, "ffn2.w", H, F)
-    B2_LK(ffn2_b, "ffn2.b", 0, H)
+    L.is_moe = d.arch == B200EMB_ARCH_MOE && d.moe_every > 0 && (l % d.moe_every) == d.moe_every - 1;
+    if (L.is_moe) {
+      const uint64_t E = d.n_experts;
+      B2_LK(router_w, "router.w", 0, E * H)
+      B2_LK(router_b, "router.b", 0, E)
+      B2_LM(ffn1_w, "experts.ffn1.w", E * F, H)
+      B2_LK(ffn1_b, "experts.ffn1.b", 0, E * F)
+      B2_LM(ffn2_w, "experts.ffn2.w", E * H, F)
+      B2_LK(ffn2_b, "experts.ffn2.b", 0, E * H)
+    } else {
+      B2_LM(ffn1_w, "ffn1.w", F, H)
+      B2_LK(ffn1_b, "ffn1.b", 0, F)
+      B2_LM(ffn2_w, "ffn2.w", H, F)
+      B2_LK(ffn2_b, "ffn2.b", 0, H)
+    }
 #undef B2_LM
     B2_LK(ln2_g, "ln2.g", 0, H)
     B2_LK(ln2_b, "ln2.b", 0, H)
@@ -377,6 +408,8 @@ static void destroy_ctx(DeviceCtx* c) {
   cudaFree(c->x); cudaFree(c->x2); cudaFree(c->qkv); cudaFree(c->ctx); cudaFree(c->y); cudaFree(c->ffn);
   cudaFree(c->pooled); cudaFree(c->head_h); cudaFree(c->d_out); cudaFree(c->d_err);
   cudaFree(c->hres); cudaFree(c->rope_cs); cudaFree(c->wscratch);
+  cudaFree(c->topk_idx); cudaFree(c->row_of); cudaFree(c->moe_counts); cudaFree(c->moe_cursor); cudaFree(c->tile_expert);
+  cudaFree(c->topk_w); cudaFree(c->xperm); cudaFree(c->hperm); cudaFree(c->yperm);
   cudaFreeHost(c->h_ids); cudaFreeHost(c->h_types); cudaFreeHost(c->h_cu); cudaFreeHost(c->h_tiles);
   cudaFreeHost(c->h_out); cudaFreeHost(c->h_err);
   for (auto& e : c->ev) if (e) cudaEventDestroy(e);
@@ -387,8 +420,12 @@ static void destroy_ctx(DeviceCtx* c) {
 
 static int validate_desc(const b200emb_model_desc& d) {
   if (d.abi_version != B200EMB_ABI_VERSION) return set_error(B200EMB_ERR_INVALID, "abi_version %d != %d", d.abi_version, B200EMB_ABI_VERSION);
-  if (d.arch != B200EMB_ARCH_BERT && d.arch != B200EMB_ARCH_XLMR && d.arch != B200EMB_ARCH_DECODER)
-    return set_error(B200EMB_ERR_UNSUPPORTED, "arch %d: the mixture-of-experts encoder is not built", d.arch);
+  if (d.arch < B200EMB_ARCH_BERT || d.arch > B200EMB_ARCH_DECODER) return set_error(B200EMB_ERR_INVALID, "unknown arch %d", d.arch);
+  if (d.arch == B200EMB_ARCH_MOE) {
+    if (d.n_experts < 1 || d.n_experts > 16 || d.top_k < 1 || d.top_k > 4 || d.top_k > d.n_experts || d.moe_every < 1)
+      return set_error(B200EMB_ERR_UNSUPPORTED, "mixture of experts: need n_experts <= 16, top_k <= min(4, n_experts), moe_every >= 1");
+    if (d.hidden > 1024) return set_error(B200EMB_ERR_UNSUPPORTED, "mixture of experts: hidden > 1024 is not built");
+  }
   if (d.weight_format < B200EMB_WFMT_BF16 || d.weight_format > B200EMB_WFMT_NVFP4)
     return set_error(B200EMB_ERR_INVALID, "unknown weight_format %d", d.weight_format);
   if (d.n_layers <= 0 || d.hidden <= 0 || d.n_heads <= 0 || d.ffn <= 0 || d.vocab <= 0 || d.max_pos <= 0)
@@ -437,6 +474,22 @@ static int gemm(DeviceCtx* c, const void* A, const void* W, const float* bias, v
   KernelScope ks(c, B200EMB_KCLASS_GEMM);
   c->gemm_flops += 2.0 * M * N * K;
   return launch_gemm_bf16(A, W, bias, C, M, N, K, epi, c->sm_count, c->d_err, c->stream, 0);
+}
+
+// One launch over all experts: A rows are expert-contiguous in 128-row blocks (tile_expert), W / bias are stacks.
+static int gemm_grouped(DeviceCtx* c, int wfmt, const void* A, const Mat& W, const float* bias, void* C, int m_padded,
+                        int m_algorithmic, int N, int K, int epi, int n_experts) {
+  const void* w = W.w;
+  if (W.q != nullptr) {
+    KernelScope ks(c, B200EMB_KCLASS_OTHER);
+    int rc = launch_dequantize(W.q, W.s, W.rows, W.cols, wfmt, c->wscratch, c->stream);
+    if (rc) return rc;
+    w = c->wscratch;
+  }
+  KernelScope ks(c, B200EMB_KCLASS_GEMM);
+  c->gemm_flops += 2.0 * m_algorithmic * N * K;
+  return launch_gemm_bf16(A, w, bias, C, m_padded, N, K, epi, c->sm_count, c->d_err, c->stream, N % 256 == 0 ? 256 : 128,
+                          W.alpha, c->tile_expert, n_experts);
 }
 
 // GEMM against a model weight; a block-quantised weight is expanded into the scratch first.
@@ -540,6 +593,33 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
       KernelScope ks(c, B200EMB_KCLASS_NORM);
       rc = launch_add_ln(c->x, c->y, L.ln1_g, L.ln1_b, T, H, d.norm_eps, c->x2, c->stream);
       if (rc) return rc;
+    }
+    if (L.is_moe) {
+      const int Mp = moe_max_row_blocks(T, d.top_k, d.n_experts) * 128;
+      {
+        KernelScope ks(c, B200EMB_KCLASS_OTHER);
+        rc = launch_moe_router(c->x2, L.router_w, L.router_b, T, H, d.n_experts, d.top_k, c->topk_idx, c->topk_w,
+                               c->moe_counts, c->stream);
+        if (rc) return rc;
+      }
+      {
+        KernelScope ks(c, B200EMB_KCLASS_OTHER);
+        c->launches++;  // offsets + scatter
+        rc = launch_moe_scatter(c->x2, c->topk_idx, c->moe_counts, T, d.top_k, H, d.n_experts, c->moe_cursor,
+                                c->tile_expert, c->row_of, c->xperm, c->stream);
+        if (rc) return rc;
+      }
+      rc = gemm_grouped(c, d.weight_format, c->xperm, L.ffn1_w, L.ffn1_b, c->hperm, Mp, T * d.top_k, F, H, EPI_BIAS_GELU,
+                        d.n_experts);
+      if (rc) return rc;
+      rc = gemm_grouped(c, d.weight_format, c->hperm, L.ffn2_w, L.ffn2_b, c->yperm, Mp, T * d.top_k, H, F, EPI_BIAS,
+                        d.n_experts);
+      if (rc) return rc;
+      KernelScope ks(c, B200EMB_KCLASS_NORM);
+      rc = launch_moe_combine_ln(c->x2, c->yperm, c->row_of, c->topk_w, d.top_k, L.ln2_g, L.ln2_b, T, H, d.norm_eps,
+                                 c->x, c->stream);
+      if (rc) return rc;
+      continue;
     }
     rc = gemm(c, d.weight_format, c->x2, L.ffn1_w, L.ffn1_b, c->ffn, T, F, H, EPI_BIAS_GELU);
     if (rc) return rc;
@@ -817,7 +897,7 @@ int b200emb_quantize_weights(const char* in_path, const char* out_path, int32_t 
   const uint64_t block = format == B200EMB_WFMT_NVFP4 ? 16 : 32;
   bool has_experts = false;
   for (const TensorEntry& e : wf.entries)
-    if (strstr(e.name, ".expert.") != nullptr) has_experts = true;
+    if (strstr(e.name, ".experts.") != nullptr) has_experts = true;
   struct OutTensor {
     TensorEntry e;
     std::vector<uint8_t> data;
@@ -842,7 +922,7 @@ int b200emb_quantize_weights(const char* in_path, const char* out_path, int32_t 
     const size_t len = strlen(e.name);
     const bool is_layer_mat = e.dtype == 1 && e.ndim == 2 && strncmp(e.name, "layer.", 6) == 0 && len > 2 &&
                               strcmp(e.name + len - 2, ".w") == 0 && e.dims[1] % block == 0 && len < 60;
-    const bool selected = is_layer_mat && (!has_experts || strstr(e.name, ".expert.") != nullptr);
+    const bool selected = is_layer_mat && (!has_experts || strstr(e.name, ".experts.") != nullptr);
     if (!selected) {
       std::vector<uint8_t> copy(wf.data.begin() + e.offset, wf.data.begin() + e.offset + e.nbytes);
       OutTensor t;

@@ -58,9 +58,54 @@ def encoder_hidden(spec, W: Dict[str, torch.Tensor], ids: torch.Tensor, mask: to
         a = torch.softmax(s, dim=-1) @ v
         a = a.transpose(1, 2).reshape(B, L, H)
         x = _ln(x + a @ W[p + "o.w"].t() + W[p + "o.b"], W[p + "ln1.g"], W[p + "ln1.b"], spec.norm_eps)
-        f = F.gelu(x @ W[p + "ffn1.w"].t() + W[p + "ffn1.b"])
-        x = _ln(x + f @ W[p + "ffn2.w"].t() + W[p + "ffn2.b"], W[p + "ln2.g"], W[p + "ln2.b"], spec.norm_eps)
+        if spec.arch == "moe" and spec.moe_every > 0 and l % spec.moe_every == spec.moe_every - 1:
+            y = moe_ffn(spec, W, p, x)
+        else:
+            y = F.gelu(x @ W[p + "ffn1.w"].t() + W[p + "ffn1.b"]) @ W[p + "ffn2.w"].t() + W[p + "ffn2.b"]
+        x = _ln(x + y, W[p + "ln2.g"], W[p + "ln2.b"], spec.norm_eps)
     return x
+
+
+def moe_route(x: np.ndarray, wr: np.ndarray, br: np.ndarray, top_k: int):
+    """Router of the mixture-of-experts layers: fp32 logits, softmax over all experts, top_k
+    experts per token with ties going to the lower index, gate = softmax probability of the
+    chosen expert, not renormalised. x [T, H] -> (idx int32 [T, k], gate float32 [T, k], probs)."""
+    logits = x.astype(np.float32) @ wr.astype(np.float32).T + br.astype(np.float32)
+    z = np.exp(logits - logits.max(axis=1, keepdims=True))
+    probs = (z / z.sum(axis=1, keepdims=True)).astype(np.float32)
+    work = probs.copy()
+    idx = np.zeros((x.shape[0], top_k), dtype=np.int32)
+    gate = np.zeros((x.shape[0], top_k), dtype=np.float32)
+    rows = np.arange(x.shape[0])
+    for k in range(top_k):
+        best = np.argmax(work, axis=1)  # first occurrence = lowest index on ties
+        idx[:, k] = best
+        gate[:, k] = probs[rows, best]
+        work[rows, best] = -1.0
+    return idx, gate, probs
+
+
+def moe_ffn(spec, W, p: str, x: torch.Tensor) -> torch.Tensor:
+    """sum_k gate_k * FFN_{e_k}(x), FFN_e = ffn2_e(gelu(ffn1_e(x))); x [B, L, H]. This block has no
+    third-party or reference implementation to follow: it is written from the benchmark
+    configuration's description (8 GELU experts of width F, top-2 softmax routing)."""
+    B, L, H = x.shape
+    F_, E = spec.ffn, spec.n_experts
+    flat = x.reshape(B * L, H)
+    idx, gate, _ = moe_route(flat.numpy(), W[p + "router.w"].numpy(), W[p + "router.b"].numpy(), spec.top_k)
+    out = torch.zeros_like(flat)
+    w1, b1 = W[p + "experts.ffn1.w"], W[p + "experts.ffn1.b"]
+    w2, b2 = W[p + "experts.ffn2.w"], W[p + "experts.ffn2.b"]
+    for e in range(E):
+        for k in range(spec.top_k):
+            sel = np.nonzero(idx[:, k] == e)[0]
+            if len(sel) == 0:
+                continue
+            xe = flat[sel]
+            he = F.gelu(xe @ w1[e * F_:(e + 1) * F_].t() + b1[e * F_:(e + 1) * F_])
+            ye = he @ w2[e * H:(e + 1) * H].t() + b2[e * H:(e + 1) * H]
+            out[sel] += torch.from_numpy(gate[sel, k])[:, None] * ye
+    return out.reshape(B, L, H)
 
 
 def pad_batch(seqs, types=None, pad_id: int = 0):

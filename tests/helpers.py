@@ -27,12 +27,12 @@ def quantized_oracle_tensors(spec, master: Dict[str, torch.Tensor], fmt: str) ->
     the same tensors the runtime quantises (fused qkv, block-interleaved gate/up), quantised and
     dequantised by the numpy statement, mapped back to the oracle's names."""
     rt = cf.runtime_tensors(master)
-    has_experts = any(".expert." in k for k in rt)
+    has_experts = any(".experts." in k for k in rt)
     out: Dict[str, torch.Tensor] = {}
     for k, v in rt.items():
         block = 16 if fmt == "nvfp4" else 32
         sel = (k.startswith("layer.") and k.endswith(".w") and v.dim() == 2 and v.shape[1] % block == 0
-               and (not has_experts or ".expert." in k))
+               and (not has_experts or ".experts." in k))
         if sel:
             w = v.float().numpy()
             if fmt == "nvfp4":

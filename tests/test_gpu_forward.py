@@ -112,6 +112,38 @@ def test_encoder_block_quantised_weights(tmp_path):
     model.close()
 
 
+@pytest.mark.parametrize("fmt,tol", [("bf16", COS_TOL), ("mxfp8", COS_TOL_BLOCK)])
+def test_tiny_moe_encoder_matches_oracle(tmp_path, fmt, tol):
+    """Mixture-of-experts encoder: router, expert-contiguous scatter, grouped GEMM over all experts,
+    gated combine + LayerNorm. With mxfp8 only the expert matrices are quantised."""
+    spec = cf.tiny_spec("moe", weight_format=fmt)
+    model, W = build_model(tmp_path, spec, 31, perturb=True)
+    batch = cf.random_batch(spec, [1, 2, 9, 64, 65, 127, 128, 160, 33, 77], 5)
+    got = model.forward(batch)
+    ref = enc.forward_batch(spec, W, batch)
+    cos = cosines(got, ref)
+    print("moe", fmt, cos.min())
+    assert cos.min() >= tol, cos
+    again = model.forward(batch)  # slots inside an expert segment may move; results must not
+    assert np.array_equal(got, again)
+    model.close()
+
+
+def test_moe_encoder_layer_shapes(tmp_path):
+    """Two layers with the configuration-4 shapes (hidden 768, 12 heads, 8 experts of width 3072,
+    top-2, MXFP8 expert matrices) and a reduced vocabulary."""
+    from dataclasses import replace
+    spec = replace(cf.MOE_ENCODER, n_layers=2, vocab=4096, name="moe-2layer")
+    model, W = build_model(tmp_path, spec, cf.SEEDS["c4"][2], perturb=False)
+    batch = cf.random_batch(spec, [16, 512, 300, 129, 64, 77, 511, 200] * 4, 6)
+    got = model.forward(batch)
+    ref = enc.forward_batch(spec, W, batch)
+    cos = cosines(got, ref)
+    print("c4 shape cosine min", cos.min())
+    assert cos.min() >= COS_TOL_BLOCK
+    model.close()
+
+
 def test_order_and_batch_independence(tmp_path):
     """Row i belongs to sequence i whatever the order, and a sequence's embedding does not
     depend on its neighbours in the batch (bit-exact: same kernels, same per-row math)."""

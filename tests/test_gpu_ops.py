@@ -194,3 +194,41 @@ def test_pool(lib, hidden, pooling, normalize):
     torch.cuda.synchronize()
     ref = OP.pool_ragged(x.float().cpu().numpy(), cu, pooling, bool(normalize))
     np.testing.assert_allclose(out.cpu().numpy(), ref, rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("T,H,E,k", [(1000, 768, 8, 2), (77, 128, 16, 4), (5, 256, 3, 1)])
+def test_moe_router_matches_numpy(lib, T, H, E, k):
+    """Routing is an index computation: expert ids must equal the numpy router's on the same
+    inputs (ties -> lower index). The only tolerated differences are tokens whose k-th and
+    (k+1)-th probabilities are closer than fp32 summation-order noise."""
+    from oracle.encoder import moe_route
+    g = torch.Generator(device="cuda").manual_seed(T + E)
+    x = torch.randn(T, H, generator=g, device="cuda").to(torch.bfloat16)
+    wr = torch.randn(E, H, generator=g, device="cuda") * 0.05
+    br = torch.randn(E, generator=g, device="cuda") * 0.1
+    if T >= 77:  # exact ties: two experts with identical weights and bias
+        wr[1] = wr[0]
+        br[1] = br[0]
+    idx = torch.full((T, k), -1, dtype=torch.int32, device="cuda")
+    gate = torch.zeros(T, k, dtype=torch.float32, device="cuda")
+    counts = torch.zeros(E, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    _lib.check(lib.b200emb_op_moe_router(x.data_ptr(), wr.data_ptr(), br.data_ptr(), T, H, E, k, idx.data_ptr(),
+                                         gate.data_ptr(), counts.data_ptr(), _stream()))
+    torch.cuda.synchronize()
+    ref_idx, ref_gate, probs = moe_route(x.float().cpu().numpy(), wr.cpu().numpy(), br.cpu().numpy(), k)
+    got_idx = idx.cpu().numpy()
+    srt = -np.sort(-probs, axis=1)
+    gap = (srt[:, :k] - srt[:, 1:k + 1]).min(axis=1) if E > k else np.ones(T)
+    differs = (got_idx != ref_idx).any(axis=1)
+    if T >= 77:
+        # tokens where the duplicated pair straddles the selection cut must pick expert 0 (lower index) first
+        pair_first = (ref_idx == 0).any(axis=1) | ~(ref_idx == 1).any(axis=1)
+        assert pair_first.all()
+        exact_tie = np.isclose(probs[:, 0], probs[:, 1], rtol=0, atol=0)
+        assert exact_tie.all()
+    assert not (differs & (gap > 1e-6)).any(), f"{differs.sum()} tokens differ"
+    ok = ~differs
+    np.testing.assert_allclose(gate.cpu().numpy()[ok], ref_gate[ok], rtol=2e-5, atol=1e-7)
+    assert counts.sum().item() == T * k
+    assert np.array_equal(np.bincount(got_idx.ravel(), minlength=E), counts.cpu().numpy())
