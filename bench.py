@@ -37,7 +37,7 @@ import numpy as np
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-CFG = "c2"
+CFG = "c2"          # the configuration the headline metric is quoted on
 SEQS_PER_GPU = 1024
 
 

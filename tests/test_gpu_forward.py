@@ -195,6 +195,29 @@ def test_config1_bge_small_shape(tmp_path):
     model.close()
 
 
+def test_config3_xlmr_large_reranker_subset(tmp_path):
+    """Configuration 3 weights (XLM-R-large shape, 250002-row vocabulary, classification head):
+    256 of its pairs on the GPU, 24 of them against the oracle; logits within 1e-2 and the
+    sigmoid scores the batcher derives from them (batch_handler.py:208-210) within 1e-2 too."""
+    spec = cf.XLMR_LARGE_RERANK
+    model, W = build_model(tmp_path, spec, cf.SEEDS["c3"][2], perturb=False)
+    batch = cf.synth_batch("c3", 256)
+    assert batch.lengths.max() <= 512 and batch.lengths.min() >= 8 + 64 + 4
+    full = model.forward(batch)
+    assert full.shape == (256, 1) and np.isfinite(full).all()
+    pick = list(range(0, 256, 11))[:24]
+    seqs = batch.sequences()
+    sub = cf.pack([seqs[i] for i in pick])
+    got = model.forward(sub)
+    assert np.array_equal(got, full[pick])
+    ref = enc.forward_batch(spec, W, sub)
+    print("c3 max |logit diff|", np.abs(got - ref).max())
+    assert np.abs(got - ref).max() <= LOGIT_TOL
+    sig = lambda z: 1.0 / (1.0 + np.exp(-z))
+    assert np.abs(sig(got) - sig(ref)).max() <= LOGIT_TOL
+    model.close()
+
+
 def test_config2_bert_large_shape_subset(tmp_path):
     """Configuration 2 weights, 48 of its sequences (the oracle needs ~1 s per sequence on CPU);
     the GPU runs the full 1024-sequence batch and the rows of the subset must be identical."""
