@@ -11,6 +11,12 @@
 //                 add the bias (staged in shared memory), apply GELU / tanh, round to bf16,
 //                 write a 128x64 sub-tile into 128-byte-swizzled shared memory and hand it to
 //                 a TMA store (one staging buffer per group, re-used once its store has read it)
+// CTA-pair variant (PAIR, large problems): two CTAs of a cluster own one 256 x 256 tile
+// (tcgen05 cta_group::2). Each CTA loads its 128 rows of A and HALF of the W tile (32 KB per
+// stage instead of 48 KB, six stages instead of four); both CTAs' TMA loads complete on the
+// leader's full barrier, the leader's MMA warp issues the 256 x 256 x 16 MMAs for the pair and
+// commits onto both CTAs' empty / accumulator-full barriers, each CTA runs the epilogue of its own
+// 128 accumulator rows and releases the accumulator on the leader's barrier. No multicast load.
 // M is ragged (token count): TMA zero-fills rows past M on loads and clips them on stores.
 // No cluster launch, no multicast: each CTA issues its own loads; W tiles are re-used
 // out of L2.
@@ -31,12 +37,15 @@ static constexpr int UMMA_K = 16;
 static constexpr int N_EPI_WARPS = 8;
 static constexpr int GEMM_THREADS = 32 * (2 + N_EPI_WARPS);
 
-template <int BN>
+// PAIR: two CTAs of a cluster share one 256 x BN tile (tcgen05 cta_group::2): each CTA loads its 128
+// rows of A and only half of the W tile, so a stage is 32 KB instead of 48 KB (six stages instead of four).
+template <int BN, bool PAIR = false>
 struct GemmCfg {
   static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int B_ROWS = PAIR ? BN / 2 : BN;  // W rows this CTA loads per stage
+  static constexpr int B_BYTES = B_ROWS * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int STAGES = (196608 / STAGE_BYTES) < 8 ? (196608 / STAGE_BYTES) : 8;
   static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // two accumulator buffers
   static constexpr int CBUF_BYTES = BM * 64 * 2;  // one 128x64 bf16 output sub-tile
   static constexpr int BIAS_BYTES = 256 * 4;
@@ -90,13 +99,14 @@ __device__ __forceinline__ uint32_t epilogue_pack2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&p);
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                          const __grid_constant__ CUtensorMap tmap_c, const float* __restrict__ bias, float alpha, int M, int N,
                          int K, const int32_t* __restrict__ tile_expert, int* __restrict__ err_flag) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, PAIR>;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int TILE_M = PAIR ? 2 * BM : BM;  // rows of one scheduled tile (both CTAs of a pair)
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled tiles must start on a 1024-byte boundary.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -111,10 +121,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int m_tiles = (M + BM - 1) / BM;
+  const int m_tiles = (M + TILE_M - 1) / TILE_M;
   const int n_tiles = (N + BN - 1) / BN;
   const int total_tiles = m_tiles * n_tiles;
   const int k_blocks = (K + BK - 1) / BK;
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;       // 0 = leader of the pair
+  const int first_tile = PAIR ? (blockIdx.x >> 1) : blockIdx.x;  // tiles are dealt to pairs
+  const int tile_step = PAIR ? (gridDim.x >> 1) : gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -123,17 +136,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full_bar[a], 1);
-      mbar_init(&acc_empty_bar[a], N_EPI_WARPS);
+      mbar_init(&acc_empty_bar[a], PAIR ? 2 * N_EPI_WARPS : N_EPI_WARPS);  // pair: both CTAs' epilogue warps
     }
     mbar_init(drain_bar, 1);
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_base_slot, Cfg::TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(tmem_base_slot, Cfg::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_base_slot, Cfg::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if (PAIR) cluster_sync_all();  // the peer's barriers exist before anything is signalled on them
+  else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
 
@@ -147,14 +166,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       uint32_t phase = 0;
       bool ok = true;
       uint32_t issued = 0;  // slots filled so far (for draining on the error path)
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / n_tiles) * BM;
+      // pair: both CTAs' loads complete on the leader's full barrier, which expects both stages' bytes
+      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
+        const int m0 = (tile / n_tiles) * TILE_M + static_cast<int>(cta_rank) * BM;
         const int n0 = (tile % n_tiles) * BN;
         // grouped mode: row block m0/BM belongs to expert e (its weights are rows [e*N, e*N + N) of W);
         // e < 0 marks an unused row block, skipped by every role alike
         const int expert = tile_expert != nullptr ? __ldg(tile_expert + tile / n_tiles) : 0;
         if (expert < 0) continue;
-        const int w_row0 = expert * N + n0;
+        const int w_row0 = expert * N + n0 + static_cast<int>(cta_rank) * Cfg::B_ROWS * (PAIR ? 1 : 0);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u)) {
             ok = false;
@@ -162,9 +182,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           }
           uint8_t* a_dst = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* b_dst = a_dst + Cfg::A_BYTES;
-          mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
-          tma_load_2d(a_dst, &tmap_a, &full_bar[stage], kb * BK, m0);
-          tma_load_2d(b_dst, &tmap_w, &full_bar[stage], kb * BK, w_row0);
+          if (PAIR) {
+            if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::STAGE_BYTES);
+            const uint32_t leader_full = mapa_shared(smem_u32(&full_bar[stage]), 0);
+            tma_load_2d_pair(a_dst, &tmap_a, leader_full, kb * BK, m0);
+            tma_load_2d_pair(b_dst, &tmap_w, leader_full, kb * BK, w_row0);
+          } else {
+            mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+            tma_load_2d(a_dst, &tmap_a, &full_bar[stage], kb * BK, m0);
+            tma_load_2d(b_dst, &tmap_w, &full_bar[stage], kb * BK, w_row0);
+          }
           ++issued;
           if (++stage == STAGES) {
             stage = 0;
@@ -176,7 +203,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         atomicExch(err_flag, 1);
         // Let the copies already in flight land before this CTA's shared memory is released:
         // wait (bounded) on the full barrier of every slot filled in the last lap.
-        const uint32_t pending = issued < (uint32_t)STAGES ? issued : (uint32_t)STAGES;
+        const uint32_t pending = (PAIR && cta_rank != 0) ? 0u : (issued < (uint32_t)STAGES ? issued : (uint32_t)STAGES);
         for (uint32_t i = 0; i < pending; ++i) {
           const uint32_t idx = issued - 1 - i;  // i-th most recent fill
           mbar_wait(&full_bar[idx % STAGES], (idx / STAGES) & 1u);
@@ -185,13 +212,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16_f32(BM, BN);
+    if (lane == 0 && cta_rank == 0) {  // pair: the leader issues the MMAs of both CTAs
+      constexpr uint32_t idesc = make_idesc_bf16_f32(TILE_M, BN);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int local_tile = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
         if (tile_expert != nullptr && __ldg(tile_expert + tile / n_tiles) < 0) continue;
         const int lt = local_tile++;
         const int acc = lt & 1;
@@ -215,19 +242,35 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advancing 16 elements along K inside the 128-byte swizzle span = +32 bytes = +2 encoded
-            tc_mma_f16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (PAIR) tc_mma_f16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            else tc_mma_f16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          tc_commit(&empty_bar[stage]);  // slot is free once these MMAs have read it
+          // slot is free once these MMAs have read it (pair: in both CTAs)
+          if (PAIR) {
+            tc_commit_pair(mapa_shared(smem_u32(&empty_bar[stage]), 0));
+            tc_commit_pair(mapa_shared(smem_u32(&empty_bar[stage]), 1));
+          } else {
+            tc_commit(&empty_bar[stage]);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) tc_commit(&acc_full_bar[acc]);  // accumulator complete
+        if (ok) {  // accumulator complete
+          if (PAIR) {
+            tc_commit_pair(mapa_shared(smem_u32(&acc_full_bar[acc]), 0));
+            tc_commit_pair(mapa_shared(smem_u32(&acc_full_bar[acc]), 1));
+          } else {
+            tc_commit(&acc_full_bar[acc]);
+          }
+        }
       }
       if (!ok) {
         atomicExch(err_flag, 2);
-        tc_commit(drain_bar);  // MMAs already issued must finish before the accumulators are freed
+        // MMAs already issued must finish before the accumulators are freed
+        if (PAIR) tc_commit_pair(mapa_shared(smem_u32(drain_bar), 0));
+        else tc_commit(drain_bar);
         mbar_wait(drain_bar, 0);
       }
     }
@@ -244,11 +287,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const bool store_thread = (ew & 3) == 0 && lane == 0;
     bool ok = true;
     int local_tile = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    for (int tile = first_tile; tile < total_tiles; tile += tile_step) {
       const int expert = tile_expert != nullptr ? __ldg(tile_expert + tile / n_tiles) : 0;
       if (expert < 0) continue;
       const int lt = local_tile++;
-      const int m0 = (tile / n_tiles) * BM;
+      const int m0 = (tile / n_tiles) * TILE_M + static_cast<int>(cta_rank) * BM;
       const int n0 = (tile % n_tiles) * BN;
       const int acc = lt & 1;
       const uint32_t acc_phase = (lt >> 1) & 1u;
@@ -281,7 +324,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           if (p == 1) {
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+            if (lane == 0) {
+            if (PAIR) mbar_arrive_cluster(mapa_shared(smem_u32(&acc_empty_bar[acc]), 0));  // the leader's barrier
+            else mbar_arrive(&acc_empty_bar[acc]);
+          }
           }
           if (have) {
             const float* bg = bias_s + grp * 64 + p * 32;
@@ -325,7 +371,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           // the accumulator is in registers: hand the TMEM buffer back to the MMA warp
           tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+          if (lane == 0) {
+            if (PAIR) mbar_arrive_cluster(mapa_shared(smem_u32(&acc_empty_bar[acc]), 0));  // the leader's barrier
+            else mbar_arrive(&acc_empty_bar[acc]);
+          }
         }
         if (sub < SUBS && n0 + sub * 64 < N) {  // uniform within the group
           if (store_thread) tma_store_wait_read();  // the previous store out of this buffer has read it
@@ -366,10 +415,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   }
 
   tc_fence_before_sync();
-  __syncthreads();
+  if (PAIR) cluster_sync_all();  // neither CTA leaves while the other may still touch its memory or barriers
+  else __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if (PAIR) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+    else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
 
@@ -408,11 +459,38 @@ int make_tmap_bf16_2d(CUtensorMap_st* out, const void* base, uint64_t rows, uint
   return B200EMB_OK;
 }
 
+// Pair kernels are launched as clusters of two CTAs; the number of resident pairs is queried once per device.
+template <int BN, int EPI>
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, const float* bias, float alpha,
+                       int M, int N, int K, int sm_count, int* err_flag, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN, true>;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, EPI, true>;
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  int pairs = sm_count / 2;
+  if (tiles < pairs) pairs = tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const int32_t* no_experts = nullptr;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tw, tc, bias, alpha, M, N, K, no_experts, err_flag);
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "gemm pair launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
 template <int BN, int EPI>
 static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, const float* bias, float alpha,
                       int M, int N, int K, const int32_t* tile_expert, int sm_count, int* err_flag, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
-  auto kern = gemm_bf16_tcgen05_kernel<BN, EPI>;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, EPI, false>;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
   const int tiles = m_tiles * n_tiles;
   const int grid = tiles < sm_count ? tiles : sm_count;
@@ -425,7 +503,18 @@ static int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tw, const CUtens
 template <int BN>
 static int launch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& tc, const float* bias,
                       float alpha, int M, int N, int K, const int32_t* tile_expert, int sm_count, int* err_flag,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, bool pair = false) {
+  if constexpr (BN == 256) {
+    if (pair) {
+      switch (epi) {
+        case EPI_BIAS: return launch_pair<BN, EPI_BIAS>(ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
+        case EPI_BIAS_GELU: return launch_pair<BN, EPI_BIAS_GELU>(ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
+        case EPI_BIAS_TANH: return launch_pair<BN, EPI_BIAS_TANH>(ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
+        case EPI_BIAS_SWIGLU: return launch_pair<BN, EPI_BIAS_SWIGLU>(ta, tw, tc, bias, alpha, M, N, K, sm_count, err_flag, stream);
+      }
+      return set_error(B200EMB_ERR_INVALID, "unknown epilogue %d", epi);
+    }
+  }
   switch (epi) {
     case EPI_BIAS: return launch_cfg<BN, EPI_BIAS>(ta, tw, tc, bias, alpha, M, N, K, tile_expert, sm_count, err_flag, stream);
     case EPI_BIAS_GELU: return launch_cfg<BN, EPI_BIAS_GELU>(ta, tw, tc, bias, alpha, M, N, K, tile_expert, sm_count, err_flag, stream);
@@ -439,8 +528,12 @@ static int launch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tw, con
 
 template <int BN, int EPI>
 static int init_one() {
-  B2_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  B2_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      GemmCfg<BN>::SMEM_BYTES));
+  if constexpr (BN == 256) {
+    B2_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       GemmCfg<BN, true>::SMEM_BYTES));
+  }
   return B200EMB_OK;
 }
 template <int BN>
@@ -477,7 +570,10 @@ int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, i
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) ||
       (reinterpret_cast<uintptr_t>(C) & 15) || (bias && (reinterpret_cast<uintptr_t>(bias) & 15)))
     return set_error(B200EMB_ERR_INVALID, "gemm: pointers must be 16-byte aligned");
-  int bn = force_bn > 0 ? force_bn : gemm_pick_bn(M, N, sm_count);
+  // force_bn 257 = CTA-pair kernel (256-wide tiles); otherwise pairs are used whenever the widest tile is
+  // chosen, the problem is not grouped, and there is at least one 256 x 256 tile per pair of SMs
+  bool pair = force_bn == 257;
+  int bn = pair ? 256 : (force_bn > 0 ? force_bn : gemm_pick_bn(M, N, sm_count));
   int n_out = N;
   if (epi == EPI_BIAS_SWIGLU) {
     // W holds 128-row blocks [gate rows | up rows]; a 256-wide tile yields 128 output columns
@@ -485,17 +581,22 @@ int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, i
     bn = 256;
     n_out = N / 2;
   }
+  if (force_bn == 0 && bn == 256 && tile_expert == nullptr &&
+      ((M + 255) / 256) * ((N + 255) / 256) >= sm_count / 2)
+    pair = true;
+  if (pair && tile_expert != nullptr) return set_error(B200EMB_ERR_INVALID, "gemm: the CTA-pair kernel has no grouped mode");
   CUtensorMap ta, tw, tc;
   int rc = make_tmap_bf16_2d(&ta, A, (uint64_t)M, (uint64_t)K, BM);
   if (rc) return rc;
   if (tile_expert != nullptr && (N % bn) != 0)
     return set_error(B200EMB_ERR_INVALID, "grouped gemm: N = %d must be a multiple of the tile width %d", N, bn);
-  rc = make_tmap_bf16_2d(&tw, W, (uint64_t)N * (tile_expert != nullptr ? n_experts : 1), (uint64_t)K, (uint32_t)bn);
+  rc = make_tmap_bf16_2d(&tw, W, (uint64_t)N * (tile_expert != nullptr ? n_experts : 1), (uint64_t)K,
+                         (uint32_t)(pair ? bn / 2 : bn));
   if (rc) return rc;
   rc = make_tmap_bf16_2d(&tc, C, (uint64_t)M, (uint64_t)n_out, BM);
   if (rc) return rc;
   switch (bn) {
-    case 256: return launch_epi<256>(epi, ta, tw, tc, bias, alpha, M, N, K, tile_expert, sm_count, err_flag, stream);
+    case 256: return launch_epi<256>(epi, ta, tw, tc, bias, alpha, M, N, K, tile_expert, sm_count, err_flag, stream, pair);
     case 128: return launch_epi<128>(epi, ta, tw, tc, bias, alpha, M, N, K, tile_expert, sm_count, err_flag, stream);
     case 64: return launch_epi<64>(epi, ta, tw, tc, bias, alpha, M, N, K, tile_expert, sm_count, err_flag, stream);
   }

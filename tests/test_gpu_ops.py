@@ -52,7 +52,7 @@ def test_gemm_bf16(lib, M, N, K, epi):
     w = (torch.randn(N, K, generator=g, device="cuda") / math.sqrt(K)).to(torch.bfloat16)
     bias = torch.randn(N, generator=g, device="cuda") * 0.5
     ref = _gemm_ref(a, w, bias, epi)
-    for bn in (0, 64, 128, 256):
+    for bn in (0, 64, 128, 256, 257):  # 257 = CTA-pair kernel (cta_group::2)
         c = _gemm(lib, a, w, bias, epi, bn)
         err = (c.float() - ref).abs().max().item()
         # bf16 output rounding: half an ulp at |x| <= ~8 is 2^-6; inputs are O(1)
@@ -85,7 +85,7 @@ def test_gemm_no_bias_and_identity(lib):
     K = N = 256
     a = torch.randn(513, K, device="cuda").to(torch.bfloat16)
     w = torch.eye(N, K, device="cuda").to(torch.bfloat16)
-    for bn in (64, 128, 256):
+    for bn in (64, 128, 256, 257):
         c = _gemm(lib, a, w, None, "bias", bn)
         assert torch.equal(c, a)
 
