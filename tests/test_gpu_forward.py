@@ -161,6 +161,28 @@ def test_order_and_batch_independence(tmp_path):
     model.close()
 
 
+def test_multi_device_handle_equals_single_device(tmp_path):
+    """One handle over several GPUs: token-balanced split, rows scattered back to batch order; the
+    result must be bit-identical to the single-GPU result (same kernels, same per-sequence math)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    spec = cf.tiny_spec("bert", hidden=256, n_heads=4, n_kv_heads=4, head_dim=64, ffn=512)
+    single, _ = build_model(tmp_path, spec, 41, perturb=True, device_ids=(0,))
+    n_dev = min(torch.cuda.device_count(), 4)
+    multi, _ = build_model(tmp_path, spec, 41, perturb=True, device_ids=tuple(range(n_dev)))
+    rng = np.random.default_rng(3)
+    batch = cf.random_batch(spec, rng.integers(1, 161, size=97), 9, with_types=True)
+    a = single.forward(batch)
+    b = multi.forward(batch)
+    assert multi.last_timing["n_devices"] == n_dev
+    assert np.array_equal(a, b)
+    cu = batch.cu_seqlens
+    one = multi.forward(cf.pack([batch.sequences()[5]], [batch.token_type_ids[cu[5]:cu[6]]]))  # runs on the first device
+    assert np.array_equal(one[0], a[5])
+    single.close()
+    multi.close()
+
+
 def test_invalid_inputs_are_rejected(tmp_path):
     from infinity_b200._lib import B200EmbError
     spec = cf.tiny_spec("bert")
