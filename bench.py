@@ -295,7 +295,7 @@ def run_ours(args):
             },
             "wall_ms_per_step": wall_ms / args.steps,
             "roofline": {
-                "kernel": "gemm_bf16_tcgen05_kernel (all 97 launches of a step)", "bound": "tensor",
+                "kernel": "gemm_bf16_tcgen05_kernel (all 96 launches of a step)", "bound": "tensor",
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": (achieved / peak) if achieved else None,
                 "peak_kind": f"bf16 sustained, {peaks['source']} (burst {peaks['bf16_tflops']})",
                 "frac_of_burst": (achieved / peaks["bf16_tflops"]) if achieved else None,
@@ -315,9 +315,10 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch from the ncu capture summarised
-# under profiles/ (null until a capture of this kernel exists).
-TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch (average over the four shapes of a layer),
+# from the ncu captures at M = 32768 summarised under profiles/gemm_bf16_tcgen05_*.md, scaled by
+# 166962 / 32768 (traffic grows in proportion to the rows).
+TRAFFIC_BYTES_PER_LAUNCH = 1.20e9
 
 
 def main():

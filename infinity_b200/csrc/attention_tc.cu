@@ -53,6 +53,13 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
+// Position of the MMA issuer in the CTA's sequence of (item, key tile) steps.
+struct StepCursor {
+  int item, it, n_kv, seq_len;
+  int qslot, kvstage;
+  uint32_t qphase, kvphase;
+};
+
 // Persistent: CTA b serves work items b, b + gridDim.x, ...; item i = (query tile i / n_heads,
 // head i % n_heads). Warp 4 runs ahead with the TMA loads (Q double-buffered, K/V through a
 // two-stage ring, slots released by tcgen05.commit), so launch, allocation and load latency
@@ -154,10 +161,54 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
   } else {
     // ---------------- softmax warps (thread 0 also issues the MMAs) ----------------
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    int qslot = 0, kvstage = 0;
-    uint32_t qphase = 0, kvphase = 0;
+    int kvstage = 0;
     uint32_t gi = 0;  // KV tiles processed so far by this CTA: phase of bar_s / bar_o
     bool failed = false;
+
+    // Thread 0 issues S = Q K^T one step AHEAD of the softmax: S of step k+1 is issued together with
+    // P V of step k (the S columns are free once every thread has read them in pass 2), so its
+    // round trip hides behind the P V wait and the O update.
+    StepCursor cur;
+    cur.item = blockIdx.x;
+    cur.it = 0;
+    cur.n_kv = 0;
+    cur.seq_len = 0;
+    cur.qslot = cur.kvstage = 0;
+    cur.qphase = cur.kvphase = 0;
+    auto issue_s = [&]() -> bool {  // false when a wait gave up
+      if (cur.item >= n_items) return true;
+      if (cur.it == 0) {
+        const AttnTile tt = tiles[cur.item / n_heads];
+        cur.seq_len = tt.seq_len;
+        cur.n_kv = (tt.seq_len + TC_BKV - 1) / TC_BKV;
+        if (!mbar_wait(&q_full[cur.qslot], cur.qphase)) return false;
+      }
+      if (!mbar_wait(&kv_full[cur.kvstage], cur.kvphase)) return false;
+      tc_fence_after_sync();
+      const int nv = min(TC_BKV, cur.seq_len - cur.it * TC_BKV);
+      const uint32_t idesc = make_idesc_bf16_f32(128, (nv + 15) & ~15);
+      const uint64_t a_desc = make_kmajor_sw128_desc(smem_u32(q_s + cur.qslot * TC_TILE_BYTES));
+      const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(kv_s + cur.kvstage * 2 * TC_TILE_BYTES));
+#pragma unroll
+      for (int k = 0; k < TC_D / 16; ++k)
+        tc_mma_f16(tmem_base + TC_S_COL, a_desc + 2 * k, b_desc + 2 * k, idesc, k != 0);
+      tc_commit(bar_s);
+      if (cur.it == cur.n_kv - 1) tc_commit(&q_empty[cur.qslot]);  // last use of this Q tile
+      if (++cur.kvstage == TC_KVSTAGES) {
+        cur.kvstage = 0;
+        cur.kvphase ^= 1u;
+      }
+      if (++cur.it == cur.n_kv) {
+        cur.it = 0;
+        cur.item += gridDim.x;
+        if (++cur.qslot == TC_QSLOTS) {
+          cur.qslot = 0;
+          cur.qphase ^= 1u;
+        }
+      }
+      return true;
+    };
+    if (threadIdx.x == 0 && !issue_s()) failed = true;
     B2_PROF_DECL
     for (int item = blockIdx.x; item < n_items && !failed; item += gridDim.x) {
       const AttnTile t = tiles[item / n_heads];
@@ -174,28 +225,7 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
         const int kv0 = it * TC_BKV;
         const int n_valid = min(TC_BKV, L - kv0);
         const int n_eff = (n_valid + 15) & ~15;
-        uint8_t* k_t = kv_s + kvstage * 2 * TC_TILE_BYTES;
-        uint8_t* v_t = k_t + TC_TILE_BYTES;
-        B2_PROF(0);  // item / tile setup
-        if (threadIdx.x == 0) {
-          bool ok = true;
-          if (it == 0) ok = mbar_wait(&q_full[qslot], qphase);
-          ok = ok && mbar_wait(&kv_full[kvstage], kvphase);
-          B2_PROF(1);  // wait for Q / K / V
-          if (ok) {
-            tc_fence_after_sync();
-            const uint32_t idesc = make_idesc_bf16_f32(128, n_eff);
-            const uint64_t a_desc = make_kmajor_sw128_desc(smem_u32(q_s + qslot * TC_TILE_BYTES));
-            const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(k_t));
-#pragma unroll
-            for (int k = 0; k < TC_D / 16; ++k)
-              tc_mma_f16(tmem_base + TC_S_COL, a_desc + 2 * k, b_desc + 2 * k, idesc, k != 0);
-            tc_commit(bar_s);
-            if (it == n_kv - 1) tc_commit(&q_empty[qslot]);  // last use of this Q tile
-          } else {
-            failed = true;
-          }
-        }
+        uint8_t* v_t = kv_s + kvstage * 2 * TC_TILE_BYTES + TC_TILE_BYTES;
         if (!failed && !mbar_wait(bar_s, gi & 1u)) failed = true;
         failed = __any_sync(0xffffffffu, failed);  // keep the warp-collective TMEM accesses below convergent
         tc_fence_after_sync();
@@ -284,6 +314,7 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
           }
           tc_commit(bar_o);
           tc_commit(&kv_empty[kvstage]);  // both MMAs of this tile have read the K/V stage
+          if (!issue_s()) failed = true;  // S of the next step queues up behind P V
         }
         if (!mbar_wait(bar_o, gi & 1u)) failed = true;
         failed = __any_sync(0xffffffffu, failed);
@@ -303,15 +334,8 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
                   __ffma2_rn(o_reg[(c + j) >> 1], alpha2, make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])));
           }
         }
-        if (++kvstage == TC_KVSTAGES) {
-          kvstage = 0;
-          kvphase ^= 1u;
-        }
+        if (++kvstage == TC_KVSTAGES) kvstage = 0;
         B2_PROF(7);  // O update
-      }
-      if (++qslot == TC_QSLOTS) {
-        qslot = 0;
-        qphase ^= 1u;
       }
       if (!failed && my_row < L) {
         const float inv = 1.f / l_run;
