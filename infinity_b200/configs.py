@@ -62,7 +62,7 @@ MOE_ENCODER = ModelSpec(name="moe-encoder-shape", arch="moe", n_layers=12, hidde
                         n_experts=8, top_k=2, moe_every=2, weight_format="mxfp8")
 QWEN2_7B = ModelSpec(name="qwen2-7b-shape", arch="decoder", n_layers=28, hidden=3584, n_heads=28, n_kv_heads=4,
                      head_dim=128, ffn=18944, vocab=151646, max_pos=2048, type_vocab=0, norm_eps=1e-6,
-                     rope_theta=1e6, pooling="last", max_len=2048)
+                     rope_theta=1e6, pooling="last", max_len=2048, weight_format="nvfp4")
 
 SPECS: Dict[str, ModelSpec] = {"c1": BGE_SMALL, "c2": BERT_LARGE, "c3": XLMR_LARGE_RERANK, "c4": MOE_ENCODER,
                                "c5": QWEN2_7B}

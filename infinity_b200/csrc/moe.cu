@@ -47,7 +47,9 @@ moe_router_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__
                   int n_tokens, int hidden, int n_experts, int top_k, int32_t* __restrict__ topk_idx,
                   float* __restrict__ topk_w, int32_t* __restrict__ counts) {
   extern __shared__ float wr_s[];  // [n_experts, hidden]
+  __shared__ int32_t cnt_s[MOE_MAX_E];  // tokens per expert seen by this CTA (one global atomic per expert at the end)
   for (int i = threadIdx.x; i < n_experts * hidden; i += blockDim.x) wr_s[i] = wr[i];
+  if (threadIdx.x < MOE_MAX_E) cnt_s[threadIdx.x] = 0;
   __syncthreads();
   const int lane = threadIdx.x & 31;
   const int n_chunks = hidden >> 3;
@@ -101,10 +103,12 @@ moe_router_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__
         taken |= 1u << best;
         topk_idx[static_cast<size_t>(t) * top_k + k] = best;
         topk_w[static_cast<size_t>(t) * top_k + k] = bv / den;
-        if (counts != nullptr) atomicAdd(counts + best, 1);
+        atomicAdd(&cnt_s[best], 1);
       }
     }
   }
+  __syncthreads();
+  if (counts != nullptr && threadIdx.x < n_experts && cnt_s[threadIdx.x] > 0) atomicAdd(counts + threadIdx.x, cnt_s[threadIdx.x]);
 }
 
 // counts[e] -> seg_off[e] (row offset of expert e's segment, multiples of 128), cursor[e] = seg_off[e],
@@ -137,16 +141,26 @@ moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restric
                    __nv_bfloat16* __restrict__ xperm) {
   const int lane = threadIdx.x & 31;
   const int warps_total = gridDim.x * MOE_WARPS;
-  for (int s = blockIdx.x * MOE_WARPS + (threadIdx.x >> 5); s < n_slots; s += warps_total) {
-    int row = 0;
-    if (lane == 0) {
-      row = atomicAdd(cursor + topk_idx[s], 1);
-      row_of[s] = row;
+  // a warp takes 32 consecutive (token, k) slots: lanes that chose the same expert reserve their rows
+  // with ONE atomic (the lowest such lane adds the group size), then the warp copies the 32 rows
+  for (int s0 = (blockIdx.x * MOE_WARPS + (threadIdx.x >> 5)) * 32; s0 < n_slots; s0 += warps_total * 32) {
+    const int s = s0 + lane;
+    const int e = s < n_slots ? topk_idx[s] : -1 - lane;  // distinct dummies for lanes past the end
+    const uint32_t peers = __match_any_sync(0xffffffffu, e);
+    const int leader = __ffs(peers) - 1;
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    int base = 0;
+    if (lane == leader && e >= 0) base = atomicAdd(cursor + e, __popc(peers));
+    base = __shfl_sync(0xffffffffu, base, leader);
+    const int my_row = base + rank;
+    if (s < n_slots) row_of[s] = my_row;
+    const int n_here = min(32, n_slots - s0);
+    for (int j = 0; j < n_here; ++j) {
+      const int row = __shfl_sync(0xffffffffu, my_row, j);
+      const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>((s0 + j) / top_k) * hidden);
+      uint4* dst = reinterpret_cast<uint4*>(xperm + static_cast<size_t>(row) * hidden);
+      for (int c = lane; c < (hidden >> 3); c += 32) dst[c] = src[c];
     }
-    row = __shfl_sync(0xffffffffu, row, 0);
-    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(s / top_k) * hidden);
-    uint4* dst = reinterpret_cast<uint4*>(xperm + static_cast<size_t>(row) * hidden);
-    for (int c = lane; c < (hidden >> 3); c += 32) dst[c] = src[c];
   }
 }
 
@@ -259,7 +273,7 @@ int launch_moe_scatter(const void* x, const int32_t* topk_idx, const int32_t* co
   if (n_tokens <= 0) return B200EMB_OK;
   const int max_blocks = moe_max_row_blocks(n_tokens, top_k, n_experts);
   moe_offsets_kernel<<<1, 256, 0, stream>>>(counts, n_experts, max_blocks, cursor, tile_expert);
-  moe_scatter_kernel<<<persistent_grid(n_tokens * top_k), MOE_WARPS * 32, 0, stream>>>(
+  moe_scatter_kernel<<<persistent_grid((n_tokens * top_k + 31) / 32), MOE_WARPS * 32, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), topk_idx, n_tokens * top_k, top_k, hidden, cursor, row_of,
       reinterpret_cast<__nv_bfloat16*>(xperm));
   cudaError_t e = cudaGetLastError();

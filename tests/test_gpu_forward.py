@@ -72,18 +72,20 @@ def test_tiny_decoder_matches_oracle(tmp_path, kw):
     model.close()
 
 
-def test_qwen2_7b_layer_shapes(tmp_path):
+@pytest.mark.parametrize("fmt,tol", [("bf16", COS_TOL), ("nvfp4", COS_TOL_BLOCK)])
+def test_qwen2_7b_layer_shapes(tmp_path, fmt, tol):
     """Two layers with the exact Qwen2-7B matrix shapes (hidden 3584, 28/4 heads of 128, FFN 18944)
-    and a reduced vocabulary: exercises the real GEMM / attention / SwiGLU tile shapes."""
+    and a reduced vocabulary: exercises the real GEMM / attention / SwiGLU tile shapes, with bf16
+    weights and with the configuration's NVFP4 weights."""
     from dataclasses import replace
-    spec = replace(cf.QWEN2_7B, n_layers=2, vocab=4096, name="qwen2-7b-2layer")
+    spec = replace(cf.QWEN2_7B, n_layers=2, vocab=4096, name="qwen2-7b-2layer", weight_format=fmt)
     model, W = build_model(tmp_path, spec, cf.SEEDS["c5"][2], perturb=False)
     batch = cf.random_batch(spec, [32, 700, 2048, 129, 1024, 63], 6)
     got = model.forward(batch)
     ref = _oracle_forward(spec, W, batch)
     cos = cosines(got, ref)
-    print("qwen2 shape cosine", cos)
-    assert cos.min() >= COS_TOL
+    print("qwen2 shape", fmt, "cosine", cos)
+    assert cos.min() >= tol
     model.close()
 
 
