@@ -54,56 +54,72 @@ moe_router_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__
   const int lane = threadIdx.x & 31;
   const int n_chunks = hidden >> 3;
   const int warps_total = gridDim.x * MOE_WARPS;
-  for (int t = blockIdx.x * MOE_WARPS + (threadIdx.x >> 5); t < n_tokens; t += warps_total) {
-    const __nv_bfloat16* xr = x + static_cast<size_t>(t) * hidden;
-    float acc[MOE_MAX_E];
+  constexpr int TPW = 4;  // tokens per warp step: every router-matrix chunk read from shared memory serves four tokens
+  for (int t0 = (blockIdx.x * MOE_WARPS + (threadIdx.x >> 5)) * TPW; t0 < n_tokens; t0 += warps_total * TPW) {
+    float acc[TPW][MOE_MAX_E];
 #pragma unroll
-    for (int e = 0; e < MOE_MAX_E; ++e) acc[e] = 0.f;
+    for (int j = 0; j < TPW; ++j)
+#pragma unroll
+      for (int e = 0; e < MOE_MAX_E; ++e) acc[j][e] = 0.f;
     for (int c = lane; c < n_chunks; c += 32) {
-      float v[8];
-      unpack8m(*reinterpret_cast<const uint4*>(xr + c * 8), v);
+      float v[TPW][8];
+#pragma unroll
+      for (int j = 0; j < TPW; ++j) {
+        const int t = min(t0 + j, n_tokens - 1);
+        unpack8m(*reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * hidden + c * 8), v[j]);
+      }
 #pragma unroll
       for (int e = 0; e < MOE_MAX_E; ++e) {
         if (e < n_experts) {
           const float4 w0 = *reinterpret_cast<const float4*>(wr_s + e * hidden + c * 8);
           const float4 w1 = *reinterpret_cast<const float4*>(wr_s + e * hidden + c * 8 + 4);
-          acc[e] += v[0] * w0.x + v[1] * w0.y + v[2] * w0.z + v[3] * w0.w + v[4] * w1.x + v[5] * w1.y + v[6] * w1.z +
-                    v[7] * w1.w;
+#pragma unroll
+          for (int j = 0; j < TPW; ++j)
+            acc[j][e] += v[j][0] * w0.x + v[j][1] * w0.y + v[j][2] * w0.z + v[j][3] * w0.w + v[j][4] * w1.x +
+                         v[j][5] * w1.y + v[j][6] * w1.z + v[j][7] * w1.w;
         }
       }
     }
 #pragma unroll
-    for (int e = 0; e < MOE_MAX_E; ++e)
-      if (e < n_experts) acc[e] = warp_sum_m(acc[e]);
-    if (lane == 0) {
-      float mx = -INFINITY;
+    for (int j = 0; j < TPW; ++j)
 #pragma unroll
       for (int e = 0; e < MOE_MAX_E; ++e)
-        if (e < n_experts) {
-          acc[e] += br != nullptr ? br[e] : 0.f;
-          mx = fmaxf(mx, acc[e]);
-        }
-      float den = 0.f;
+        if (e < n_experts) acc[j][e] = warp_sum_m(acc[j][e]);
+    // lane j finishes token t0 + j (softmax, top-k)
 #pragma unroll
-      for (int e = 0; e < MOE_MAX_E; ++e)
-        if (e < n_experts) {
-          acc[e] = expf(acc[e] - mx);
-          den += acc[e];
-        }
-      uint32_t taken = 0;
-      for (int k = 0; k < top_k; ++k) {
-        int best = -1;
-        float bv = -1.f;
+    for (int j = 0; j < TPW; ++j) {
+      if (lane == j && t0 + j < n_tokens) {
+        const int t = t0 + j;
+        float* a = acc[j];
+        float mx = -INFINITY;
 #pragma unroll
         for (int e = 0; e < MOE_MAX_E; ++e)
-          if (e < n_experts && !((taken >> e) & 1u) && acc[e] > bv) {  // strict >: a tie keeps the lower index
-            bv = acc[e];
-            best = e;
+          if (e < n_experts) {
+            a[e] += br != nullptr ? br[e] : 0.f;
+            mx = fmaxf(mx, a[e]);
           }
-        taken |= 1u << best;
-        topk_idx[static_cast<size_t>(t) * top_k + k] = best;
-        topk_w[static_cast<size_t>(t) * top_k + k] = bv / den;
-        atomicAdd(&cnt_s[best], 1);
+        float den = 0.f;
+#pragma unroll
+        for (int e = 0; e < MOE_MAX_E; ++e)
+          if (e < n_experts) {
+            a[e] = expf(a[e] - mx);
+            den += a[e];
+          }
+        uint32_t taken = 0;
+        for (int k = 0; k < top_k; ++k) {
+          int best = -1;
+          float bv = -1.f;
+#pragma unroll
+          for (int e = 0; e < MOE_MAX_E; ++e)
+            if (e < n_experts && !((taken >> e) & 1u) && a[e] > bv) {  // strict >: a tie keeps the lower index
+              bv = a[e];
+              best = e;
+            }
+          taken |= 1u << best;
+          topk_idx[static_cast<size_t>(t) * top_k + k] = best;
+          topk_w[static_cast<size_t>(t) * top_k + k] = bv / den;
+          atomicAdd(&cnt_s[best], 1);
+        }
       }
     }
   }
@@ -256,7 +272,7 @@ int launch_moe_router(const void* x, const float* wr, const float* br, int n_tok
     attr = true;
   }
   if (counts != nullptr) B2_CUDA_CHECK(cudaMemsetAsync(counts, 0, sizeof(int32_t) * n_experts, stream));
-  moe_router_kernel<<<persistent_grid(n_tokens), MOE_WARPS * 32, smem, stream>>>(
+  moe_router_kernel<<<persistent_grid((n_tokens + 3) / 4), MOE_WARPS * 32, smem, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), wr, br, n_tokens, hidden, n_experts, top_k, topk_idx, topk_w, counts);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "router launch: %s", cudaGetErrorString(e));

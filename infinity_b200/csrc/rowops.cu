@@ -84,6 +84,29 @@ __device__ __forceinline__ void layernorm_store(float (&v)[NCH][8], int lane, in
   }
 }
 
+// Plain row gather out[t,:] = table[ids[t],:] (decoder embedding lookup): persistent warps, four
+// 16-byte loads in flight per lane, nothing kept in registers.
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+gather_rows_kernel(const int32_t* __restrict__ ids, int n_tokens, const __nv_bfloat16* __restrict__ table, int hidden,
+                   __nv_bfloat16* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int n_chunks = hidden >> 3;
+  const int warps_total = gridDim.x * ROW_WARPS;
+  for (int t = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5); t < n_tokens; t += warps_total) {
+    const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<size_t>(__ldg(ids + t)) * hidden);
+    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * hidden);
+    for (int c = lane; c < n_chunks; c += 128) {
+      uint4 u[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (c + 32 * j < n_chunks) u[j] = __ldg(src + c + 32 * j);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (c + 32 * j < n_chunks) dst[c + 32 * j] = u[j];
+    }
+  }
+}
+
 template <int NCH>
 __global__ void __launch_bounds__(ROW_WARPS * 32)
 embed_ln_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ types, const int32_t* __restrict__ cu,
@@ -95,13 +118,16 @@ embed_ln_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ typ
   if (t >= n_tokens) return;
   const int lane = threadIdx.x & 31;
   const int n_chunks = hidden >> 3;
-  // sequence of token t: largest i with cu[i] <= t
-  int lo = 0, hi = n_seqs;
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (__ldg(cu + mid) <= t) lo = mid; else hi = mid;
+  // sequence of token t: largest i with cu[i] <= t (only needed for the position row)
+  int p = 0;
+  if (pos != nullptr) {
+    int lo = 0, hi = n_seqs;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (__ldg(cu + mid) <= t) lo = mid; else hi = mid;
+    }
+    p = pos_offset + t - __ldg(cu + lo);
   }
-  const int p = pos_offset + t - __ldg(cu + lo);
   const int id = __ldg(ids + t);
   const __nv_bfloat16* wrow = word + static_cast<size_t>(id) * hidden;
   const __nv_bfloat16* prow = pos != nullptr ? pos + static_cast<size_t>(p) * hidden : nullptr;
@@ -253,6 +279,65 @@ add_rmsnorm_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ y, c
   }
 }
 
+// Same step for wide rows (hidden > 2048): one CTA of 256 threads per row, at most two 16-byte
+// chunks per thread, so few registers and many rows in flight per SM; the sum of squares meets in
+// shared memory.
+static constexpr int RMS_BLOCK = 256;
+__global__ void __launch_bounds__(RMS_BLOCK)
+add_rmsnorm_wide_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ y, const float* __restrict__ gamma,
+                        int n_rows, int hidden, float eps, __nv_bfloat16* __restrict__ out) {
+  __shared__ float red[RMS_BLOCK / 32];
+  const int n_chunks = hidden >> 3;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {
+    float* hr = h + static_cast<size_t>(row) * hidden;
+    const __nv_bfloat16* yr = y != nullptr ? y + static_cast<size_t>(row) * hidden : nullptr;
+    float v[2][8];
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = threadIdx.x + RMS_BLOCK * i;
+      if (c < n_chunks) {
+        const float4 a0 = *reinterpret_cast<const float4*>(hr + c * 8);
+        const float4 a1 = *reinterpret_cast<const float4*>(hr + c * 8 + 4);
+        v[i][0] = a0.x; v[i][1] = a0.y; v[i][2] = a0.z; v[i][3] = a0.w;
+        v[i][4] = a1.x; v[i][5] = a1.y; v[i][6] = a1.z; v[i][7] = a1.w;
+        if (yr != nullptr) {
+          float b[8];
+          unpack8(*reinterpret_cast<const uint4*>(yr + c * 8), b);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[i][e] += b[e];
+          *reinterpret_cast<float4*>(hr + c * 8) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+          *reinterpret_cast<float4*>(hr + c * 8 + 4) = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sq += v[i][e] * v[i][e];
+      }
+    }
+    sq = warp_sum(sq);
+    __syncthreads();  // the previous row's readers of red[] are done
+    if (lane == 0) red[warp] = sq;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < RMS_BLOCK / 32; ++w) tot += red[w];  // same order in every thread: deterministic
+    const float rstd = rsqrtf(tot / hidden + eps);
+    __nv_bfloat16* dst = out + static_cast<size_t>(row) * hidden;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = threadIdx.x + RMS_BLOCK * i;
+      if (c < n_chunks) {
+        const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + c * 8));
+        const float4 g1 = __ldg(reinterpret_cast<const float4*>(gamma + c * 8 + 4));
+        float o[8];
+        o[0] = v[i][0] * rstd * g0.x; o[1] = v[i][1] * rstd * g0.y; o[2] = v[i][2] * rstd * g0.z; o[3] = v[i][3] * rstd * g0.w;
+        o[4] = v[i][4] * rstd * g1.x; o[5] = v[i][5] * rstd * g1.y; o[6] = v[i][6] * rstd * g1.z; o[7] = v[i][7] * rstd * g1.w;
+        *reinterpret_cast<uint4*>(dst + c * 8) = pack8(o);
+      }
+    }
+  }
+}
+
 // bf16 rows -> fp32 rows (starts the fp32 residual stream from the embedding gather).
 __global__ void widen_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, size_t n_chunks) {
   for (size_t c = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; c < n_chunks;
@@ -328,16 +413,27 @@ pool_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ cu,
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
   if (rg < row_groups) {
-    for (int r = r_begin + rg; r < r_end; r += row_groups) {
-      const __nv_bfloat16* xr = x + static_cast<size_t>(r) * hidden;
+    // four rows per step so that each thread keeps several loads in flight; rows are still added
+    // in ascending order, so the sum does not depend on the unrolling
+    for (int r = r_begin + rg; r < r_end; r += 4 * row_groups) {
 #pragma unroll
       for (int i = 0; i < POOL_MAXC; ++i) {
         const int c = cg + cols * i;
         if (c < n_chunks) {
-          float a[8];
-          unpack8(__ldg(reinterpret_cast<const uint4*>(xr + c * 8)), a);
+          uint4 u[4];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[i][e] += a[e];
+          for (int j = 0; j < 4; ++j) {
+            const int rr = r + j * row_groups;
+            u[j] = rr < r_end ? __ldg(reinterpret_cast<const uint4*>(x + static_cast<size_t>(rr) * hidden + c * 8))
+                              : make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float a[8];
+            unpack8(u[j], a);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[i][e] += a[e];
+          }
         }
       }
     }
@@ -432,6 +528,17 @@ int launch_embed_ln(const int32_t* ids, const int32_t* types, const int32_t* d_c
   if (n_tokens <= 0) return B200EMB_OK;
   int rc = check_hidden(hidden, 16);
   if (rc) return rc;
+  if (gamma == nullptr && pos == nullptr && type_table == nullptr) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int full = (n_tokens + ROW_WARPS - 1) / ROW_WARPS;
+    gather_rows_kernel<<<full < sms * 8 ? full : sms * 8, ROW_WARPS * 32, 0, stream>>>(
+        ids, n_tokens, reinterpret_cast<const __nv_bfloat16*>(word), hidden, reinterpret_cast<__nv_bfloat16*>(out));
+    cudaError_t eg = cudaGetLastError();
+    if (eg != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "gather launch: %s", cudaGetErrorString(eg));
+    return B200EMB_OK;
+  }
   const int nch = ((hidden >> 3) + 31) / 32;
   const int grid = (n_tokens + ROW_WARPS - 1) / ROW_WARPS;
   B2_DISPATCH_NCH(nch, (embed_ln_kernel<NCH><<<grid, ROW_WARPS * 32, 0, stream>>>(
@@ -473,6 +580,14 @@ int launch_add_rmsnorm(float* h, const void* y, const float* gamma, int n_rows, 
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (hidden > 2048) {
+    const int grid_w = n_rows < sms * 8 ? n_rows : sms * 8;
+    add_rmsnorm_wide_kernel<<<grid_w, RMS_BLOCK, 0, stream>>>(h, reinterpret_cast<const __nv_bfloat16*>(y), gamma, n_rows,
+                                                             hidden, eps, reinterpret_cast<__nv_bfloat16*>(out));
+    cudaError_t ew = cudaGetLastError();
+    if (ew != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "add_rmsnorm launch: %s", cudaGetErrorString(ew));
+    return B200EMB_OK;
+  }
   const int full = (n_rows + ROW_WARPS - 1) / ROW_WARPS;
   const int grid = full < sms * 4 ? full : sms * 4;
   const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
