@@ -192,6 +192,13 @@ int b200emb_device_count(void);
 int b200emb_op_gemm_bf16(const void* A, const void* W, const float* bias, void* C, int32_t M, int32_t N,
                          int32_t K, int32_t epilogue, void* stream);
 
+/* C[M,N] (bf16) = epilogue(mxfp8(A) * W^T + bias) on the block-scaled tensor-core path
+ * (tcgen05.mma kind::mxf8f6f4.block_scale): A [M,K] bf16 is quantised to MXFP8 on the fly (same rule
+ * as b200emb_op_quantize), W_q [N,K] e4m3 and W_scales [N, K/32] e8m0 come from b200emb_op_quantize.
+ * N and K multiples of 128; epilogue B200EMB_EPI_BIAS or B200EMB_EPI_BIAS_GELU. Synchronises the stream. */
+int b200emb_op_gemm_mxfp8(const void* A_bf16, const void* W_q, const void* W_scales, const float* bias, void* C,
+                          int32_t M, int32_t N, int32_t K, int32_t epilogue, void* stream);
+
 /* Variable-length attention over a packed qkv buffer [n_tokens, (n_heads + 2*n_kv_heads) * head_dim]
  * (all query heads, then all key heads, then all value heads), bf16.
  * out [n_tokens, n_heads * head_dim] bf16. h_cu_seqlens is the host copy used

@@ -42,6 +42,16 @@ int gemm_init_device();
 // TMA descriptor of a bf16 row-major [rows, cols] matrix: box [box_rows x 64 columns], 128-byte swizzle.
 int make_tmap_bf16_2d(::CUtensorMap_st* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 
+// ---- MXFP8 block-scaled GEMM (gemm_mxfp8.cu) ----
+// Aq / Wq: e4m3 [M, K] / [N (x n_experts), K]; sf*_atoms: e8m0 scales in 512-byte atoms (128 rows x 4 K-blocks).
+int launch_gemm_mxfp8(const void* Aq, const void* sfa_atoms, const void* Wq, const void* sfw_atoms, const float* bias,
+                      void* C, int M, int N, int K, int epi, int sm_count, int* err_flag, cudaStream_t stream,
+                      const int32_t* tile_expert = nullptr, int n_experts = 1);
+int gemm_mxfp8_init_device();
+size_t mxfp8_sf_atoms_bytes(int64_t rows, int64_t K);
+int launch_quant_act_mxfp8(const void* x, int64_t rows, int K, void* q, void* sf_atoms, cudaStream_t stream);
+int launch_sf_to_atoms(const void* scales, int64_t rows, int K, void* atoms, cudaStream_t stream);
+
 // ---- attention (attention.cu) ----
 struct AttnTile {
   int32_t seq_start;  // first token of the sequence

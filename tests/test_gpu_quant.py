@@ -96,3 +96,31 @@ def test_quantiser_rejects_bad_shapes(lib):
     assert lib.b200emb_op_quantize(w.data_ptr(), 4, 40, MXFP8, q.data_ptr(), q.data_ptr(), None, None) == -1
     assert "multiple of the block size" in _lib.last_error()
     assert lib.b200emb_op_quantize(w.data_ptr(), 4, 40, 9, q.data_ptr(), q.data_ptr(), None, None) == -1
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 256, 384), (1000, 768, 3072), (4099, 3072, 768)])
+@pytest.mark.parametrize("epi", ["bias", "gelu"])
+def test_gemm_mxfp8_block_scaled(lib, M, N, K, epi):
+    """The block-scaled tensor-core GEMM against fp32 matmul of the dequantised operands: the
+    activation is quantised on the fly with the same rule as the numpy statement, so the only
+    differences are fp32 summation order and the bf16 rounding of the output."""
+    import math
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = (torch.randn(M, K, generator=g, device="cuda") * torch.exp(torch.randn(M, 1, generator=g, device="cuda"))).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g, device="cuda") / math.sqrt(K)).to(torch.bfloat16)
+    bias = torch.randn(N, generator=g, device="cuda") * 0.3
+    wq = torch.zeros(N, K, dtype=torch.uint8, device="cuda")
+    ws = torch.zeros(N, K // 32, dtype=torch.uint8, device="cuda")
+    _lib.check(lib.b200emb_op_quantize(w.data_ptr(), N, K, MXFP8, wq.data_ptr(), ws.data_ptr(), None, None))
+    c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()
+    _lib.check(lib.b200emb_op_gemm_mxfp8(a.data_ptr(), wq.data_ptr(), ws.data_ptr(), bias.data_ptr(), c.data_ptr(), M, N, K,
+                                         _lib.EPI[epi], None))
+    a_dq = torch.from_numpy(Q.dequantize_mxfp8(*Q.quantize_mxfp8(a.float().cpu().numpy()))).cuda()
+    w_dq = torch.from_numpy(Q.dequantize_mxfp8(wq.cpu().numpy(), ws.cpu().numpy())).cuda()
+    ref = a_dq @ w_dq.t() + bias
+    if epi == "gelu":
+        ref = torch.nn.functional.gelu(ref)
+    err = (c.float() - ref).abs().max().item()
+    tol = 2.0 ** -8 * max(1.0, ref.abs().max().item()) + 2e-3
+    assert err <= tol, (err, tol)
