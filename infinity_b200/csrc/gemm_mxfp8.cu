@@ -94,6 +94,11 @@ __device__ __forceinline__ float2 f8_gelu2(float2 x) {
   const float2 phi = __fadd2_rn(make_float2(0.5f, 0.5f), make_float2(copysignf(r.x, x.x), copysignf(r.y, x.y)));
   return __fmul2_rn(x, phi);
 }
+__device__ __forceinline__ size_t sf_atom_offset(size_t row, int kblock, int k_groups) {
+  // atom (row / 128, kblock / 4) of 512 bytes; inside: (row % 32) * 16 + ((row % 128) / 32) * 4 + kblock % 4
+  return ((row >> 7) * k_groups + (kblock >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (kblock & 3);
+}
+
 template <int EPI>
 __device__ __forceinline__ uint32_t f8_pack2(float a, float b) {
   float2 v = make_float2(a, b);
@@ -102,12 +107,15 @@ __device__ __forceinline__ uint32_t f8_pack2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&p);
 }
 
-template <int EPI>
+// OUT_FP8: the result is written as MXFP8 as well (e4m3 bytes through tmap_c, which then describes a
+// byte matrix, plus e8m0 scales into out_sf_atoms in atom layout), ready to be the next GEMM's A operand.
+template <int EPI, bool OUT_FP8>
 __global__ void __launch_bounds__(F8_THREADS, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                   const __grid_constant__ CUtensorMap tmap_c, const uint8_t* __restrict__ sfa_atoms,
                   const uint8_t* __restrict__ sfw_atoms, const float* __restrict__ bias, int M, int N, int K,
-                  const int32_t* __restrict__ tile_expert, int* __restrict__ err_flag) {
+                  const int32_t* __restrict__ tile_expert, uint8_t* __restrict__ out_sf_atoms,
+                  int* __restrict__ err_flag) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* a_tiles = smem;
@@ -277,6 +285,43 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         if (store_thread) tma_store_wait_read();
         named_barrier_sync(2 + grp, 128);
         const float* bsub = bias_s + grp * 64;
+        if constexpr (OUT_FP8) {
+          // this thread's 64 columns = two 32-element blocks of its row: one e8m0 scale each
+          uint8_t* rowp = cbuf + row_in_tile * 64;  // un-swizzled 64-byte rows
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk) {
+            float v[32];
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              float2 t = make_float2(__uint_as_float(blk == 0 ? r0[e] : r1[e]) + bsub[blk * 32 + e],
+                                     __uint_as_float(blk == 0 ? r0[e + 1] : r1[e + 1]) + bsub[blk * 32 + e + 1]);
+              if (EPI == EPI_BIAS_GELU) t = f8_gelu2(t);
+              v[e] = t.x;
+              v[e + 1] = t.y;
+            }
+            float amax = 0.f;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) amax = fmaxf(amax, fabsf(v[e]));
+            int ex = -127;
+            if (amax > 0.f) {
+              ex = ilogbf(amax) - 8;
+              ex = ex < -127 ? -127 : (ex > 127 ? 127 : ex);
+            }
+            const float inv = ex == -127 ? 0.f : exp2f(static_cast<float>(-ex));
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[i * 4] * inv, v[i * 4 + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+              const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[i * 4 + 2] * inv, v[i * 4 + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+              w[i] = (lo & 0xffffu) | ((hi & 0xffffu) << 16);
+            }
+            *reinterpret_cast<uint4*>(rowp + blk * 32) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4*>(rowp + blk * 32 + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+            const size_t grow = static_cast<size_t>(m0 + row_in_tile);
+            const int kblock = ((n0 + grp * 64) >> 5) + blk;
+            out_sf_atoms[sf_atom_offset(grow, kblock, N >> 7)] = static_cast<uint8_t>(ex + 127);
+          }
+        } else {
         uint8_t* rowp = cbuf + row_in_tile * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
@@ -289,6 +334,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           packed.z = f8_pack2<EPI>(v[4], v[5]);
           packed.w = f8_pack2<EPI>(v[6], v[7]);
           *reinterpret_cast<uint4*>(rowp + ((c ^ (row_in_tile & 7)) << 4)) = packed;
+        }
         }
         fence_proxy_async_smem();
         named_barrier_sync(2 + grp, 128);
@@ -312,10 +358,6 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
 // ---- activation quantiser and scale-factor repacking ---------------------------------------------
 
-__device__ __forceinline__ size_t sf_atom_offset(size_t row, int kblock, int k_groups) {
-  // atom (row / 128, kblock / 4) of 512 bytes; inside: (row % 32) * 16 + ((row % 128) / 32) * 4 + kblock % 4
-  return ((row >> 7) * k_groups + (kblock >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (kblock & 3);
-}
 
 // x bf16 [rows, K] -> e4m3 [rows, K] + e8m0 scales in atom layout (same rule as the weight quantiser)
 __global__ void __launch_bounds__(256)
@@ -406,7 +448,8 @@ typedef CUresult (*EncodeTiledFn8)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-static int make_tmap_u8_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols) {
+static int make_tmap_u8_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols = 128,
+                           bool swizzle = true) {
   static EncodeTiledFn8 fn = nullptr;
   if (fn == nullptr) {
     void* p = nullptr;
@@ -418,24 +461,27 @@ static int make_tmap_u8_2d(CUtensorMap* out, const void* base, uint64_t rows, ui
   if (fn == nullptr) return set_error(B200EMB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {cols};
-  cuuint32_t box[2] = {128, 128};
+  cuuint32_t box[2] = {box_cols, 128};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return set_error(B200EMB_ERR_CUDA, "cuTensorMapEncodeTiled (u8) failed (%d)", (int)r);
   return B200EMB_OK;
 }
 
 int gemm_mxfp8_init_device() {
-  B2_CUDA_CHECK(cudaFuncSetAttribute(gemm_mxfp8_kernel<EPI_BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM_BYTES));
-  B2_CUDA_CHECK(cudaFuncSetAttribute(gemm_mxfp8_kernel<EPI_BIAS_GELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM_BYTES));
+  B2_CUDA_CHECK(cudaFuncSetAttribute(gemm_mxfp8_kernel<EPI_BIAS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM_BYTES));
+  B2_CUDA_CHECK(cudaFuncSetAttribute(gemm_mxfp8_kernel<EPI_BIAS_GELU, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM_BYTES));
+  B2_CUDA_CHECK(cudaFuncSetAttribute(gemm_mxfp8_kernel<EPI_BIAS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM_BYTES));
+  B2_CUDA_CHECK(cudaFuncSetAttribute(gemm_mxfp8_kernel<EPI_BIAS_GELU, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, F8_SMEM_BYTES));
   return B200EMB_OK;
 }
 
 int launch_gemm_mxfp8(const void* Aq, const void* sfa_atoms, const void* Wq, const void* sfw_atoms, const float* bias,
                       void* C, int M, int N, int K, int epi, int sm_count, int* err_flag, cudaStream_t stream,
-                      const int32_t* tile_expert, int n_experts) {
+                      const int32_t* tile_expert, int n_experts, void* out_sf_atoms) {
   if (M <= 0) return B200EMB_OK;
   if (N <= 0 || K <= 0 || (K % 128) != 0 || (N % 8) != 0)
     return set_error(B200EMB_ERR_INVALID, "mxfp8 gemm: need K %% 128 == 0 and N %% 8 == 0 (N=%d K=%d)", N, K);
@@ -449,16 +495,23 @@ int launch_gemm_mxfp8(const void* Aq, const void* sfa_atoms, const void* Wq, con
   if (rc) return rc;
   rc = make_tmap_u8_2d(&tw, Wq, (uint64_t)N * (tile_expert != nullptr ? n_experts : 1), (uint64_t)K);
   if (rc) return rc;
-  rc = make_tmap_bf16_2d(&tc, C, (uint64_t)M, (uint64_t)N, 128);
+  const bool out_fp8 = out_sf_atoms != nullptr;
+  if (out_fp8 && (N % 128) != 0) return set_error(B200EMB_ERR_INVALID, "mxfp8 gemm: MXFP8 output needs N %% 128 == 0");
+  rc = out_fp8 ? make_tmap_u8_2d(&tc, C, (uint64_t)M, (uint64_t)N, 64, false) : make_tmap_bf16_2d(&tc, C, (uint64_t)M, (uint64_t)N, 128);
   if (rc) return rc;
   const int tiles = ((M + F8_BM - 1) / F8_BM) * ((N + F8_BN - 1) / F8_BN);
   const int grid = tiles < sm_count ? tiles : sm_count;
   const uint8_t* sa = reinterpret_cast<const uint8_t*>(sfa_atoms);
   const uint8_t* sw = reinterpret_cast<const uint8_t*>(sfw_atoms);
-  if (epi == EPI_BIAS_GELU)
-    gemm_mxfp8_kernel<EPI_BIAS_GELU><<<grid, F8_THREADS, F8_SMEM_BYTES, stream>>>(ta, tw, tc, sa, sw, bias, M, N, K, tile_expert, err_flag);
+  uint8_t* osf = reinterpret_cast<uint8_t*>(out_sf_atoms);
+  if (epi == EPI_BIAS_GELU && out_fp8)
+    gemm_mxfp8_kernel<EPI_BIAS_GELU, true><<<grid, F8_THREADS, F8_SMEM_BYTES, stream>>>(ta, tw, tc, sa, sw, bias, M, N, K, tile_expert, osf, err_flag);
+  else if (epi == EPI_BIAS_GELU)
+    gemm_mxfp8_kernel<EPI_BIAS_GELU, false><<<grid, F8_THREADS, F8_SMEM_BYTES, stream>>>(ta, tw, tc, sa, sw, bias, M, N, K, tile_expert, osf, err_flag);
+  else if (out_fp8)
+    gemm_mxfp8_kernel<EPI_BIAS, true><<<grid, F8_THREADS, F8_SMEM_BYTES, stream>>>(ta, tw, tc, sa, sw, bias, M, N, K, tile_expert, osf, err_flag);
   else
-    gemm_mxfp8_kernel<EPI_BIAS><<<grid, F8_THREADS, F8_SMEM_BYTES, stream>>>(ta, tw, tc, sa, sw, bias, M, N, K, tile_expert, err_flag);
+    gemm_mxfp8_kernel<EPI_BIAS, false><<<grid, F8_THREADS, F8_SMEM_BYTES, stream>>>(ta, tw, tc, sa, sw, bias, M, N, K, tile_expert, osf, err_flag);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "mxfp8 gemm launch: %s", cudaGetErrorString(e));
   return B200EMB_OK;

@@ -46,7 +46,8 @@ int make_tmap_bf16_2d(::CUtensorMap_st* out, const void* base, uint64_t rows, ui
 // Aq / Wq: e4m3 [M, K] / [N (x n_experts), K]; sf*_atoms: e8m0 scales in 512-byte atoms (128 rows x 4 K-blocks).
 int launch_gemm_mxfp8(const void* Aq, const void* sfa_atoms, const void* Wq, const void* sfw_atoms, const float* bias,
                       void* C, int M, int N, int K, int epi, int sm_count, int* err_flag, cudaStream_t stream,
-                      const int32_t* tile_expert = nullptr, int n_experts = 1);
+                      const int32_t* tile_expert = nullptr, int n_experts = 1, void* out_sf_atoms = nullptr);
+// out_sf_atoms != null: C is written as MXFP8 (e4m3 bytes [M, N] + scales in atom layout) instead of bf16
 int gemm_mxfp8_init_device();
 size_t mxfp8_sf_atoms_bytes(int64_t rows, int64_t K);
 int launch_quant_act_mxfp8(const void* x, int64_t rows, int K, void* q, void* sf_atoms, cudaStream_t stream);
@@ -89,7 +90,7 @@ int launch_moe_router(const void* x, const float* wr, const float* br, int n_tok
 int moe_max_row_blocks(int n_tokens, int top_k, int n_experts);
 int launch_moe_scatter(const void* x, const int32_t* topk_idx, const int32_t* counts, int n_tokens, int top_k,
                        int hidden, int n_experts, int32_t* cursor, int32_t* tile_expert, int32_t* row_of, void* xperm,
-                       cudaStream_t stream);
+                       cudaStream_t stream, void* xq = nullptr, void* sf_atoms = nullptr);  // xq != null: write MXFP8 instead of bf16
 int launch_moe_combine_ln(const void* x, const void* yperm, const int32_t* row_of, const float* topk_w, int top_k,
                           const float* gamma, const float* beta, int n_tokens, int hidden, float eps, void* out,
                           cudaStream_t stream);

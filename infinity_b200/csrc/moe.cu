@@ -9,6 +9,7 @@
 // The slot a token gets inside its expert's segment depends on atomics and may differ from run
 // to run; results do not, because every GEMM row is computed independently of its position.
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -180,6 +181,66 @@ moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restric
   }
 }
 
+// Scatter that quantises on the way: the expert-contiguous copy is written as MXFP8 (e4m3 bytes +
+// e8m0 scales in the 512-byte atoms the block-scaled GEMM reads), so the expert GEMM needs no
+// separate activation-quantisation pass. Lane b of the warp owns 32-element block b of the row.
+__global__ void __launch_bounds__(MOE_WARPS * 32)
+moe_scatter_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ topk_idx, int n_slots,
+                         int top_k, int hidden, int32_t* __restrict__ cursor, int32_t* __restrict__ row_of,
+                         uint8_t* __restrict__ xq, uint8_t* __restrict__ sf_atoms) {
+  const int lane = threadIdx.x & 31;
+  const int warps_total = gridDim.x * MOE_WARPS;
+  const int kblocks = hidden >> 5, kgroups = hidden >> 7;
+  for (int s0 = (blockIdx.x * MOE_WARPS + (threadIdx.x >> 5)) * 32; s0 < n_slots; s0 += warps_total * 32) {
+    const int s = s0 + lane;
+    const int e = s < n_slots ? topk_idx[s] : -1 - lane;
+    const uint32_t peers = __match_any_sync(0xffffffffu, e);
+    const int leader = __ffs(peers) - 1;
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    int base = 0;
+    if (lane == leader && e >= 0) base = atomicAdd(cursor + e, __popc(peers));
+    base = __shfl_sync(0xffffffffu, base, leader);
+    const int my_row = base + rank;
+    if (s < n_slots) row_of[s] = my_row;
+    const int n_here = min(32, n_slots - s0);
+    for (int j = 0; j < n_here; ++j) {
+      const size_t row = static_cast<size_t>(__shfl_sync(0xffffffffu, my_row, j));
+      const __nv_bfloat16* src = x + static_cast<size_t>((s0 + j) / top_k) * hidden;
+      for (int b = lane; b < kblocks; b += 32) {
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) unpack8m(*reinterpret_cast<const uint4*>(src + b * 32 + i * 8), reinterpret_cast<float(&)[8]>(v[i * 8]));
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        int ex = -127;
+        if (amax > 0.f) {
+          ex = ilogbf(amax) - 8;
+          ex = ex < -127 ? -127 : (ex > 127 ? 127 : ex);
+        }
+        const float inv = ex == -127 ? 0.f : exp2f(static_cast<float>(-ex));
+        uint32_t out[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          uint32_t word = 0;
+#pragma unroll
+          for (int k = 0; k < 4; k += 2) {
+            const uint32_t two = __nv_cvt_float2_to_fp8x2(make_float2(v[i * 4 + k] * inv, v[i * 4 + k + 1] * inv),
+                                                          __NV_SATFINITE, __NV_E4M3);
+            word |= (two & 0xffffu) << (8 * k);
+          }
+          out[i] = word;
+        }
+        uint4* dst = reinterpret_cast<uint4*>(xq + row * hidden + b * 32);
+        dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
+        dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
+        sf_atoms[((row >> 7) * kgroups + (b >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (b & 3)] =
+            static_cast<uint8_t>(ex + 127);
+      }
+    }
+  }
+}
+
 template <int NCH>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_combine_ln_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ yperm,
@@ -285,10 +346,16 @@ int moe_max_row_blocks(int n_tokens, int top_k, int n_experts) {
 
 int launch_moe_scatter(const void* x, const int32_t* topk_idx, const int32_t* counts, int n_tokens, int top_k,
                        int hidden, int n_experts, int32_t* cursor, int32_t* tile_expert, int32_t* row_of, void* xperm,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, void* xq, void* sf_atoms) {
   if (n_tokens <= 0) return B200EMB_OK;
   const int max_blocks = moe_max_row_blocks(n_tokens, top_k, n_experts);
   moe_offsets_kernel<<<1, 256, 0, stream>>>(counts, n_experts, max_blocks, cursor, tile_expert);
+  if (xq != nullptr) {
+    if (hidden % 128) return set_error(B200EMB_ERR_INVALID, "moe scatter (mxfp8): hidden %d not a multiple of 128", hidden);
+    moe_scatter_mxfp8_kernel<<<persistent_grid((n_tokens * top_k + 31) / 32), MOE_WARPS * 32, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x), topk_idx, n_tokens * top_k, top_k, hidden, cursor, row_of,
+        reinterpret_cast<uint8_t*>(xq), reinterpret_cast<uint8_t*>(sf_atoms));
+  } else
   moe_scatter_kernel<<<persistent_grid((n_tokens * top_k + 31) / 32), MOE_WARPS * 32, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), topk_idx, n_tokens * top_k, top_k, hidden, cursor, row_of,
       reinterpret_cast<__nv_bfloat16*>(xperm));

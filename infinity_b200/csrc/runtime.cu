@@ -159,6 +159,8 @@ struct DeviceCtx {
   // MXFP8 block-scaled GEMMs: the activation operand quantised on the fly
   uint8_t *act_q = nullptr, *act_sf = nullptr;
   size_t act_q_bytes = 0, act_sf_bytes = 0;
+  uint8_t *act2_q = nullptr, *act2_sf = nullptr;  // second operand buffer (expert hidden activations)
+  size_t act2_q_bytes = 0, act2_sf_bytes = 0;
   std::vector<uint8_t*> owned_atoms;
   float* hres = nullptr;     // decoder: fp32 residual stream [T, H]
   float* rope_cs = nullptr;  // decoder: (cos, sin) table [max_pos, head_dim / 2]
@@ -422,7 +424,7 @@ static void destroy_ctx(DeviceCtx* c) {
   cudaFree(c->d_ids); cudaFree(c->d_types); cudaFree(c->d_cu); cudaFree(c->d_tiles);
   cudaFree(c->x); cudaFree(c->x2); cudaFree(c->qkv); cudaFree(c->ctx); cudaFree(c->y); cudaFree(c->ffn);
   cudaFree(c->pooled); cudaFree(c->head_h); cudaFree(c->d_out); cudaFree(c->d_err);
-  cudaFree(c->hres); cudaFree(c->rope_cs); cudaFree(c->wscratch); cudaFree(c->act_q); cudaFree(c->act_sf);
+  cudaFree(c->hres); cudaFree(c->rope_cs); cudaFree(c->wscratch); cudaFree(c->act_q); cudaFree(c->act_sf); cudaFree(c->act2_q); cudaFree(c->act2_sf);
   for (uint8_t* p : c->owned_atoms) cudaFree(p);
   cudaFree(c->topk_idx); cudaFree(c->row_of); cudaFree(c->moe_counts); cudaFree(c->moe_cursor); cudaFree(c->tile_expert);
   cudaFree(c->topk_w); cudaFree(c->xperm); cudaFree(c->hperm); cudaFree(c->yperm);
@@ -510,6 +512,16 @@ static int quantize_activation(DeviceCtx* c, const void* A, int rows_padded, int
   }
   KernelScope ks(c, B200EMB_KCLASS_OTHER);
   return launch_quant_act_mxfp8(A, rows_padded, K, c->act_q, c->act_sf, c->stream);
+}
+
+static int grow_bytes(uint8_t** p, size_t* have, size_t want, bool zero) {
+  if (want <= *have) return B200EMB_OK;
+  cudaFree(*p);
+  *p = nullptr;
+  B2_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(p), want));
+  if (zero) B2_CUDA_CHECK(cudaMemset(*p, 0, want));
+  *have = want;
+  return B200EMB_OK;
 }
 
 static bool use_block_scaled(int wfmt, const Mat& W, int epi) {
@@ -653,6 +665,42 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
         rc = launch_moe_router(c->x2, L.router_w, L.router_b, T, H, d.n_experts, d.top_k, c->topk_idx, c->topk_w,
                                c->moe_counts, c->stream);
         if (rc) return rc;
+      }
+      if (use_block_scaled(d.weight_format, L.ffn1_w, EPI_BIAS_GELU) && use_block_scaled(d.weight_format, L.ffn2_w, EPI_BIAS) &&
+          H % 128 == 0 && F % 128 == 0) {
+        // MXFP8 experts on the block-scaled tensor-core path, activations in MXFP8 end to end: the scatter
+        // writes e4m3 + scales, GEMM 1 (GELU) writes its output as MXFP8 again, GEMM 2 returns bf16.
+        rc = grow_bytes(&c->act_q, &c->act_q_bytes, (size_t)Mp * H, false);
+        if (!rc) rc = grow_bytes(&c->act_sf, &c->act_sf_bytes, mxfp8_sf_atoms_bytes(Mp, H), true);
+        if (!rc) rc = grow_bytes(&c->act2_q, &c->act2_q_bytes, (size_t)Mp * F, false);
+        if (!rc) rc = grow_bytes(&c->act2_sf, &c->act2_sf_bytes, mxfp8_sf_atoms_bytes(Mp, F), true);
+        if (rc) return rc;
+        {
+          KernelScope ks(c, B200EMB_KCLASS_OTHER);
+          c->launches++;
+          rc = launch_moe_scatter(c->x2, c->topk_idx, c->moe_counts, T, d.top_k, H, d.n_experts, c->moe_cursor,
+                                  c->tile_expert, c->row_of, nullptr, c->stream, c->act_q, c->act_sf);
+          if (rc) return rc;
+        }
+        {
+          KernelScope ks(c, B200EMB_KCLASS_GEMM);
+          c->gemm_flops += 2.0 * T * d.top_k * (double)F * H;
+          rc = launch_gemm_mxfp8(c->act_q, c->act_sf, L.ffn1_w.q, L.ffn1_w.sf_atoms, L.ffn1_b, c->act2_q, Mp, F, H,
+                                 EPI_BIAS_GELU, c->sm_count, c->d_err, c->stream, c->tile_expert, d.n_experts, c->act2_sf);
+          if (rc) return rc;
+        }
+        {
+          KernelScope ks(c, B200EMB_KCLASS_GEMM);
+          c->gemm_flops += 2.0 * T * d.top_k * (double)F * H;
+          rc = launch_gemm_mxfp8(c->act2_q, c->act2_sf, L.ffn2_w.q, L.ffn2_w.sf_atoms, L.ffn2_b, c->yperm, Mp, H, F,
+                                 EPI_BIAS, c->sm_count, c->d_err, c->stream, c->tile_expert, d.n_experts);
+          if (rc) return rc;
+        }
+        KernelScope ks(c, B200EMB_KCLASS_NORM);
+        rc = launch_moe_combine_ln(c->x2, c->yperm, c->row_of, c->topk_w, d.top_k, L.ln2_g, L.ln2_b, T, H, d.norm_eps,
+                                   c->x, c->stream);
+        if (rc) return rc;
+        continue;
       }
       {
         KernelScope ks(c, B200EMB_KCLASS_OTHER);
