@@ -264,10 +264,14 @@ def run_ours(args):
         step_host()
     barrier()
     t0 = time.perf_counter()
+    step_ms = []
     for _ in range(args.steps):
+        t1 = time.perf_counter()
         step_host()
+        step_ms.append((time.perf_counter() - t1) * 1e3)
     barrier()
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)
+    p50_ms = max_over_ranks(statistics.median(step_ms))
     e2e_value = total_tokens * args.steps / (e2e_ms / 1e3)
     n_tiles = int(sum((int(L) + 63) // 64 for L in batch.lengths))
     h2d_bytes = 4 * (batch.n_tokens + batch.n_seqs + 1) + 16 * n_tiles
@@ -304,6 +308,7 @@ def run_ours(args):
             },
             "kernel_class_ms_per_step": {k: v / args.steps for k, v in kclass.items()},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
+                    "batch_latency_p50_ms": p50_ms,
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
             "gpu_launches": launches_all,
             "clocks": clocks,
