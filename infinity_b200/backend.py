@@ -40,7 +40,10 @@ class _B200Backend:
         loudly when the CUDA library or a GPU is missing."""
         self.engine_args = engine_args
         self.spec = spec
-        self.tokenizer = tokenizer if tokenizer is not None else IdStringTokenizer(spec.max_len)
+        if tokenizer is None:
+            limit = spec.max_len if spec.arch == "decoder" else min(spec.max_len, spec.max_pos - spec.pos_offset)
+            tokenizer = IdStringTokenizer(limit)
+        self.tokenizer = tokenizer
         self.model = model if model is not None else B200Model(spec, weight_path, device_ids)
         # Results travel through two bounded queues (depth 3 and 5, batch_handler.py:499-500)
         # before the batcher hands rows out, so up to ~9 batches are alive per replica:

@@ -1,0 +1,73 @@
+"""The reference-interface backends (encode_pre -> encode_core -> encode_post) on the real CUDA
+model, with id-string sentences standing in for tokenised text."""
+import numpy as np
+import pytest
+
+from helpers import cosines
+from infinity_b200 import configs as cf
+from infinity_b200 import weights as wt
+from infinity_b200.backend import B200Classifier, B200CrossEncoder, B200Embedder
+from infinity_b200.packing import IdStringTokenizer
+from oracle import encoder as enc
+
+pytestmark = pytest.mark.gpu
+
+
+def _weights(tmp_path, spec, seed):
+    master = cf.init_weights(spec, seed, perturb=True)
+    path = tmp_path / f"{spec.name}.b2ew"
+    wt.save_weights(path, cf.runtime_tensors(master))
+    return str(path), cf.oracle_tensors(spec, master)
+
+
+def _sentence(rng, n, vocab):
+    return " ".join(str(int(x)) for x in rng.integers(3, vocab, size=n))
+
+
+def test_embedder_backend_pipeline(tmp_path):
+    spec = cf.tiny_spec("bert")
+    path, W = _weights(tmp_path, spec, 51)
+    backend = B200Embedder(spec=spec, weight_path=path, device_ids=(0,))
+    rng = np.random.default_rng(0)
+    sentences = [_sentence(rng, n, spec.vocab) for n in (5, 90, 17, 160, 1)]
+    assert backend.tokenize_lengths(sentences) == [5, 90, 17, 160, 1]
+    feats = backend.encode_pre(sentences)
+    out = backend.encode_post(backend.encode_core(feats))
+    assert out.shape == (5, spec.hidden) and out.dtype == np.float32
+    ref = enc.forward_batch(spec, W, cf.pack([np.array(s.split(), dtype=np.int64) for s in sentences]))
+    assert cosines(out, ref).min() >= 0.9999
+    # the ring hands out distinct buffers for consecutive batches (results stay valid while queued)
+    again = backend.encode_core(feats)
+    assert again.ctypes.data != out.ctypes.data and np.array_equal(again, out)
+    eps, secs, log = backend.warmup(batch_size=8, n_tokens=64)
+    assert eps > 0 and "ms inference" in log
+    backend.model.close()
+
+
+def test_cross_encoder_and_classifier_backends(tmp_path):
+    spec = cf.tiny_spec("xlmr")
+    path, W = _weights(tmp_path, spec, 52)
+    ce = B200CrossEncoder(spec=spec, weight_path=path, device_ids=(0,),
+                          tokenizer=IdStringTokenizer(spec.max_pos - spec.pos_offset))
+    rng = np.random.default_rng(1)
+    pairs = [(_sentence(rng, q, spec.vocab), _sentence(rng, d, spec.vocab)) for q, d in ((4, 30), (10, 120), (3, 3), (60, 200))]
+    feats = ce.encode_pre(pairs)
+    assert feats.n_seqs == 4 and int(np.diff(feats.cu_seqlens).max()) <= spec.max_pos - spec.pos_offset
+    logits = ce.encode_post(ce.encode_core(feats))
+    assert logits.shape == (4,) and logits.dtype == np.float32
+    ref = enc.forward_batch(spec, W, cf.Batch(feats.input_ids, feats.cu_seqlens))
+    assert np.abs(logits - ref[:, 0]).max() <= 1e-2
+    ce.model.close()
+
+    spec3 = cf.tiny_spec("xlmr", n_labels=3)
+    path3, W3 = _weights(tmp_path, spec3, 53)
+    clf = B200Classifier(spec=spec3, weight_path=path3, device_ids=(0,), labels=["neg", "neu", "pos"])
+    sentences = [_sentence(rng, n, spec3.vocab) for n in (7, 50)]
+    res = clf.encode_post(clf.encode_core(clf.encode_pre(sentences)))
+    ref3 = enc.forward_batch(spec3, W3, cf.pack([np.array(s.split(), dtype=np.int64) for s in sentences]))
+    z = np.exp(ref3 - ref3.max(1, keepdims=True))
+    probs = z / z.sum(1, keepdims=True)
+    for row, p in zip(res, probs):
+        assert [d["label"] for d in row] == [["neg", "neu", "pos"][j] for j in np.argsort(-p)]
+        assert abs(row[0]["score"] - p.max()) < 1e-2
+    clf.model.close()
