@@ -179,6 +179,12 @@ const char* b200emb_last_error(void);
 /* Number of CUDA devices visible, or a negative status. */
 int b200emb_device_count(void);
 
+/* Failure-detection self-test: launches one thread that waits on a barrier nothing signals, with
+ * the same bounded wait the pipelined kernels use but a limit of limit_ms. Expected result:
+ * B200EMB_ERR_DEVICE_WAIT after about limit_ms, with the context still usable. No GPU fault,
+ * trap or endless loop is involved. */
+int b200emb_selftest_bounded_wait(int32_t limit_ms);
+
 /* ---- single kernels on device buffers (used by the parity tests) -------------
  * Pointers are DEVICE pointers on the current device; `stream` is a
  * cudaStream_t (NULL = default stream). The calls are asynchronous on that

@@ -96,6 +96,7 @@ int launch_moe_combine_ln(const void* x, const void* yperm, const int32_t* row_o
                           cudaStream_t stream);
 
 // ---- row kernels (rowops.cu) ----
+int launch_wait_selftest(unsigned long long limit_ns, int* err_flag, cudaStream_t stream);
 int launch_embed_ln(const int32_t* ids, const int32_t* types, const int32_t* d_cu, int n_seqs, int n_tokens,
                     const void* word, const void* pos, const void* type_table, const float* gamma, const float* beta,
                     int hidden, int pos_offset, float eps, void* out, cudaStream_t stream);

@@ -68,14 +68,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, ui
 }
 // Bounded wait. Returns false when the phase did not complete within
 // WAIT_LIMIT_NS; the caller records the failure and leaves its loop.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns = WAIT_LIMIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   uint32_t polls = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++polls & 0x3fu) == 0u) {
-      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) return false;
+      if (globaltimer_ns() - t0 > limit_ns) return false;
     }
   }
 }

@@ -10,8 +10,28 @@
 #include <stdint.h>
 
 #include "kernels.h"
+#include "ptx.cuh"
 
 namespace b2 {
+
+// Self-test of the bounded-wait mechanism every pipelined kernel relies on: one thread waits on an
+// mbarrier that nothing ever signals. The wait must give up after limit_ns, record a code in the
+// error word and let the kernel end normally, leaving the context usable.
+__global__ void wait_selftest_kernel(unsigned long long limit_ns, int* err_flag) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+    if (!mbar_wait(&bar, 0, limit_ns)) atomicExch(err_flag, 9);
+  }
+}
+
+int launch_wait_selftest(unsigned long long limit_ns, int* err_flag, cudaStream_t stream) {
+  wait_selftest_kernel<<<1, 32, 0, stream>>>(limit_ns, err_flag);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "wait self-test launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
 
 static constexpr int ROW_WARPS = 8;  // rows per CTA
 

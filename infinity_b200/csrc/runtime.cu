@@ -1297,6 +1297,20 @@ int b200emb_op_gemm_bf16(const void* A, const void* W, const float* bias, void* 
   return B200EMB_OK;
 }
 
+int b200emb_selftest_bounded_wait(int32_t limit_ms) {
+  if (limit_ms <= 0 || limit_ms > 5000) return set_error(B200EMB_ERR_INVALID, "selftest: limit must be in (0, 5000] ms");
+  int* d_err = nullptr;
+  int rc = op_error_word(&d_err);
+  if (rc) return rc;
+  rc = launch_wait_selftest(static_cast<unsigned long long>(limit_ms) * 1000000ull, d_err, nullptr);
+  if (rc) return rc;
+  int herr = 0;
+  B2_CUDA_CHECK(cudaMemcpy(&herr, d_err, sizeof(int), cudaMemcpyDeviceToHost));
+  B2_CUDA_CHECK(cudaMemset(d_err, 0, sizeof(int)));
+  if (herr != 0) return set_error(B200EMB_ERR_DEVICE_WAIT, "self-test: the device-side wait gave up as intended (code %d)", herr);
+  return B200EMB_OK;
+}
+
 int b200emb_op_gemm_mxfp8(const void* A_bf16, const void* W_q, const void* W_scales, const float* bias, void* C,
                           int32_t M, int32_t N, int32_t K, int32_t epilogue, void* stream) {
   if (A_bf16 == nullptr || W_q == nullptr || W_scales == nullptr || C == nullptr)

@@ -7,6 +7,8 @@ device buffers whose raw pointers cross the C ABI; no torch operator runs on the
 from __future__ import annotations
 
 import ctypes as C
+import os
+import sys
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
@@ -55,6 +57,23 @@ class B200Model:
                                             C.byref(self._handle)))
         self.device_ids = list(device_ids)
         self.last_timing: Optional[Dict] = None
+        # per-replica counters (the reference exposes only wall-clock warm-up numbers and queue
+        # statistics: abstract.py:228-250, infinity_server.py:189-214); B200EMB_TRACE=1 prints one line per call
+        self.stats: Dict[str, float] = {"calls": 0, "sequences": 0, "tokens": 0, "total_ms": 0.0, "kernels_ms": 0.0,
+                                        "h2d_ms": 0.0, "d2h_ms": 0.0, "launches": 0}
+        self._trace = os.environ.get("B200EMB_TRACE", "0") not in ("", "0")
+
+    def _account(self, n_seqs: int, n_tokens: int) -> None:
+        t = self.last_timing
+        st = self.stats
+        st["calls"] += 1
+        st["sequences"] += n_seqs
+        st["tokens"] += n_tokens
+        for k in ("total_ms", "kernels_ms", "h2d_ms", "d2h_ms", "launches"):
+            st[k] += t[k]
+        if self._trace:
+            print(f"[b200emb] {n_seqs} seqs {n_tokens} tokens: h2d {t['h2d_ms']:.3f} ms, kernels {t['kernels_ms']:.3f} ms "
+                  f"({t['launches']} launches), d2h {t['d2h_ms']:.3f} ms, total {t['total_ms']:.3f} ms", file=sys.stderr)
 
     def close(self) -> None:
         if getattr(self, "_handle", None) is not None and self._handle.value:
@@ -85,6 +104,7 @@ class B200Model:
             self._handle, ids.ctypes.data, None if tt is None else tt.ctypes.data, cu.ctypes.data, n_seqs, n_tokens,
             out.ctypes.data, self.spec.out_dim, C.byref(timing)))
         self.last_timing = timing_dict(timing)
+        self._account(n_seqs, n_tokens)
         return out
 
     def forward(self, batch: Batch, **kw) -> np.ndarray:

@@ -41,6 +41,8 @@ def test_embedder_backend_pipeline(tmp_path):
     assert again.ctypes.data != out.ctypes.data and np.array_equal(again, out)
     eps, secs, log = backend.warmup(batch_size=8, n_tokens=64)
     assert eps > 0 and "ms inference" in log
+    st = backend.model.stats
+    assert st["calls"] == 3 and st["sequences"] == 5 + 5 + 8 and st["tokens"] == 2 * 273 + 8 * 64 and st["launches"] > 0
     backend.model.close()
 
 

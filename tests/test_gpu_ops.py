@@ -232,3 +232,17 @@ def test_moe_router_matches_numpy(lib, T, H, E, k):
     np.testing.assert_allclose(gate.cpu().numpy()[ok], ref_gate[ok], rtol=2e-5, atol=1e-7)
     assert counts.sum().item() == T * k
     assert np.array_equal(np.bincount(got_idx.ravel(), minlength=E), counts.cpu().numpy())
+
+
+def test_bounded_wait_gives_up_and_context_survives(lib):
+    """Failure detection without a fault: a wait on a barrier nothing signals runs into its limit,
+    the host sees B200EMB_ERR_DEVICE_WAIT, and the next kernel on the same context works."""
+    import time
+    t0 = time.perf_counter()
+    st = lib.b200emb_selftest_bounded_wait(300)
+    dt = time.perf_counter() - t0
+    assert st == 2 and "gave up" in _lib.last_error()
+    assert 0.25 < dt < 3.0, dt
+    a = torch.randn(256, 128, device="cuda").to(torch.bfloat16)
+    w = torch.eye(128, device="cuda").to(torch.bfloat16)
+    assert torch.equal(_gemm(lib, a, w, None, "bias"), a)
