@@ -53,8 +53,24 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // One probe of the barrier. The hardware may park the thread for up to `suspend_ns` while the
 // phase is pending (it resumes as soon as the phase completes), which keeps waiting warps from
 // burning issue slots that co-resident warps need.
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t suspend_ns = 1000) {
+#ifndef B2_MBAR_SUSPEND_NS
+#define B2_MBAR_SUSPEND_NS 1000
+#endif
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t suspend_ns = B2_MBAR_SUSPEND_NS) {
   uint32_t ok;
+#if B2_MBAR_SUSPEND_NS == 0
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  (void)suspend_ns;
+  return ok != 0;
+#endif
   asm volatile(
       "{\n"
       " .reg .pred p;\n"

@@ -177,3 +177,38 @@ def test_rerank_through_the_reference_batch_handler(reference):
     assert [r.index for r in results] == [1, 0, 2]
     for r in results:
         assert abs(r.relevance_score - want[r.index]) < 1e-6
+
+
+def test_engine_api_with_patched_select_model(reference):
+    """The reference's public engine API (AsyncEmbeddingEngine.embed / rerank) with our backend
+    returned by a patched ``select_model`` (engine.py:56-58 looks the name up at call time): the
+    drop-in route that needs no edit of the reference tree."""
+    import infinity_emb.engine as engine_mod
+    from infinity_emb.args import EngineArgs
+
+    spec = cf.tiny_spec("bert")
+    made = {}
+
+    def fake_select_model(engine_args):
+        backend = B200Embedder(engine_args=engine_args, spec=spec, model=FakeDeviceModel(spec.hidden))
+        made["backend"] = backend
+        return [backend], 0.0, 0.0
+
+    original = engine_mod.select_model
+    engine_mod.select_model = fake_select_model
+    try:
+        args = EngineArgs(model_name_or_path="b200/tiny", engine="debugengine", batch_size=8, model_warmup=False,
+                          lengths_via_tokenize=True)
+        eng = engine_mod.AsyncEmbeddingEngine.from_args(args)
+
+        async def run():
+            async with eng:
+                return await eng.embed(sentences=["1 2 3", "4 5 6 7 8", "9"])
+
+        embeddings, usage = asyncio.run(run())
+    finally:
+        engine_mod.select_model = original
+    assert usage == 9
+    assert [int(e[0]) for e in embeddings] == [3, 5, 1]
+    assert [int(e[1]) for e in embeddings] == [6, 30, 9]
+    assert made["backend"].engine_args.model_name_or_path == "b200/tiny" and made["backend"].engine_args.batch_size == 8
