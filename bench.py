@@ -316,6 +316,8 @@ def run_ours(args):
         }
         print(json.dumps(line), flush=True)
     model.close()
+    import shutil
+    shutil.rmtree(tmpdir, ignore_errors=True)
     if world > 1:
         dist.destroy_process_group()
 
