@@ -149,16 +149,26 @@ attn_varlen_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restr
     // mask (sequence end, causal diagonal) and online softmax
     const int key0 = it * ATT_BKV + 2 * tq;
     float mx[2] = {-INFINITY, -INFINITY};
+    // only the last key tile (sequence end) and, for causal attention, the tile on the diagonal need a mask
+    const bool needs_mask = (it + 1) * ATT_BKV > L || (CAUSAL && (it + 1) * ATT_BKV > q0 + warp * 16 + 1);
+    if (needs_mask) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 8; ++j) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = key0 + 8 * j + (e & 1);
-        const int qr = qrow0 + (e >> 1) * 8;
-        const bool keep = key < L && (!CAUSAL || key <= qr);
-        const float v = keep ? s[j][e] : -INFINITY;
-        s[j][e] = v;
-        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        for (int e = 0; e < 4; ++e) {
+          const int key = key0 + 8 * j + (e & 1);
+          const int qr = qrow0 + (e >> 1) * 8;
+          const bool keep = key < L && (!CAUSAL || key <= qr);
+          const float v = keep ? s[j][e] : -INFINITY;
+          s[j][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
       }
     }
     float corr[2], m_use[2];

@@ -84,6 +84,7 @@ int launch_dequantize(const void* q, const void* scales, int64_t rows, int64_t c
                       cudaStream_t stream);
 
 // ---- mixture of experts (moe.cu) ----
+int moe_init_device();
 int launch_moe_router(const void* x, const float* wr, const float* br, int n_tokens, int hidden, int n_experts,
                       int top_k, int32_t* topk_idx, float* topk_w, int32_t* counts, cudaStream_t stream);
 // upper bound of 128-row blocks of the expert-contiguous layout (segments padded to 128 rows)

@@ -311,6 +311,11 @@ moe_combine_ln_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
   }
 }
 
+int moe_init_device() {
+  B2_CUDA_CHECK(cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+  return B200EMB_OK;
+}
+
 static int persistent_grid(int n_rows) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -327,11 +332,6 @@ int launch_moe_router(const void* x, const float* wr, const float* br, int n_tok
   if (hidden % 8) return set_error(B200EMB_ERR_UNSUPPORTED, "router: hidden %d not a multiple of 8", hidden);
   const size_t smem = static_cast<size_t>(n_experts) * hidden * sizeof(float);
   if (smem > 96 * 1024) return set_error(B200EMB_ERR_UNSUPPORTED, "router: n_experts * hidden too large for shared memory");
-  static bool attr = false;
-  if (!attr || smem > 48 * 1024) {
-    cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-    attr = true;
-  }
   if (counts != nullptr) B2_CUDA_CHECK(cudaMemsetAsync(counts, 0, sizeof(int32_t) * n_experts, stream));
   moe_router_kernel<<<persistent_grid((n_tokens + 3) / 4), MOE_WARPS * 32, smem, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), wr, br, n_tokens, hidden, n_experts, top_k, topk_idx, topk_w, counts);
@@ -396,6 +396,8 @@ extern "C" int b200emb_op_moe_router(const void* x, const float* router_w, const
                                      float* topk_weight, int32_t* counts, void* stream) {
   if (x == nullptr || router_w == nullptr || topk_idx == nullptr || topk_weight == nullptr)
     return set_error(B200EMB_ERR_INVALID, "moe_router: null pointer");
+  int rc = kernels_init_device();
+  if (rc) return rc;
   return launch_moe_router(x, router_w, router_b, n_tokens, hidden, n_experts, top_k, topk_idx, topk_weight, counts,
                            reinterpret_cast<cudaStream_t>(stream));
 }

@@ -44,6 +44,7 @@ int kernels_init_device() {
   if (!rc) rc = attention_init_device();
   if (!rc) rc = attention_tc_init_device();
   if (!rc) rc = gemm_mxfp8_init_device();
+  if (!rc) rc = moe_init_device();
   if (rc) return rc;
   if (dev >= 0 && dev < 64) g_dev_inited[dev] = true;
   return B200EMB_OK;
