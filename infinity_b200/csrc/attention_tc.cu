@@ -1,17 +1,24 @@
 // Variable-length bidirectional attention on the 5th-generation tensor cores (head_dim 64).
 //
-// One CTA = one 128-row query tile of one (sequence, head); tiles never cross a sequence
+// One work item = one 128-row query tile of one (sequence, head); tiles never cross a sequence
 // boundary. Q, K and V tiles (128 rows x 64, 128-byte swizzle) arrive by TMA straight from the
 // packed qkv buffer. Per 128-key tile:
 //   S = Q K^T      tcgen05.mma 128 x N x 16 (N = valid keys rounded up to 16), fp32 in TMEM
-//   softmax        128 threads, one TMEM lane (= one query row) each: two passes over the row
-//                  (max, then exp2 / sum), no cross-thread reduction; P is rounded to bf16 and
-//                  written back to tensor memory (two keys per 32-bit column)
-//   O_tile = P V   tcgen05.mma with the A operand read from tensor memory and V as an MN-major
-//                  shared-memory operand (no transpose of V anywhere)
-//   O = O * alpha + O_tile in registers (online softmax; nothing to rescale in TMEM)
+//   softmax        128 threads, one TMEM lane (= one query row) each, ONE pass over the row in
+//                  32-key chunks whose loads run one chunk ahead of the math: p = exp2(s - m_ref)
+//                  against a per-row reference point that is the maximum of the row's first 32 keys
+//                  and is moved (with a second pass and a rescale of O) only when a later score
+//                  exceeds it by more than 2^10; no cross-thread reduction; P is rounded to bf16
+//                  and written back to tensor memory (two keys per 32-bit column)
+//   O += P V       tcgen05.mma with the A operand read from tensor memory and V as an MN-major
+//                  shared-memory operand (no transpose of V anywhere); O accumulates in tensor
+//                  memory across the key tiles and is read once per query tile
+// Warp roles: 0-3 softmax, 4 TMA producer (Q, K and V double-buffered), 5 MMA
+// issuer. The issuer runs warp-uniform code with only the tcgen05 instructions under elect.sync, so
+// descriptors live in uniform registers: an MMA issued from divergent single-thread code costs about
+// 90 cycles of operand moves, more than the 32-64 cycles these small MMAs take to execute.
 // The kernel is persistent, two CTAs per SM (256 of the 512 TMEM columns each), so one CTA's
-// softmax overlaps the other's MMAs; a producer warp keeps the next tiles' Q / K / V in flight.
+// softmax overlaps the other's MMAs.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -26,20 +33,33 @@ static constexpr int TC_BKV = 128;
 static constexpr int TC_D = 64;
 static constexpr int TC_TILE_BYTES = 128 * TC_D * 2;  // 16 KB
 static constexpr int TC_QSLOTS = 2;
-static constexpr int TC_KVSTAGES = 2;
-static constexpr int TC_SMEM_BYTES = (TC_QSLOTS + 2 * TC_KVSTAGES) * TC_TILE_BYTES + 128 + 1024;
-static constexpr int TC_THREADS = 160;         // 4 softmax warps + 1 TMA producer warp
+static constexpr int TC_KSLOTS = 2;
+static constexpr int TC_VSLOTS = 2;
+static constexpr int TC_N_TILES = TC_QSLOTS + TC_KSLOTS + TC_VSLOTS;
+static constexpr int TC_BAR_BYTES = 160;
+// two CTAs per SM: each may use half of the SM's 228 KB less the 1 KB the system reserves per CTA;
+// the tiles need 1024-byte alignment, which the start of dynamic shared memory has when the kernel
+// declares no static shared memory (checked at run time, reported through the error flag)
+static constexpr int TC_SMEM_BYTES = TC_N_TILES * TC_TILE_BYTES + 1024;
+static constexpr int TC_THREADS = 192;         // 4 softmax warps + TMA producer warp + MMA warp
 static constexpr uint32_t TC_TMEM_COLS = 256;  // S 128 | P 64 | O 64
 static constexpr uint32_t TC_S_COL = 0, TC_P_COL = 128, TC_O_COL = 192;
+static constexpr float TC_LAZY_LOG2 = 10.f;  // how far (log2 units) a score may exceed the row's reference point
 
 #ifdef B2_ATT_PROFILE
 // Phase timing of CTA 0 / thread 0 (development aid; not part of normal builds).
 __device__ long long g_att_prof[16];
-#define B2_PROF_DECL long long prof_t0 = clock64(); const bool prof_on = (blockIdx.x == 0 && threadIdx.x == 0);
-#define B2_PROF(slot) do { if (prof_on) { const long long n__ = clock64(); g_att_prof[slot] += n__ - prof_t0; prof_t0 = n__; } } while (0)
+#define B2_PROF_DECL_T(tid) unsigned prof_acc[10] = {}; unsigned prof_t0 = (unsigned)clock(); const bool prof_on = (blockIdx.x == 0 && threadIdx.x == (tid));
+#define B2_PROF_DECL B2_PROF_DECL_T(0)
+#define B2_PROF(slot) do { if (prof_on) { const unsigned n__ = (unsigned)clock(); prof_acc[slot] += n__ - prof_t0; prof_t0 = n__; } } while (0)
+#define B2_PROF_FLUSH do { if (prof_on) { for (int i__ = 0; i__ < 10; ++i__) g_att_prof[i__] += prof_acc[i__]; } } while (0)
+#define B2_PROF_FLUSH_HI do { if (prof_on) { for (int i__ = 0; i__ < 6; ++i__) g_att_prof[10 + i__] += prof_acc[i__]; } } while (0)
 #else
 #define B2_PROF_DECL
+#define B2_PROF_DECL_T(tid)
 #define B2_PROF(slot) do { } while (0)
+#define B2_PROF_FLUSH do { } while (0)
+#define B2_PROF_FLUSH_HI do { } while (0)
 #endif
 
 __device__ __forceinline__ float max3f(float a, float b, float c) {
@@ -53,46 +73,53 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
-// Position of the MMA issuer in the CTA's sequence of (item, key tile) steps.
-struct StepCursor {
-  int item, it, n_kv, seq_len;
-  int qslot, kvstage;
-  uint32_t qphase, kvphase;
-};
-
 // Persistent: CTA b serves work items b, b + gridDim.x, ...; item i = (query tile i / n_heads,
-// head i % n_heads). Warp 4 runs ahead with the TMA loads (Q double-buffered, K/V through a
-// two-stage ring, slots released by tcgen05.commit), so launch, allocation and load latency
-// are paid once per CTA, not once per tile.
+// head i % n_heads). Every role walks the same sequence of (item, key tile) steps.
 __global__ void __launch_bounds__(TC_THREADS, 2)
 attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __restrict__ out,
                    const AttnTile* __restrict__ tiles, int n_items, int n_heads, int n_kv_heads, float scale_log2,
                    int* __restrict__ err_flag) {
   extern __shared__ uint8_t att_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(att_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* q_s = smem;                                // [TC_QSLOTS]
-  uint8_t* kv_s = smem + TC_QSLOTS * TC_TILE_BYTES;   // [TC_KVSTAGES] x (K tile, V tile)
-  uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + (TC_QSLOTS + 2 * TC_KVSTAGES) * TC_TILE_BYTES);
+  uint8_t* q_s = smem;
+  uint8_t* k_s = q_s + TC_QSLOTS * TC_TILE_BYTES;
+  uint8_t* v_s = k_s + TC_KSLOTS * TC_TILE_BYTES;
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(v_s + TC_VSLOTS * TC_TILE_BYTES);
   uint64_t* q_empty = q_full + TC_QSLOTS;
-  uint64_t* kv_full = q_empty + TC_QSLOTS;
-  uint64_t* kv_empty = kv_full + TC_KVSTAGES;
-  uint64_t* bar_s = kv_empty + TC_KVSTAGES;
-  uint64_t* bar_o = bar_s + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o + 1);
+  uint64_t* k_full = q_empty + TC_QSLOTS;
+  uint64_t* k_empty = k_full + TC_KSLOTS;
+  uint64_t* v_full = k_empty + TC_KSLOTS;
+  uint64_t* v_empty = v_full + TC_VSLOTS;
+  uint64_t* bar_s = v_empty + TC_VSLOTS;  // S of a step is in tensor memory
+  uint64_t* bar_p = bar_s + 1;            // all 128 softmax threads have written P of a step
+  uint64_t* bar_pv = bar_p + 1;           // P V of a step has finished: P may be overwritten, O may be read
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_pv + 1);
+  static_assert((2 * TC_QSLOTS + 2 * TC_KSLOTS + 2 * TC_VSLOTS + 3) * 8 + 4 <= TC_BAR_BYTES, "barrier area");
+  // shared memory too small once aligned: report and leave before anything is initialised (uniform per CTA)
+  if (smem + TC_N_TILES * TC_TILE_BYTES + TC_BAR_BYTES > att_raw + TC_SMEM_BYTES) {
+    if (threadIdx.x == 0) atomicExch(err_flag, 6);
+    return;
+  }
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // warp-uniform in the compiler's view too
+  const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < TC_QSLOTS; ++i) {
       mbar_init(&q_full[i], 1);
-      mbar_init(&q_empty[i], 1);
+      mbar_init(&q_empty[i], 4);  // one arrival per softmax warp, after it staged its output rows there
     }
-    for (int i = 0; i < TC_KVSTAGES; ++i) {
-      mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+    for (int i = 0; i < TC_KSLOTS; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+    }
+    for (int i = 0; i < TC_VSLOTS; ++i) {
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
     }
     mbar_init(bar_s, 1);
-    mbar_init(bar_o, 1);
+    mbar_init(bar_p, 128);
+    mbar_init(bar_pv, 1);
     fence_mbar_init();
   }
   if (warp == 0) {
@@ -108,9 +135,9 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       tma_prefetch_desc(&tmap_qkv);
-      int qslot = 0, kvstage = 0;
-      uint32_t qphase = 0, kvphase = 0;
-      uint32_t q_fills = 0, kv_fills = 0;
+      int qslot = 0, kslot = 0, vslot = 0;
+      uint32_t qphase = 0, kphase = 0, vphase = 0;
+      uint32_t q_fills = 0, k_fills = 0, v_fills = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
         const AttnTile t = tiles[item / n_heads];
@@ -129,146 +156,190 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
           qphase ^= 1u;
         }
         for (int it = 0; it < n_kv; ++it) {
-          if (!mbar_wait(&kv_empty[kvstage], kvphase ^ 1u)) {
+          if (!mbar_wait(&k_empty[kslot], kphase ^ 1u)) {
             ok = false;
             break;
           }
-          uint8_t* kdst = kv_s + kvstage * 2 * TC_TILE_BYTES;
-          mbar_arrive_expect_tx(&kv_full[kvstage], 2 * TC_TILE_BYTES);
-          tma_load_2d(kdst, &tmap_qkv, &kv_full[kvstage], (n_heads + hk) * TC_D, t.seq_start + it * TC_BKV);
-          tma_load_2d(kdst + TC_TILE_BYTES, &tmap_qkv, &kv_full[kvstage], (n_heads + n_kv_heads + hk) * TC_D,
+          mbar_arrive_expect_tx(&k_full[kslot], TC_TILE_BYTES);
+          tma_load_2d(k_s + kslot * TC_TILE_BYTES, &tmap_qkv, &k_full[kslot], (n_heads + hk) * TC_D,
                       t.seq_start + it * TC_BKV);
-          ++kv_fills;
-          if (++kvstage == TC_KVSTAGES) {
-            kvstage = 0;
-            kvphase ^= 1u;
+          ++k_fills;
+          if (++kslot == TC_KSLOTS) {
+            kslot = 0;
+            kphase ^= 1u;
+          }
+          if (!mbar_wait(&v_empty[vslot], vphase ^ 1u)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&v_full[vslot], TC_TILE_BYTES);
+          tma_load_2d(v_s + vslot * TC_TILE_BYTES, &tmap_qkv, &v_full[vslot], (n_heads + n_kv_heads + hk) * TC_D,
+                      t.seq_start + it * TC_BKV);
+          ++v_fills;
+          if (++vslot == TC_VSLOTS) {
+            vslot = 0;
+            vphase ^= 1u;
           }
         }
       }
       if (!ok) {
         atomicExch(err_flag, 5);
         // let the copies still in flight land before shared memory is released (bounded)
-        for (uint32_t i = 0; i < (q_fills < TC_QSLOTS ? q_fills : (uint32_t)TC_QSLOTS); ++i) {
-          const uint32_t idx = q_fills - 1 - i;
-          mbar_wait(&q_full[idx % TC_QSLOTS], (idx / TC_QSLOTS) & 1u);
-        }
-        for (uint32_t i = 0; i < (kv_fills < TC_KVSTAGES ? kv_fills : (uint32_t)TC_KVSTAGES); ++i) {
-          const uint32_t idx = kv_fills - 1 - i;
-          mbar_wait(&kv_full[idx % TC_KVSTAGES], (idx / TC_KVSTAGES) & 1u);
-        }
+        auto drain = [](uint64_t* full, uint32_t fills, uint32_t slots) {
+          for (uint32_t i = 0; i < (fills < slots ? fills : slots); ++i) {
+            const uint32_t idx = fills - 1 - i;
+            mbar_wait(&full[idx % slots], (idx / slots) & 1u);
+          }
+        };
+        drain(q_full, q_fills, TC_QSLOTS);
+        drain(k_full, k_fills, TC_KSLOTS);
+        drain(v_full, v_fills, TC_VSLOTS);
       }
     }
-  } else {
-    // ---------------- softmax warps (thread 0 also issues the MMAs) ----------------
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    int kvstage = 0;
-    uint32_t gi = 0;  // KV tiles processed so far by this CTA: phase of bar_s / bar_o
-    bool failed = false;
-
-    // Thread 0 issues S = Q K^T one step AHEAD of the softmax: S of step k+1 is issued together with
-    // P V of step k (the S columns are free once every thread has read them in pass 2), so its
-    // round trip hides behind the P V wait and the O update.
-    StepCursor cur;
-    cur.item = blockIdx.x;
-    cur.it = 0;
-    cur.n_kv = 0;
-    cur.seq_len = 0;
-    cur.qslot = cur.kvstage = 0;
-    cur.qphase = cur.kvphase = 0;
+  } else if (warp == 5) {
+    // ---------------- MMA issuer: all 32 lanes walk the loops, one elected lane issues ----------------
+    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+    const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
+    // S = Q K^T runs one step AHEAD of the softmax: S of step n + 1 is issued as soon as every softmax
+    // thread has arrived on bar_p for step n (the S columns are free then), in front of P V of step n.
+    int s_item = blockIdx.x, s_it = 0, s_nkv = 0, s_len = 0;
+    int qslot = 0, kslot = 0, vslot = 0;
+    uint32_t qphase = 0, kphase = 0, vphase = 0;
+    bool ok = true;
+    B2_PROF_DECL_T(160)
+    // every lane waits; the warp agrees on the outcome so that it never splits around elect.sync
+    auto wait_all = [](uint64_t* bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbar_wait(bar, parity)); };
     auto issue_s = [&]() -> bool {  // false when a wait gave up
-      if (cur.item >= n_items) return true;
-      if (cur.it == 0) {
-        const AttnTile tt = tiles[cur.item / n_heads];
-        cur.seq_len = tt.seq_len;
-        cur.n_kv = (tt.seq_len + TC_BKV - 1) / TC_BKV;
-        if (!mbar_wait(&q_full[cur.qslot], cur.qphase)) return false;
+      if (s_item >= n_items) return true;
+      if (s_it == 0) {
+        s_len = __shfl_sync(0xffffffffu, tiles[s_item / n_heads].seq_len, 0);
+        s_nkv = (s_len + TC_BKV - 1) / TC_BKV;
+        if (!wait_all(&q_full[qslot], qphase)) return false;
       }
-      if (!mbar_wait(&kv_full[cur.kvstage], cur.kvphase)) return false;
+      if (!wait_all(&k_full[kslot], kphase)) return false;
       tc_fence_after_sync();
-      const int nv = min(TC_BKV, cur.seq_len - cur.it * TC_BKV);
+      B2_PROF(3);  // Q / K waits
+      const int nv = min(TC_BKV, s_len - s_it * TC_BKV);
       const uint32_t idesc = make_idesc_bf16_f32(128, (nv + 15) & ~15);
-      const uint64_t a_desc = make_kmajor_sw128_desc(smem_u32(q_s + cur.qslot * TC_TILE_BYTES));
-      const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(kv_s + cur.kvstage * 2 * TC_TILE_BYTES));
+      const uint64_t a_desc = make_kmajor_sw128_desc(q_addr + qslot * TC_TILE_BYTES);
+      const uint64_t b_desc = make_kmajor_sw128_desc(k_addr + kslot * TC_TILE_BYTES);
 #pragma unroll
       for (int k = 0; k < TC_D / 16; ++k)
-        tc_mma_f16(tmem_base + TC_S_COL, a_desc + 2 * k, b_desc + 2 * k, idesc, k != 0);
-      tc_commit(bar_s);
-      if (cur.it == cur.n_kv - 1) tc_commit(&q_empty[cur.qslot]);  // last use of this Q tile
-      if (++cur.kvstage == TC_KVSTAGES) {
-        cur.kvstage = 0;
-        cur.kvphase ^= 1u;
+        if (elect_one()) tc_mma_f16(tmem_u + TC_S_COL, a_desc + 2 * k, b_desc + 2 * k, idesc, k != 0);
+      if (elect_one()) {
+        tc_commit(bar_s);
+        tc_commit(&k_empty[kslot]);
       }
-      if (++cur.it == cur.n_kv) {
-        cur.it = 0;
-        cur.item += gridDim.x;
-        if (++cur.qslot == TC_QSLOTS) {
-          cur.qslot = 0;
-          cur.qphase ^= 1u;
+      B2_PROF(4);  // S issue
+      if (++kslot == TC_KSLOTS) {
+        kslot = 0;
+        kphase ^= 1u;
+      }
+      if (++s_it == s_nkv) {
+        s_it = 0;
+        s_item += gridDim.x;
+        if (++qslot == TC_QSLOTS) {
+          qslot = 0;
+          qphase ^= 1u;
         }
       }
       return true;
     };
-    if (threadIdx.x == 0 && !issue_s()) failed = true;
+    ok = issue_s();
+    uint32_t gi = 0;
+    const uint32_t idesc_pv = make_idesc_bf16_f32_b_mn(128, TC_D);
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const int L = __shfl_sync(0xffffffffu, tiles[item / n_heads].seq_len, 0);
+      const int n_kv = (L + TC_BKV - 1) / TC_BKV;
+      for (int it = 0; it < n_kv; ++it, ++gi) {
+        const int n_eff = (min(TC_BKV, L - it * TC_BKV) + 15) & ~15;
+        if (!wait_all(bar_p, gi & 1u)) {
+          ok = false;
+          break;
+        }
+        B2_PROF(0);  // wait for P
+        // S of the next step first: it only needs the S columns, which bar_p has just released, and lets
+        // the next softmax start while P V of this step executes. The softmax threads hold back their
+        // first P store of the next step until bar_pv says that P V has read this step's P.
+        if (!issue_s()) {
+          ok = false;
+          break;
+        }
+        if (!wait_all(&v_full[vslot], vphase)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        B2_PROF(1);  // wait for V
+        const uint64_t v_desc = make_mnmajor_sw128_desc(v_addr + vslot * TC_TILE_BYTES, 16);
+        // 16 keys = two 8-row groups of the MN-major V tile = 2048 bytes (128 in descriptor units); 16 keys
+        // of P = 8 columns
+#pragma unroll
+        for (int k = 0; k < TC_BKV / 16; ++k)
+          if (k * 16 < n_eff && elect_one())
+            tc_mma_f16_tmem_a(tmem_u + TC_O_COL, tmem_u + TC_P_COL + k * 8, v_desc + k * 128, idesc_pv, (it | k) != 0);
+        if (elect_one()) {
+          tc_commit(bar_pv);
+          tc_commit(&v_empty[vslot]);
+        }
+        B2_PROF(2);  // P V issue
+        if (++vslot == TC_VSLOTS) {
+          vslot = 0;
+          vphase ^= 1u;
+        }
+      }
+    }
+    B2_PROF_FLUSH_HI;
+    if (!ok && lane == 0) atomicExch(err_flag, 7);
+  } else {
+    // ---------------- softmax warps ----------------
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    uint32_t gi = 0;      // key tiles processed so far by this CTA: phase of bar_s
+    int oslot = 0;        // Q slot of the current work item (reused to stage its output rows)
+    // A warp whose wait gave up leaves its loops; the other roles then run into their own bounded waits.
+    bool failed = false;
     B2_PROF_DECL
-    for (int item = blockIdx.x; item < n_items && !failed; item += gridDim.x) {
+    const float2 scale2 = make_float2(scale_log2, scale_log2);
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
       const AttnTile t = tiles[item / n_heads];
       const int h = item % n_heads;
       const int L = t.seq_len;
       const int n_kv = (L + TC_BKV - 1) / TC_BKV;
-      const int my_row = t.q_start + warp * 32 + lane;  // query row of this thread within the sequence
-      float2 o_reg[TC_D / 2];
-#pragma unroll
-      for (int j = 0; j < TC_D / 2; ++j) o_reg[j] = make_float2(0.f, 0.f);
-      float m_run = -INFINITY, l_run = 0.f;
+      // a warp whose 32 query rows all lie past the end of the sequence has nothing to compute
+      const bool warp_active = t.q_start + warp * 32 < L;
+      // Softmax reference point of this row (raw score units) and running denominator. The reference is
+      // NOT the running maximum: it is only moved when a score exceeds it by more than TC_LAZY_LOG2 (in
+      // log2 units), so nearly every step leaves O in tensor memory untouched; exp2 then yields values up
+      // to 2^TC_LAZY_LOG2, which numerator and denominator share.
+      float m_ref = 0.f, l_run = 0.f;
 
       for (int it = 0; it < n_kv; ++it, ++gi) {
         const int kv0 = it * TC_BKV;
         const int n_valid = min(TC_BKV, L - kv0);
         const int n_eff = (n_valid + 15) & ~15;
-        uint8_t* v_t = kv_s + kvstage * 2 * TC_TILE_BYTES + TC_TILE_BYTES;
-        if (!failed && !mbar_wait(bar_s, gi & 1u)) failed = true;
-        failed = __any_sync(0xffffffffu, failed);  // keep the warp-collective TMEM accesses below convergent
+        const int n_chunks = (n_eff + 31) >> 5;
+        if (!mbar_wait(bar_s, gi & 1u)) failed = true;
+        failed = __any_sync(0xffffffffu, failed);  // the warp leaves together
+        if (failed) break;
         tc_fence_after_sync();
-        B2_PROF(2);  // S MMA issue -> visible
+        B2_PROF(2);  // wait for S
 
-        float alpha = 1.f, l_add = 0.f;
-        // a warp whose 32 query rows all lie past the end of the sequence has nothing to compute
-        const bool warp_active = t.q_start + warp * 32 < L;
-        if (!failed && warp_active) {
-          // pass 1: row maximum over the valid keys (only the last, partial chunk needs masking)
-          float mx0 = -INFINITY, mx1 = -INFINITY;
-          for (int c = 0; c < n_eff; c += 32) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(lane_base + TC_S_COL + c, r);
-            tmem_ld_wait();
+        if (warp_active) {
+          uint32_t ra[32], rb[32];
+          bool pv_seen = false;
+          float mx0, mx1, l0;
+          float2 lsum;
+          float2 negm2;
+          // One 32-key chunk: p = exp2(s * scale - m_ref * scale), bf16 pairs into the P columns; also
+          // tracks the true row maximum. Only the last, partial chunk needs masking.
+          auto chunk = [&](const uint32_t (&r)[32], int c) {
+            uint32_t pk[16];
             if (c + 32 <= n_valid) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
                 mx0 = max3f(mx0, __uint_as_float(r[j]), __uint_as_float(r[j + 1]));
                 mx1 = max3f(mx1, __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
               }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) mx0 = fmaxf(mx0, (c + j < n_valid) ? __uint_as_float(r[j]) : -INFINITY);
-            }
-          }
-          B2_PROF(3);  // pass 1
-          const float m_new = fmaxf(m_run, fmaxf(mx0, mx1));
-          const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-          alpha = ex2f((m_run - m_use) * scale_log2);
-          m_run = m_new;
-          const float m_scaled = m_use * scale_log2;
-          // pass 2: p = exp2(s * scale - m * scale), bf16 pairs into the P columns
-          float l0 = 0.f, l1 = 0.f;
-          float2 lsum = make_float2(0.f, 0.f);
-          const float2 scale2 = make_float2(scale_log2, scale_log2);
-          const float2 negm2 = make_float2(-m_scaled, -m_scaled);
-          for (int c = 0; c < n_eff; c += 32) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(lane_base + TC_S_COL + c, r);
-            tmem_ld_wait();
-            uint32_t pk[16];
-            if (c + 32 <= n_valid) {
 #pragma unroll
               for (int j = 0; j < 32; j += 2) {
                 // packed fp32 pair: one FFMA2 / FADD2 per two keys
@@ -281,84 +352,170 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
             } else {
 #pragma unroll
               for (int j = 0; j < 32; j += 2) {
-                const float p0 = (c + j < n_valid) ? ex2f(fmaf(__uint_as_float(r[j]), scale_log2, -m_scaled)) : 0.f;
-                const float p1 =
-                    (c + j + 1 < n_valid) ? ex2f(fmaf(__uint_as_float(r[j + 1]), scale_log2, -m_scaled)) : 0.f;
-                l0 += p0;
-                l1 += p1;
+                const bool v0 = c + j < n_valid, v1 = c + j + 1 < n_valid;
+                const float s0 = __uint_as_float(r[j]), s1 = __uint_as_float(r[j + 1]);
+                mx0 = fmaxf(mx0, v0 ? s0 : -INFINITY);
+                mx1 = fmaxf(mx1, v1 ? s1 : -INFINITY);
+                const float p0 = v0 ? ex2f(fmaf(s0, scale_log2, negm2.x)) : 0.f;
+                const float p1 = v1 ? ex2f(fmaf(s1, scale_log2, negm2.x)) : 0.f;
+                l0 += p0 + p1;
                 __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
                 pk[j >> 1] = *reinterpret_cast<uint32_t*>(&b);
               }
             }
-            tmem_st_32x32b_x16(lane_base + TC_P_COL + (c >> 1), pk);
+            if (c == 0 && gi > 0 && !pv_seen) {
+              // P V of the previous step may still be reading the P columns
+              if (!__all_sync(0xffffffffu, mbar_wait(bar_pv, (gi - 1) & 1u))) failed = true;
+              pv_seen = true;
+            }
+            if (!failed) tmem_st_32x32b_x16(lane_base + TC_P_COL + (c >> 1), pk);
+          };
+          auto reset_sums = [&]() {
+            mx0 = mx1 = -INFINITY;
+            l0 = 0.f;
+            lsum = make_float2(0.f, 0.f);
+            negm2 = make_float2(-m_ref * scale_log2, -m_ref * scale_log2);
+          };
+
+          tmem_ld_32x32b_x32(lane_base + TC_S_COL, ra);
+          tmem_ld_wait_for(ra);
+          if (it == 0) {
+            // first key tile of the row: the reference point is the maximum of its first 32 keys
+            float e0 = -INFINITY, e1 = -INFINITY;
+            if (n_valid >= 32) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                e0 = max3f(e0, __uint_as_float(ra[j]), __uint_as_float(ra[j + 1]));
+                e1 = max3f(e1, __uint_as_float(ra[j + 2]), __uint_as_float(ra[j + 3]));
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) e0 = fmaxf(e0, (j < n_valid) ? __uint_as_float(ra[j]) : -INFINITY);
+            }
+            m_ref = fmaxf(e0, e1);
           }
-          l_add = (l0 + l1) + (lsum.x + lsum.y);
+          reset_sums();
+          // the load of chunk c + 1 is in flight while chunk c is computed
+          if (n_chunks > 1) tmem_ld_32x32b_x32(lane_base + TC_S_COL + 32, rb);
+          chunk(ra, 0);
+          if (n_chunks > 1) {
+            tmem_ld_wait_for(rb);
+            if (n_chunks > 2) tmem_ld_32x32b_x32(lane_base + TC_S_COL + 64, ra);
+            chunk(rb, 32);
+            if (n_chunks > 2) {
+              tmem_ld_wait_for(ra);
+              if (n_chunks > 3) tmem_ld_32x32b_x32(lane_base + TC_S_COL + 96, rb);
+              chunk(ra, 64);
+              if (n_chunks > 3) {
+                tmem_ld_wait_for(rb);
+                chunk(rb, 96);
+              }
+            }
+          }
+          B2_PROF(3);  // softmax pass
+          float alpha = 1.f;
+          const float mx = fmaxf(mx0, mx1);
+          const bool move_ref = (mx - m_ref) * scale_log2 > TC_LAZY_LOG2;
+          if (__any_sync(0xffffffffu, move_ref)) {
+            // Rare: some row of this warp met a score far above its reference point. Move the reference
+            // to the row maximum, redo this tile's P with it and rescale what O and l hold so far.
+            if (move_ref) {
+              alpha = ex2f((m_ref - mx) * scale_log2);
+              m_ref = mx;
+            }
+            reset_sums();
+            for (int c = 0; c < n_eff; c += 32) {
+              tmem_ld_32x32b_x32(lane_base + TC_S_COL + c, ra);
+              tmem_ld_wait_for(ra);
+              chunk(ra, c);
+            }
+            if (it > 0) {
+              // P V of the previous step has finished: this step's S was issued behind it
+              const float2 alpha2 = make_float2(alpha, alpha);
+#pragma unroll
+              for (int c = 0; c < TC_D; c += 32) {
+                tmem_ld_32x32b_x32(lane_base + TC_O_COL + c, ra);
+                tmem_ld_wait_for(ra);
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                  const float2 o = __fmul2_rn(make_float2(__uint_as_float(ra[j]), __uint_as_float(ra[j + 1])), alpha2);
+                  ra[j] = __float_as_uint(o.x);
+                  ra[j + 1] = __float_as_uint(o.y);
+                }
+                uint32_t half[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) half[j] = ra[j];
+                tmem_st_32x32b_x16(lane_base + TC_O_COL + c, half);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) half[j] = ra[16 + j];
+                tmem_st_32x32b_x16(lane_base + TC_O_COL + c + 16, half);
+              }
+            }
+          }
+          l_run = l_run * alpha + (l0 + (lsum.x + lsum.y));
           tmem_st_wait();
         }
-        B2_PROF(4);  // pass 2
+        B2_PROF(4);  // reference move + store wait
+        if (failed) break;  // warp-uniform: set from __all_sync
         tc_fence_before_sync();
-        // every softmax thread has written its P row (and agrees on whether to go on)
-        if (!named_barrier_and(1, 128, !failed)) {
-          failed = true;
-          break;
-        }
-        B2_PROF(5);  // barrier
-        if (threadIdx.x == 0) {
-          tc_fence_after_sync();
-          const uint32_t idesc = make_idesc_bf16_f32_b_mn(128, TC_D);
-          const uint32_t v_addr = smem_u32(v_t);
-          for (int k = 0; k < n_eff / 16; ++k) {
-            // 16 keys = two 8-row groups of the MN-major V tile = 2048 bytes; 16 keys of P = 8 columns
-            tc_mma_f16_tmem_a(tmem_base + TC_O_COL, tmem_base + TC_P_COL + k * 8,
-                              make_mnmajor_sw128_desc(v_addr + k * 2048, 16), idesc, k != 0);
-          }
-          tc_commit(bar_o);
-          tc_commit(&kv_empty[kvstage]);  // both MMAs of this tile have read the K/V stage
-          if (!issue_s()) failed = true;  // S of the next step queues up behind P V
-        }
-        if (!mbar_wait(bar_o, gi & 1u)) failed = true;
-        failed = __any_sync(0xffffffffu, failed);
-        tc_fence_after_sync();
-        B2_PROF(6);  // PV MMA issue -> visible
-        if (!failed && warp_active) {
-          l_run = l_run * alpha + l_add;
-#pragma unroll
-          for (int c = 0; c < TC_D; c += 32) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(lane_base + TC_O_COL + c, r);
-            tmem_ld_wait();
-            const float2 alpha2 = make_float2(alpha, alpha);
-#pragma unroll
-            for (int j = 0; j < 32; j += 2)
-              o_reg[(c + j) >> 1] =
-                  __ffma2_rn(o_reg[(c + j) >> 1], alpha2, make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])));
-          }
-        }
-        if (++kvstage == TC_KVSTAGES) kvstage = 0;
-        B2_PROF(7);  // O update
+        mbar_arrive(bar_p);  // this thread's P row is in tensor memory and its reads of S are done
       }
-      if (!failed && my_row < L) {
+      if (failed || !mbar_wait(bar_pv, (gi - 1) & 1u)) failed = true;  // the item's last P V
+      failed = __any_sync(0xffffffffu, failed);
+      if (failed) break;
+      tc_fence_after_sync();
+      B2_PROF(7);  // last P V -> visible
+      // The item's Q tile is dead (all its S MMAs have completed): each warp stages its 32 output rows
+      // there (128 bytes per row, 16-byte chunks XOR-swizzled by row so that neither pass has bank
+      // conflicts) and writes them out as whole 128-byte lines, four rows per instruction.
+      uint8_t* stage = q_s + oslot * TC_TILE_BYTES + warp * (32 * 128);
+      if (warp_active) {
+        uint32_t ra[32], rb[32];
+        tmem_ld_32x32b_x32(lane_base + TC_O_COL, ra);
+        tmem_ld_32x32b_x32(lane_base + TC_O_COL + 32, rb);
+        tmem_ld_wait_for(ra);
+        tmem_ld_wait_for(rb);
         const float inv = 1.f / l_run;
-        __nv_bfloat16* dst = out + static_cast<size_t>(t.seq_start + my_row) * (n_heads * TC_D) + h * TC_D;
-        const float2 inv2 = make_float2(inv, inv);
-#pragma unroll
-        for (int c = 0; c < TC_D; c += 8) {
+        auto stage8 = [&](const uint32_t* r, int chunk) {
           uint4 u;
-          const float2 a0 = __fmul2_rn(o_reg[c / 2], inv2), a1 = __fmul2_rn(o_reg[c / 2 + 1], inv2);
-          const float2 a2 = __fmul2_rn(o_reg[c / 2 + 2], inv2), a3 = __fmul2_rn(o_reg[c / 2 + 3], inv2);
-          __nv_bfloat162 p0 = __floats2bfloat162_rn(a0.x, a0.y);
-          __nv_bfloat162 p1 = __floats2bfloat162_rn(a1.x, a1.y);
-          __nv_bfloat162 p2 = __floats2bfloat162_rn(a2.x, a2.y);
-          __nv_bfloat162 p3 = __floats2bfloat162_rn(a3.x, a3.y);
+          __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
+          __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
+          __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
+          __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
           u.x = *reinterpret_cast<uint32_t*>(&p0);
           u.y = *reinterpret_cast<uint32_t*>(&p1);
           u.z = *reinterpret_cast<uint32_t*>(&p2);
           u.w = *reinterpret_cast<uint32_t*>(&p3);
-          *reinterpret_cast<uint4*>(dst + c) = u;
+          *reinterpret_cast<uint4*>(stage + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = u;
+        };
+#pragma unroll
+        for (int c = 0; c < 4; ++c) stage8(&ra[c * 8], c);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) stage8(&rb[c * 8], 4 + c);
+        __syncwarp();
+        const int rows_here = min(32, L - (t.q_start + warp * 32));  // > 0 for an active warp
+        __nv_bfloat16* dst0 = out + static_cast<size_t>(t.seq_start + t.q_start + warp * 32) * (n_heads * TC_D) + h * TC_D;
+        const int sub = lane >> 3, chunk = lane & 7;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = i * 4 + sub;
+          if (r < rows_here) {
+            const uint4 u = *reinterpret_cast<const uint4*>(stage + r * 128 + ((chunk ^ (r & 7)) << 4));
+            *reinterpret_cast<uint4*>(dst0 + static_cast<size_t>(r) * (n_heads * TC_D) + chunk * 8) = u;
+          }
         }
+        __syncwarp();
       }
+      // hand the Q slot back to the producer: generic-proxy accesses above, TMA write next
+      fence_proxy_async_smem();
+      if (lane == 0) mbar_arrive(&q_empty[oslot]);
+      oslot ^= 1;
+      B2_PROF(9);  // output
+      // The next item's first P V (which overwrites O) is issued only after this thread's next arrival
+      // on bar_p, which follows the loads above in program order.
     }
-    B2_PROF(8);  // output
+    B2_PROF(8);  // tail
+    B2_PROF_FLUSH;
     if (failed && lane == 0) atomicExch(err_flag, 4);
   }
 
@@ -372,7 +529,12 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
 
 #ifdef B2_ATT_PROFILE
 extern "C" int b200emb_debug_att_prof(long long* out16, int reset) {
-  if (out16) cudaMemcpyFromSymbol(out16, g_att_prof, sizeof(long long) * 16);
+  if (out16) {
+    cudaMemcpyFromSymbol(out16, g_att_prof, sizeof(long long) * 16);
+    int occ = -1;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, b2::attn_tc_d64_kernel, b2::TC_THREADS, b2::TC_SMEM_BYTES);
+    out16[15] = occ;
+  }
   if (reset) {
     long long z[16] = {};
     cudaMemcpyToSymbol(g_att_prof, z, sizeof(z));

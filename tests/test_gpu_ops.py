@@ -135,6 +135,38 @@ def test_attention_varlen(lib, d, nh, nkv, causal):
     assert err < 2e-2, err  # P and the output are rounded to bf16 (values are O(1))
 
 
+@pytest.mark.parametrize("kind", ["wide", "rising"])
+def test_attention_wide_score_range(lib, kind):
+    """Scores far above a row's first keys: the head_dim-64 kernel keeps a per-row reference point
+    (maximum of the first 32 keys) and must move it, redo P and rescale O when a later score exceeds
+    it by more than 2^10. 'wide' draws scores with a standard deviation of 12; 'rising' makes every
+    later key score higher than all earlier ones, so the reference moves on every key tile."""
+    nh, d = 4, 64
+    lens = [512, 130, 257, 31, 33, 384, 96]
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    T = int(cu[-1])
+    g = torch.Generator(device="cuda").manual_seed(7)
+    qkv = torch.randn(T, 3 * nh * d, generator=g, device="cuda")
+    if kind == "wide":
+        qkv[:, : nh * d] *= 12.0
+    else:
+        # k_j = (j / 8) * u + noise, q_i = 8 * u + noise: score grows by about one unit per key
+        u = torch.nn.functional.normalize(torch.randn(nh, d, generator=g, device="cuda"), dim=1)
+        pos = torch.cat([torch.arange(n, device="cuda", dtype=torch.float32) for n in lens])
+        qkv[:, : nh * d] = (8.0 * u).reshape(1, nh * d) + 0.1 * qkv[:, : nh * d]
+        qkv[:, nh * d : 2 * nh * d] = (pos[:, None, None] / 8.0 * u[None]).reshape(T, nh * d) + 0.1 * qkv[:, nh * d : 2 * nh * d]
+    qkv = qkv.to(torch.bfloat16)
+    out = torch.full((T, nh * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    d_cu = torch.from_numpy(cu).cuda()
+    torch.cuda.synchronize()
+    _lib.check(lib.b200emb_op_attention(qkv.data_ptr(), out.data_ptr(), d_cu.data_ptr(), cu.ctypes.data, len(lens), T,
+                                        nh, nh, d, 0, _stream()))
+    ref = _attention_ref(qkv, cu, nh, nh, d, 0)
+    assert not torch.isnan(out.float()).any()
+    err = (out.float() - ref).abs().max().item()
+    assert err < 3e-2, err
+
+
 @pytest.mark.parametrize("hidden", [128, 384, 768, 1024, 3584])
 def test_embed_ln_and_add_ln(lib, hidden):
     lens = [3, 50, 1, 129]
