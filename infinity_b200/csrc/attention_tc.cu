@@ -36,11 +36,9 @@ static constexpr int TC_QSLOTS = 2;
 static constexpr int TC_KSLOTS = 2;
 static constexpr int TC_VSLOTS = 2;
 static constexpr int TC_N_TILES = TC_QSLOTS + TC_KSLOTS + TC_VSLOTS;
+static constexpr int TC_STAGE_BYTES = 4 * 16 * 128;  // output staging: 16 rows of 128 bytes per softmax warp
 static constexpr int TC_BAR_BYTES = 160;
-// two CTAs per SM: each may use half of the SM's 228 KB less the 1 KB the system reserves per CTA;
-// the tiles need 1024-byte alignment, which the start of dynamic shared memory has when the kernel
-// declares no static shared memory (checked at run time, reported through the error flag)
-static constexpr int TC_SMEM_BYTES = TC_N_TILES * TC_TILE_BYTES + 1024;
+static constexpr int TC_SMEM_BYTES = TC_N_TILES * TC_TILE_BYTES + TC_STAGE_BYTES + TC_BAR_BYTES + 1024;
 static constexpr int TC_THREADS = 192;         // 4 softmax warps + TMA producer warp + MMA warp
 static constexpr uint32_t TC_TMEM_COLS = 256;  // S 128 | P 64 | O 64
 static constexpr uint32_t TC_S_COL = 0, TC_P_COL = 128, TC_O_COL = 192;
@@ -84,7 +82,8 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
   uint8_t* q_s = smem;
   uint8_t* k_s = q_s + TC_QSLOTS * TC_TILE_BYTES;
   uint8_t* v_s = k_s + TC_KSLOTS * TC_TILE_BYTES;
-  uint64_t* q_full = reinterpret_cast<uint64_t*>(v_s + TC_VSLOTS * TC_TILE_BYTES);
+  uint8_t* stage_s = v_s + TC_VSLOTS * TC_TILE_BYTES;
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(stage_s + TC_STAGE_BYTES);
   uint64_t* q_empty = q_full + TC_QSLOTS;
   uint64_t* k_full = q_empty + TC_QSLOTS;
   uint64_t* k_empty = k_full + TC_KSLOTS;
@@ -96,7 +95,7 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_pv + 1);
   static_assert((2 * TC_QSLOTS + 2 * TC_KSLOTS + 2 * TC_VSLOTS + 3) * 8 + 4 <= TC_BAR_BYTES, "barrier area");
   // shared memory too small once aligned: report and leave before anything is initialised (uniform per CTA)
-  if (smem + TC_N_TILES * TC_TILE_BYTES + TC_BAR_BYTES > att_raw + TC_SMEM_BYTES) {
+  if (smem + TC_N_TILES * TC_TILE_BYTES + TC_STAGE_BYTES + TC_BAR_BYTES > att_raw + TC_SMEM_BYTES) {
     if (threadIdx.x == 0) atomicExch(err_flag, 6);
     return;
   }
@@ -107,7 +106,7 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
   if (threadIdx.x == 0) {
     for (int i = 0; i < TC_QSLOTS; ++i) {
       mbar_init(&q_full[i], 1);
-      mbar_init(&q_empty[i], 4);  // one arrival per softmax warp, after it staged its output rows there
+      mbar_init(&q_empty[i], 1);
     }
     for (int i = 0; i < TC_KSLOTS; ++i) {
       mbar_init(&k_full[i], 1);
@@ -229,6 +228,7 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
       if (elect_one()) {
         tc_commit(bar_s);
         tc_commit(&k_empty[kslot]);
+        if (s_it == s_nkv - 1) tc_commit(&q_empty[qslot]);  // last use of this Q tile
       }
       B2_PROF(4);  // S issue
       if (++kslot == TC_KSLOTS) {
@@ -294,10 +294,68 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
   } else {
     // ---------------- softmax warps ----------------
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    uint32_t gi = 0;      // key tiles processed so far by this CTA: phase of bar_s
-    int oslot = 0;        // Q slot of the current work item (reused to stage its output rows)
+    uint8_t* stage = stage_s + warp * (16 * 128);  // 16 output rows of this warp at a time
+    uint32_t gi = 0;  // key tiles processed so far by this CTA: phase of bar_s, bar_p, bar_pv
     // A warp whose wait gave up leaves its loops; the other roles then run into their own bounded waits.
     bool failed = false;
+    // Output of the previous work item, written out during the first step of the next one (its last
+    // P V has long finished by then, so nobody idles waiting for it).
+    bool out_pending = false;
+    float out_inv = 0.f;
+    int out_rows = 0;
+    __nv_bfloat16* out_dst = nullptr;
+    const size_t out_stride = static_cast<size_t>(n_heads) * TC_D;
+    // O of the pending item -> bf16 rows in global memory. Each warp stages 16 rows at a time in shared
+    // memory (128 bytes per row, 16-byte chunks XOR-swizzled by row so that neither pass has bank
+    // conflicts) and writes them out as whole 128-byte lines, four rows per instruction.
+    auto write_pending = [&]() {
+      if (!mbar_wait(bar_pv, (gi - 1) & 1u)) failed = true;  // the item's last P V (normally long done)
+      failed = __any_sync(0xffffffffu, failed);
+      if (failed) return;
+      tc_fence_after_sync();
+      if (out_rows > 0) {
+        uint32_t ra[32], rb[32];
+        tmem_ld_32x32b_x32(lane_base + TC_O_COL, ra);
+        tmem_ld_32x32b_x32(lane_base + TC_O_COL + 32, rb);
+        tmem_ld_wait_for(ra);
+        tmem_ld_wait_for(rb);
+        const float inv = out_inv;
+        auto stage8 = [&](const uint32_t* r, int chunk) {
+          uint4 u;
+          __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
+          __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
+          __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
+          __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
+          u.x = *reinterpret_cast<uint32_t*>(&p0);
+          u.y = *reinterpret_cast<uint32_t*>(&p1);
+          u.z = *reinterpret_cast<uint32_t*>(&p2);
+          u.w = *reinterpret_cast<uint32_t*>(&p3);
+          *reinterpret_cast<uint4*>(stage + (lane & 15) * 128 + ((chunk ^ (lane & 7)) << 4)) = u;
+        };
+        const int sub = lane >> 3, chunk = lane & 7;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          if ((lane >> 4) == half) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) stage8(&ra[c * 8], c);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) stage8(&rb[c * 8], 4 + c);
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int rl = i * 4 + sub;  // row within this half
+            const int r = half * 16 + rl;
+            if (r < out_rows) {
+              const uint4 u = *reinterpret_cast<const uint4*>(stage + rl * 128 + ((chunk ^ (rl & 7)) << 4));
+              *reinterpret_cast<uint4*>(out_dst + static_cast<size_t>(r) * out_stride + chunk * 8) = u;
+            }
+          }
+          __syncwarp();
+        }
+      }
+      out_pending = false;
+    };
     B2_PROF_DECL
     const float2 scale2 = make_float2(scale_log2, scale_log2);
     for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
@@ -326,14 +384,13 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
 
         if (warp_active) {
           uint32_t ra[32], rb[32];
-          bool pv_seen = false;
+          uint32_t pa[16], pb[16];
           float mx0, mx1, l0;
           float2 lsum;
           float2 negm2;
-          // One 32-key chunk: p = exp2(s * scale - m_ref * scale), bf16 pairs into the P columns; also
-          // tracks the true row maximum. Only the last, partial chunk needs masking.
-          auto chunk = [&](const uint32_t (&r)[32], int c) {
-            uint32_t pk[16];
+          // One 32-key chunk: p = exp2(s * scale - m_ref * scale) as bf16 pairs; also tracks the true row
+          // maximum. Only the last, partial chunk needs masking.
+          auto chunk = [&](const uint32_t (&r)[32], uint32_t (&pk)[16], int c) {
             if (c + 32 <= n_valid) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
@@ -363,13 +420,8 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
                 pk[j >> 1] = *reinterpret_cast<uint32_t*>(&b);
               }
             }
-            if (c == 0 && gi > 0 && !pv_seen) {
-              // P V of the previous step may still be reading the P columns
-              if (!__all_sync(0xffffffffu, mbar_wait(bar_pv, (gi - 1) & 1u))) failed = true;
-              pv_seen = true;
-            }
-            if (!failed) tmem_st_32x32b_x16(lane_base + TC_P_COL + (c >> 1), pk);
           };
+          auto store_p = [&](const uint32_t (&pk)[16], int c) { tmem_st_32x32b_x16(lane_base + TC_P_COL + (c >> 1), pk); };
           auto reset_sums = [&]() {
             mx0 = mx1 = -INFINITY;
             l0 = 0.f;
@@ -395,125 +447,92 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
             m_ref = fmaxf(e0, e1);
           }
           reset_sums();
-          // the load of chunk c + 1 is in flight while chunk c is computed
+          // The load of chunk c + 1 is in flight while chunk c is computed. The first two chunks are held
+          // in registers until P V of the previous step (issued behind this step's S) has read the P
+          // columns; by then that wait is normally over.
           if (n_chunks > 1) tmem_ld_32x32b_x32(lane_base + TC_S_COL + 32, rb);
-          chunk(ra, 0);
+          chunk(ra, pa, 0);
           if (n_chunks > 1) {
             tmem_ld_wait_for(rb);
             if (n_chunks > 2) tmem_ld_32x32b_x32(lane_base + TC_S_COL + 64, ra);
-            chunk(rb, 32);
+            chunk(rb, pb, 32);
+          }
+          if (gi > 0 && !__all_sync(0xffffffffu, mbar_wait(bar_pv, (gi - 1) & 1u))) failed = true;
+          if (!failed) {
+            store_p(pa, 0);
+            if (n_chunks > 1) store_p(pb, 32);
             if (n_chunks > 2) {
               tmem_ld_wait_for(ra);
               if (n_chunks > 3) tmem_ld_32x32b_x32(lane_base + TC_S_COL + 96, rb);
-              chunk(ra, 64);
+              chunk(ra, pa, 64);
+              store_p(pa, 64);
               if (n_chunks > 3) {
                 tmem_ld_wait_for(rb);
-                chunk(rb, 96);
+                chunk(rb, pb, 96);
+                store_p(pb, 96);
               }
             }
-          }
-          B2_PROF(3);  // softmax pass
-          float alpha = 1.f;
-          const float mx = fmaxf(mx0, mx1);
-          const bool move_ref = (mx - m_ref) * scale_log2 > TC_LAZY_LOG2;
-          if (__any_sync(0xffffffffu, move_ref)) {
-            // Rare: some row of this warp met a score far above its reference point. Move the reference
-            // to the row maximum, redo this tile's P with it and rescale what O and l hold so far.
-            if (move_ref) {
-              alpha = ex2f((m_ref - mx) * scale_log2);
-              m_ref = mx;
-            }
-            reset_sums();
-            for (int c = 0; c < n_eff; c += 32) {
-              tmem_ld_32x32b_x32(lane_base + TC_S_COL + c, ra);
-              tmem_ld_wait_for(ra);
-              chunk(ra, c);
-            }
-            if (it > 0) {
-              // P V of the previous step has finished: this step's S was issued behind it
-              const float2 alpha2 = make_float2(alpha, alpha);
-#pragma unroll
-              for (int c = 0; c < TC_D; c += 32) {
-                tmem_ld_32x32b_x32(lane_base + TC_O_COL + c, ra);
+            B2_PROF(3);  // softmax pass
+            float alpha = 1.f;
+            const float mx = fmaxf(mx0, mx1);
+            const bool move_ref = (mx - m_ref) * scale_log2 > TC_LAZY_LOG2;
+            if (__any_sync(0xffffffffu, move_ref)) {
+              // Rare: some row of this warp met a score far above its reference point. Move the reference
+              // to the row maximum, redo this tile's P with it and rescale what O and l hold so far.
+              if (move_ref) {
+                alpha = ex2f((m_ref - mx) * scale_log2);
+                m_ref = mx;
+              }
+              reset_sums();
+              for (int c = 0; c < n_eff; c += 32) {
+                tmem_ld_32x32b_x32(lane_base + TC_S_COL + c, ra);
                 tmem_ld_wait_for(ra);
+                chunk(ra, pa, c);
+                store_p(pa, c);
+              }
+              if (it > 0) {
+                // P V of the previous step has finished (waited for above)
+                const float2 alpha2 = make_float2(alpha, alpha);
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                  const float2 o = __fmul2_rn(make_float2(__uint_as_float(ra[j]), __uint_as_float(ra[j + 1])), alpha2);
-                  ra[j] = __float_as_uint(o.x);
-                  ra[j + 1] = __float_as_uint(o.y);
+                for (int c = 0; c < TC_D; c += 32) {
+                  tmem_ld_32x32b_x32(lane_base + TC_O_COL + c, ra);
+                  tmem_ld_wait_for(ra);
+#pragma unroll
+                  for (int j = 0; j < 32; j += 2) {
+                    const float2 o = __fmul2_rn(make_float2(__uint_as_float(ra[j]), __uint_as_float(ra[j + 1])), alpha2);
+                    ra[j] = __float_as_uint(o.x);
+                    ra[j + 1] = __float_as_uint(o.y);
+                  }
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) pa[j] = ra[j];
+                  tmem_st_32x32b_x16(lane_base + TC_O_COL + c, pa);
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) pb[j] = ra[16 + j];
+                  tmem_st_32x32b_x16(lane_base + TC_O_COL + c + 16, pb);
                 }
-                uint32_t half[16];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) half[j] = ra[j];
-                tmem_st_32x32b_x16(lane_base + TC_O_COL + c, half);
-#pragma unroll
-                for (int j = 0; j < 16; ++j) half[j] = ra[16 + j];
-                tmem_st_32x32b_x16(lane_base + TC_O_COL + c + 16, half);
               }
             }
+            l_run = l_run * alpha + (l0 + (lsum.x + lsum.y));
+            tmem_st_wait();
           }
-          l_run = l_run * alpha + (l0 + (lsum.x + lsum.y));
-          tmem_st_wait();
         }
         B2_PROF(4);  // reference move + store wait
         if (failed) break;  // warp-uniform: set from __all_sync
+        if (out_pending) {
+          write_pending();  // previous item's rows; its O is overwritten only after the arrival below
+          if (failed) break;
+          B2_PROF(9);  // output
+        }
         tc_fence_before_sync();
         mbar_arrive(bar_p);  // this thread's P row is in tensor memory and its reads of S are done
       }
-      if (failed || !mbar_wait(bar_pv, (gi - 1) & 1u)) failed = true;  // the item's last P V
-      failed = __any_sync(0xffffffffu, failed);
       if (failed) break;
-      tc_fence_after_sync();
-      B2_PROF(7);  // last P V -> visible
-      // The item's Q tile is dead (all its S MMAs have completed): each warp stages its 32 output rows
-      // there (128 bytes per row, 16-byte chunks XOR-swizzled by row so that neither pass has bank
-      // conflicts) and writes them out as whole 128-byte lines, four rows per instruction.
-      uint8_t* stage = q_s + oslot * TC_TILE_BYTES + warp * (32 * 128);
-      if (warp_active) {
-        uint32_t ra[32], rb[32];
-        tmem_ld_32x32b_x32(lane_base + TC_O_COL, ra);
-        tmem_ld_32x32b_x32(lane_base + TC_O_COL + 32, rb);
-        tmem_ld_wait_for(ra);
-        tmem_ld_wait_for(rb);
-        const float inv = 1.f / l_run;
-        auto stage8 = [&](const uint32_t* r, int chunk) {
-          uint4 u;
-          __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
-          __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
-          __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
-          __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
-          u.x = *reinterpret_cast<uint32_t*>(&p0);
-          u.y = *reinterpret_cast<uint32_t*>(&p1);
-          u.z = *reinterpret_cast<uint32_t*>(&p2);
-          u.w = *reinterpret_cast<uint32_t*>(&p3);
-          *reinterpret_cast<uint4*>(stage + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = u;
-        };
-#pragma unroll
-        for (int c = 0; c < 4; ++c) stage8(&ra[c * 8], c);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) stage8(&rb[c * 8], 4 + c);
-        __syncwarp();
-        const int rows_here = min(32, L - (t.q_start + warp * 32));  // > 0 for an active warp
-        __nv_bfloat16* dst0 = out + static_cast<size_t>(t.seq_start + t.q_start + warp * 32) * (n_heads * TC_D) + h * TC_D;
-        const int sub = lane >> 3, chunk = lane & 7;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int r = i * 4 + sub;
-          if (r < rows_here) {
-            const uint4 u = *reinterpret_cast<const uint4*>(stage + r * 128 + ((chunk ^ (r & 7)) << 4));
-            *reinterpret_cast<uint4*>(dst0 + static_cast<size_t>(r) * (n_heads * TC_D) + chunk * 8) = u;
-          }
-        }
-        __syncwarp();
-      }
-      // hand the Q slot back to the producer: generic-proxy accesses above, TMA write next
-      fence_proxy_async_smem();
-      if (lane == 0) mbar_arrive(&q_empty[oslot]);
-      oslot ^= 1;
-      B2_PROF(9);  // output
-      // The next item's first P V (which overwrites O) is issued only after this thread's next arrival
-      // on bar_p, which follows the loads above in program order.
+      out_pending = true;
+      out_inv = 1.f / l_run;
+      out_rows = warp_active ? min(32, L - (t.q_start + warp * 32)) : 0;
+      out_dst = out + static_cast<size_t>(t.seq_start + t.q_start + warp * 32) * out_stride + h * TC_D;
     }
+    if (!failed && out_pending) write_pending();
     B2_PROF(8);  // tail
     B2_PROF_FLUSH;
     if (failed && lane == 0) atomicExch(err_flag, 4);
