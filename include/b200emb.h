@@ -208,8 +208,10 @@ int b200emb_op_gemm_mxfp8(const void* A_bf16, const void* W_q, const void* W_sca
 /* Variable-length attention over a packed qkv buffer [n_tokens, (n_heads + 2*n_kv_heads) * head_dim]
  * (all query heads, then all key heads, then all value heads), bf16.
  * out [n_tokens, n_heads * head_dim] bf16. h_cu_seqlens is the host copy used
- * to build the tile list. causal: 0 = bidirectional, 1 = causal; adding 0x100 forces the
- * mma.sync kernel where the tensor-memory kernel (head_dim 64, bidirectional) would be chosen.
+ * to build the tile list. causal: 0 = bidirectional, 1 = causal. head_dim 64 and 128 run on the
+ * tensor-memory (tcgen05) kernels, other head dims on the mma.sync kernel; adding 0x100 forces the
+ * mma.sync kernel, adding 0x200 forces the one-CTA-per-SM tensor-memory kernel (which otherwise serves
+ * head_dim 128 and causal batches) for head_dim 64 bidirectional too.
  * Synchronises the stream before returning. */
 int b200emb_op_attention(const void* qkv, void* out, const int32_t* d_cu_seqlens, const int32_t* h_cu_seqlens,
                          int32_t n_seqs, int32_t n_tokens, int32_t n_heads, int32_t n_kv_heads,

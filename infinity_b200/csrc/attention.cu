@@ -248,7 +248,10 @@ static constexpr int att_smem_bytes() {
   return (ATT_BQ + 4 * ATT_BKV) * (D + 8) * 2;
 }
 
-int attention_tile_rows(int head_dim, int causal) { return (head_dim == 64 && !causal) ? 128 : ATT_BQ; }
+int attention_tile_rows(int head_dim, int causal) {
+  (void)causal;
+  return (head_dim == 64 || head_dim == 128) ? 128 : ATT_BQ;
+}
 
 int attention_build_tiles_q(const int32_t* cu, int n_seqs, int bq, AttnTile* tiles) {
   // Longest sequences first, so the most expensive tiles start early and the tail is short.

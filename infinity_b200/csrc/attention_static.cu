@@ -81,6 +81,7 @@ extern "C" int b200emb_op_attention_static(const void* qkv, void* out, const int
     return set_error(B200EMB_ERR_INVALID, "attention_static: null pointer or empty batch");
   if (h_cu_seqlens[0] != 0 || h_cu_seqlens[n_seqs] != n_tokens)
     return set_error(B200EMB_ERR_INVALID, "attention_static: cu_seqlens does not span n_tokens");
+  const int variant = (causal >> 9) & 1;  // bit 9: one-CTA-per-SM tensor-memory kernel whatever the shape
   causal &= 1;
   const int bq = attention_tile_rows(head_dim, causal);
   long long n_tiles = 0;
@@ -111,8 +112,8 @@ extern "C" int b200emb_op_attention_static(const void* qkv, void* out, const int
     int dev = 0, sms = 0;
     B2_CUDA_CHECK(cudaGetDevice(&dev));
     B2_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    rc = launch_attention_tc(qkv, out, d_tiles, static_cast<int>(n_tiles), n_tokens, n_heads, n_kv_heads, head_dim, sms,
-                             d_err, s);
+    rc = launch_attention_tc(qkv, out, d_tiles, static_cast<int>(n_tiles), n_tokens, n_heads, n_kv_heads, head_dim, causal,
+                             variant, sms, d_err, s);
   } else {
     rc = launch_attention(qkv, out, d_tiles, static_cast<int>(n_tiles), n_heads, n_kv_heads, head_dim, causal, s);
   }

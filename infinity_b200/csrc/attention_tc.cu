@@ -568,9 +568,12 @@ int attention_tc_init_device() {
 }
 
 int launch_attention_tc(const void* qkv, void* out, const AttnTile* d_tiles, int n_tiles, int n_tokens, int n_heads,
-                        int n_kv_heads, int head_dim, int sm_count, int* err_flag, cudaStream_t stream) {
+                        int n_kv_heads, int head_dim, int causal, int variant, int sm_count, int* err_flag,
+                        cudaStream_t stream) {
+  if (head_dim != TC_D || causal || variant == 1)
+    return launch_attention_tc2(qkv, out, d_tiles, n_tiles, n_tokens, n_heads, n_kv_heads, head_dim, causal, sm_count,
+                                err_flag, stream);
   if (n_tiles <= 0) return B200EMB_OK;
-  if (head_dim != TC_D) return set_error(B200EMB_ERR_UNSUPPORTED, "tensor-memory attention is built for head_dim 64");
   if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_heads > 65535)
     return set_error(B200EMB_ERR_INVALID, "attention: bad head counts %d / %d", n_heads, n_kv_heads);
   CUtensorMap tm;

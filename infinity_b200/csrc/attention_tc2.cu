@@ -1,0 +1,669 @@
+// Variable-length attention on the 5th-generation tensor cores, one CTA per SM, for head_dim 64 and
+// 128, bidirectional or causal, with grouped-query heads.
+//
+// One work item = one 128-row query tile of one (sequence, head); tiles never cross a sequence
+// boundary. Q, K and V arrive by TMA straight from the packed qkv buffer as boxes of 128 rows x 64
+// columns (128-byte swizzle); a head_dim-128 tile is two such boxes. Per 128-key tile ("step"):
+//   S = Q K^T      tcgen05.mma 128 x N x 16 (N = valid keys rounded up to 16), fp32 in tensor memory.
+//                  S is DOUBLE-BUFFERED (2 x 128 columns): S of step n + 2 is issued as soon as the
+//                  softmax threads have read S of step n, so the softmax of step n + 1 never waits
+//                  for an MMA round trip.
+//   softmax        128 threads, one TMEM lane (= one query row) each, one pass over the row in
+//                  32-key chunks whose loads run one chunk ahead of the math: p = exp2(s - m_ref)
+//                  against a per-row reference point that is the maximum of the row's first 32 valid
+//                  keys and is moved (second pass + rescale of O) only when a later score exceeds it
+//                  by more than 2^10. Causal masking touches only the diagonal key tile. P is rounded
+//                  to bf16 and written to tensor memory (two keys per 32-bit column).
+//   O += P V       tcgen05.mma with A = P from tensor memory and V as an MN-major shared-memory
+//                  operand; O accumulates in tensor memory and is read once per query tile, during the
+//                  first step of the NEXT work item (so nobody idles waiting for the last P V).
+// Warp roles: 0-3 softmax, 4 TMA producer for Q and K, 5 MMA issuer (warp-uniform code, tcgen05
+// instructions under elect.sync so that descriptors stay in uniform registers), 6 TMA producer for V
+// (its own thread, so that a full V ring never holds back the K loads that S needs earlier).
+// Tensor memory (512 columns): S0 0..127 | S1 128..255 | P 256..319 | O 320..320+D-1.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace b2 {
+
+static constexpr int T2_BKV = 128;
+static constexpr int T2_BOX_BYTES = 128 * 64 * 2;  // one TMA box: 128 rows x 64 bf16
+static constexpr int T2_THREADS = 224;
+static constexpr uint32_t T2_TMEM_COLS = 512;
+static constexpr uint32_t T2_S_COL = 0, T2_P_COL = 256, T2_O_COL = 320;
+static constexpr float T2_LAZY_LOG2 = 10.f;  // how far (log2 units) a score may exceed the row's reference point
+
+#ifdef B2_ATT_PROFILE
+// Phase timing of CTA 0 (development aid; not part of normal builds).
+__device__ long long g_att2_prof[16];
+#define T2_PROF_DECL(tid) unsigned prof_acc[8] = {}; unsigned prof_t0 = (unsigned)clock(); const bool prof_on = (blockIdx.x == 0 && threadIdx.x == (tid));
+#define T2_PROF(slot) do { if (prof_on) { const unsigned n__ = (unsigned)clock(); prof_acc[slot] += n__ - prof_t0; prof_t0 = n__; } } while (0)
+#define T2_PROF_FLUSH(base) do { if (prof_on) { for (int i__ = 0; i__ < 8; ++i__) g_att2_prof[(base) + i__] += prof_acc[i__]; } } while (0)
+#else
+#define T2_PROF_DECL(tid)
+#define T2_PROF(slot) do { } while (0)
+#define T2_PROF_FLUSH(base) do { } while (0)
+#endif
+
+template <int D>
+struct T2Cfg {
+  static constexpr int BOXES = D / 64;
+  static constexpr int TILE_BYTES = BOXES * T2_BOX_BYTES;
+  static constexpr int QSLOTS = 2;
+  static constexpr int KSLOTS = D == 64 ? 4 : 2;
+  static constexpr int VSLOTS = D == 64 ? 4 : 2;
+  static constexpr int STAGE_BYTES = 4 * 16 * 128;  // output staging: 16 rows x 128 bytes per softmax warp
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int N_BARS = 2 * (QSLOTS + KSLOTS + VSLOTS) + 4;
+  static constexpr int SMEM_BYTES = (QSLOTS + KSLOTS + VSLOTS) * TILE_BYTES + STAGE_BYTES + BAR_BYTES + 1024;
+  static_assert(N_BARS * 8 + 4 <= BAR_BYTES, "barrier area");
+  static_assert(T2_O_COL + D <= T2_TMEM_COLS, "tensor memory columns");
+};
+
+__device__ __forceinline__ float t2_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float t2_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// After a failed wait: lets the copies still in flight land before shared memory is released (bounded).
+__device__ __forceinline__ void t2_drain(uint64_t* full, uint32_t fills, uint32_t slots) {
+  for (uint32_t i = 0; i < (fills < slots ? fills : slots); ++i) {
+    const uint32_t idx = fills - 1 - i;
+    mbar_wait(&full[idx % slots], (idx / slots) & 1u);
+  }
+}
+
+// Key tiles a query tile visits.
+template <bool CAUSAL>
+__device__ __forceinline__ int t2_n_kv(int seq_len, int q_start) {
+  const int all = (seq_len + T2_BKV - 1) / T2_BKV;
+  return CAUSAL ? min(all, q_start / T2_BKV + 1) : all;
+}
+
+// Persistent: CTA b serves work items b, b + gridDim.x, ...; item i = (query tile i / n_heads,
+// head i % n_heads). Every role walks the same sequence of (item, key tile) steps.
+template <int D, bool CAUSAL>
+__global__ void __launch_bounds__(T2_THREADS, 1)
+attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __restrict__ out,
+                const AttnTile* __restrict__ tiles, int n_items, int n_heads, int n_kv_heads, float scale_log2,
+                int* __restrict__ err_flag) {
+  using Cfg = T2Cfg<D>;
+  constexpr int TILE = Cfg::TILE_BYTES;
+  extern __shared__ uint8_t att2_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(att2_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = smem;
+  uint8_t* k_s = q_s + Cfg::QSLOTS * TILE;
+  uint8_t* v_s = k_s + Cfg::KSLOTS * TILE;
+  uint8_t* stage_s = v_s + Cfg::VSLOTS * TILE;
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(stage_s + Cfg::STAGE_BYTES);
+  uint64_t* q_empty = q_full + Cfg::QSLOTS;
+  uint64_t* k_full = q_empty + Cfg::QSLOTS;
+  uint64_t* k_empty = k_full + Cfg::KSLOTS;
+  uint64_t* v_full = k_empty + Cfg::KSLOTS;
+  uint64_t* v_empty = v_full + Cfg::VSLOTS;
+  uint64_t* bar_s = v_empty + Cfg::VSLOTS;  // [2]: S of a step is in tensor memory (one per S buffer)
+  uint64_t* bar_p = bar_s + 2;              // all 128 softmax threads have written P of a step
+  uint64_t* bar_pv = bar_p + 1;             // P V of a step has finished: P may be overwritten, O may be read
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_pv + 1);
+
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // warp-uniform in the compiler's view too
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < Cfg::QSLOTS; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+    }
+    for (int i = 0; i < Cfg::KSLOTS; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+    }
+    for (int i = 0; i < Cfg::VSLOTS; ++i) {
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+    }
+    mbar_init(&bar_s[0], 1);
+    mbar_init(&bar_s[1], 1);
+    mbar_init(bar_p, 128);
+    mbar_init(bar_pv, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, T2_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // ---------------- TMA producer: Q and K ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_qkv);
+      int qslot = 0, kslot = 0;
+      uint32_t qphase = 0, kphase = 0;
+      uint32_t q_fills = 0, k_fills = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const AttnTile t = tiles[item / n_heads];
+        const int h = item % n_heads;
+        const int hk = h / (n_heads / n_kv_heads);
+        const int n_kv = t2_n_kv<CAUSAL>(t.seq_len, t.q_start);
+        if (!mbar_wait(&q_empty[qslot], qphase ^ 1u)) {
+          ok = false;
+          break;
+        }
+        mbar_arrive_expect_tx(&q_full[qslot], TILE);
+#pragma unroll
+        for (int b = 0; b < Cfg::BOXES; ++b)
+          tma_load_2d(q_s + qslot * TILE + b * T2_BOX_BYTES, &tmap_qkv, &q_full[qslot], h * D + b * 64,
+                      t.seq_start + t.q_start);
+        ++q_fills;
+        if (++qslot == Cfg::QSLOTS) {
+          qslot = 0;
+          qphase ^= 1u;
+        }
+        for (int it = 0; it < n_kv; ++it) {
+          if (!mbar_wait(&k_empty[kslot], kphase ^ 1u)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&k_full[kslot], TILE);
+#pragma unroll
+          for (int b = 0; b < Cfg::BOXES; ++b)
+            tma_load_2d(k_s + kslot * TILE + b * T2_BOX_BYTES, &tmap_qkv, &k_full[kslot], (n_heads + hk) * D + b * 64,
+                        t.seq_start + it * T2_BKV);
+          ++k_fills;
+          if (++kslot == Cfg::KSLOTS) {
+            kslot = 0;
+            kphase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        atomicExch(err_flag, 5);
+        // let the copies still in flight land before shared memory is released (bounded)
+        t2_drain(q_full, q_fills, Cfg::QSLOTS);
+        t2_drain(k_full, k_fills, Cfg::KSLOTS);
+      }
+    }
+  } else if (warp == 6) {
+    // ---------------- TMA producer: V ----------------
+    if (lane == 0) {
+      int vslot = 0;
+      uint32_t vphase = 0, v_fills = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const AttnTile t = tiles[item / n_heads];
+        const int hk = (item % n_heads) / (n_heads / n_kv_heads);
+        const int n_kv = t2_n_kv<CAUSAL>(t.seq_len, t.q_start);
+        for (int it = 0; it < n_kv; ++it) {
+          if (!mbar_wait(&v_empty[vslot], vphase ^ 1u)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&v_full[vslot], TILE);
+#pragma unroll
+          for (int b = 0; b < Cfg::BOXES; ++b)
+            tma_load_2d(v_s + vslot * TILE + b * T2_BOX_BYTES, &tmap_qkv, &v_full[vslot],
+                        (n_heads + n_kv_heads + hk) * D + b * 64, t.seq_start + it * T2_BKV);
+          ++v_fills;
+          if (++vslot == Cfg::VSLOTS) {
+            vslot = 0;
+            vphase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        atomicExch(err_flag, 8);
+        t2_drain(v_full, v_fills, Cfg::VSLOTS);
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer: all 32 lanes walk the loops, one elected lane issues ----------------
+    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+    const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
+    int s_item = blockIdx.x, s_it = 0, s_nkv = 0, s_len = 0;
+    uint32_t s_count = 0;  // S tiles issued so far: buffer = s_count & 1
+    int qslot = 0, kslot = 0, vslot = 0;
+    uint32_t qphase = 0, kphase = 0, vphase = 0;
+    bool ok = true;
+    // every lane waits; the warp agrees on the outcome so that it never splits around elect.sync
+    auto wait_all = [](uint64_t* bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbar_wait(bar, parity)); };
+    // Issues S of the next step in the CTA's step sequence into S buffer (s_count & 1). The caller makes
+    // sure that buffer is free: the first two are, afterwards S of step n + 2 follows bar_p of step n.
+    auto issue_s = [&]() -> bool {  // false when a wait gave up
+      if (s_item >= n_items) return true;
+      if (s_it == 0) {
+        const AttnTile* tp = &tiles[s_item / n_heads];
+        s_len = __shfl_sync(0xffffffffu, tp->seq_len, 0);
+        const int q_start = __shfl_sync(0xffffffffu, tp->q_start, 0);
+        s_nkv = t2_n_kv<CAUSAL>(s_len, q_start);
+        if (!wait_all(&q_full[qslot], qphase)) return false;
+      }
+      if (!wait_all(&k_full[kslot], kphase)) return false;
+      tc_fence_after_sync();
+      const int nv = min(T2_BKV, s_len - s_it * T2_BKV);
+      const uint32_t idesc = make_idesc_bf16_f32(128, (nv + 15) & ~15);
+      const uint32_t s_col = T2_S_COL + (s_count & 1u) * 128u;
+#pragma unroll
+      for (int k = 0; k < D / 16; ++k) {
+        // 16 head-dim elements per MMA: box k / 4, 32 bytes (2 descriptor units) further per step inside it
+        const uint64_t a_desc = make_kmajor_sw128_desc(q_addr + qslot * TILE + (k / 4) * T2_BOX_BYTES) + 2 * (k % 4);
+        const uint64_t b_desc = make_kmajor_sw128_desc(k_addr + kslot * TILE + (k / 4) * T2_BOX_BYTES) + 2 * (k % 4);
+        if (elect_one()) tc_mma_f16(tmem_u + s_col, a_desc, b_desc, idesc, k != 0);
+      }
+      if (elect_one()) {
+        tc_commit(&bar_s[s_count & 1u]);
+        tc_commit(&k_empty[kslot]);
+        if (s_it == s_nkv - 1) tc_commit(&q_empty[qslot]);  // last use of this Q tile
+      }
+      ++s_count;
+      if (++kslot == Cfg::KSLOTS) {
+        kslot = 0;
+        kphase ^= 1u;
+      }
+      if (++s_it == s_nkv) {
+        s_it = 0;
+        s_item += gridDim.x;
+        if (++qslot == Cfg::QSLOTS) {
+          qslot = 0;
+          qphase ^= 1u;
+        }
+      }
+      return true;
+    };
+    ok = issue_s() && issue_s();  // S of the first two steps
+    uint32_t gi = 0;
+    T2_PROF_DECL(160)
+    const uint32_t idesc_pv = make_idesc_bf16_f32_b_mn(128, D);
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const AttnTile* tp = &tiles[item / n_heads];
+      const int L = __shfl_sync(0xffffffffu, tp->seq_len, 0);
+      const int q_start = __shfl_sync(0xffffffffu, tp->q_start, 0);
+      const int n_kv = t2_n_kv<CAUSAL>(L, q_start);
+      for (int it = 0; it < n_kv; ++it, ++gi) {
+        const int n_eff = (min(T2_BKV, L - it * T2_BKV) + 15) & ~15;
+        if (!wait_all(bar_p, gi & 1u)) {
+          ok = false;
+          break;
+        }
+        T2_PROF(0);  // wait for P
+        if (!wait_all(&v_full[vslot], vphase)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        T2_PROF(1);  // wait for V
+        // V tile: MN-major, head-dim blocks of 64 are T2_BOX_BYTES apart; 16 keys = two 8-row groups =
+        // 2048 bytes (128 descriptor units); 16 keys of P = 8 columns
+        const uint64_t v_desc = make_mnmajor_sw128_desc(v_addr + vslot * TILE, T2_BOX_BYTES);
+#pragma unroll
+        for (int k = 0; k < T2_BKV / 16; ++k)
+          if (k * 16 < n_eff && elect_one())
+            tc_mma_f16_tmem_a(tmem_u + T2_O_COL, tmem_u + T2_P_COL + k * 8, v_desc + k * 128, idesc_pv, (it | k) != 0);
+        if (elect_one()) {
+          tc_commit(bar_pv);
+          tc_commit(&v_empty[vslot]);
+        }
+        T2_PROF(2);  // P V issue
+        if (++vslot == Cfg::VSLOTS) {
+          vslot = 0;
+          vphase ^= 1u;
+        }
+        // bar_p of this step also released S buffer (gi & 1): S of step gi + 2 goes there
+        if (!issue_s()) {
+          ok = false;
+          break;
+        }
+        T2_PROF(3);  // S issue incl. waits for Q / K
+      }
+    }
+    T2_PROF_FLUSH(8);
+    if (!ok && lane == 0) atomicExch(err_flag, 7);
+  } else {
+    // ---------------- softmax warps ----------------
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    uint8_t* stage = stage_s + warp * (16 * 128);  // 16 output rows x 64 columns of this warp at a time
+    uint32_t gi = 0;  // key tiles processed so far by this CTA: phases of bar_s, bar_p, bar_pv
+    // A warp whose wait gave up leaves its loops; the other roles then run into their own bounded waits.
+    bool failed = false;
+    // Output of the previous work item, written out during the first step of the next one.
+    bool out_pending = false;
+    float out_inv = 0.f;
+    int out_rows = 0;
+    __nv_bfloat16* out_dst = nullptr;
+    const size_t out_stride = static_cast<size_t>(n_heads) * D;
+    // O of the pending item -> bf16 rows in global memory, 64 columns at a time. Each warp stages 16 rows
+    // in shared memory (128 bytes per row, 16-byte chunks XOR-swizzled by row so that neither pass has
+    // bank conflicts) and writes them out as whole 128-byte lines, four rows per instruction.
+    auto write_pending = [&]() {
+      if (!mbar_wait(bar_pv, (gi - 1) & 1u)) failed = true;  // the item's last P V (normally long done)
+      failed = __any_sync(0xffffffffu, failed);
+      if (failed) return;
+      tc_fence_after_sync();
+      if (out_rows > 0) {
+        const float inv = out_inv;
+        const int sub = lane >> 3, chunk = lane & 7;
+#pragma unroll 1
+        for (int seg = 0; seg < D / 64; ++seg) {
+          uint32_t ra[32], rb[32];
+          tmem_ld_32x32b_x32(lane_base + T2_O_COL + seg * 64, ra);
+          tmem_ld_32x32b_x32(lane_base + T2_O_COL + seg * 64 + 32, rb);
+          tmem_ld_wait_for(ra);
+          tmem_ld_wait_for(rb);
+          auto stage8 = [&](const uint32_t* r, int ch) {
+            uint4 u;
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
+            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
+            u.x = *reinterpret_cast<uint32_t*>(&p0);
+            u.y = *reinterpret_cast<uint32_t*>(&p1);
+            u.z = *reinterpret_cast<uint32_t*>(&p2);
+            u.w = *reinterpret_cast<uint32_t*>(&p3);
+            *reinterpret_cast<uint4*>(stage + (lane & 15) * 128 + ((ch ^ (lane & 7)) << 4)) = u;
+          };
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            if ((lane >> 4) == half) {
+#pragma unroll
+              for (int c = 0; c < 4; ++c) stage8(&ra[c * 8], c);
+#pragma unroll
+              for (int c = 0; c < 4; ++c) stage8(&rb[c * 8], 4 + c);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int rl = i * 4 + sub;  // row within this half
+              const int r = half * 16 + rl;
+              if (r < out_rows) {
+                const uint4 u = *reinterpret_cast<const uint4*>(stage + rl * 128 + ((chunk ^ (rl & 7)) << 4));
+                *reinterpret_cast<uint4*>(out_dst + static_cast<size_t>(r) * out_stride + seg * 64 + chunk * 8) = u;
+              }
+            }
+            __syncwarp();
+          }
+        }
+      }
+      out_pending = false;
+    };
+    const float2 scale2 = make_float2(scale_log2, scale_log2);
+    const int row_local = warp * 32 + lane;
+    T2_PROF_DECL(0)
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      const AttnTile t = tiles[item / n_heads];
+      const int h = item % n_heads;
+      const int L = t.seq_len;
+      const int n_kv = t2_n_kv<CAUSAL>(L, t.q_start);
+      // a warp whose 32 query rows all lie past the end of the sequence has nothing to compute
+      const bool warp_active = t.q_start + warp * 32 < L;
+      // Softmax reference point of this row (raw score units) and running denominator. The reference is
+      // NOT the running maximum: it is only moved when a score exceeds it by more than T2_LAZY_LOG2 (in
+      // log2 units), so nearly every step leaves O in tensor memory untouched; exp2 then yields values up
+      // to 2^T2_LAZY_LOG2, which numerator and denominator share.
+      float m_ref = 0.f, l_run = 0.f;
+
+      for (int it = 0; it < n_kv; ++it, ++gi) {
+        const int kv0 = it * T2_BKV;
+        const int n_valid = min(T2_BKV, L - kv0);
+        const int n_eff = (n_valid + 15) & ~15;
+        const int n_chunks = (n_eff + 31) >> 5;
+        // Causal: only the diagonal tile (kv0 == q_start) is cut, to keys <= the row's own position.
+        const bool diag = CAUSAL && kv0 == t.q_start;
+        const int lim = diag ? min(n_valid, row_local + 1) : n_valid;         // this row's valid keys
+        const int lim_lo = diag ? min(n_valid, warp * 32 + 1) : n_valid;      // smallest over the warp
+        const int lim_hi = diag ? min(n_valid, warp * 32 + 32) : n_valid;     // largest over the warp
+        const uint32_t s_base = lane_base + T2_S_COL + (gi & 1u) * 128u;
+        if (!mbar_wait(&bar_s[gi & 1u], (gi >> 1) & 1u)) failed = true;
+        // S runs two steps ahead, so bar_s does not pace a warp that has nothing to compute: it must not
+        // arrive on bar_p for this step before the previous step's phase has completed (a warp that
+        // computes is paced by its wait on bar_pv below).
+        if (!warp_active && gi > 0 && !mbar_wait(bar_p, (gi - 1) & 1u)) failed = true;
+        failed = __any_sync(0xffffffffu, failed);  // the warp leaves together
+        if (failed) break;
+        tc_fence_after_sync();
+        T2_PROF(0);  // wait for S
+
+        if (warp_active) {
+          uint32_t ra[32], rb[32];
+          uint32_t pa[16], pb[16];
+          float mx0, mx1, l0;
+          float2 lsum;
+          float2 negm2;
+          // One 32-key chunk: p = exp2(s * scale - m_ref * scale) as bf16 pairs; also tracks the true row
+          // maximum. Chunks that are valid for the whole warp take the unmasked path, chunks past every
+          // row's limit are zeros.
+          auto chunk = [&](const uint32_t (&r)[32], uint32_t (&pk)[16], int c) {
+            if (c + 32 <= lim_lo) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                mx0 = t2_max3(mx0, __uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                mx1 = t2_max3(mx1, __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+              }
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                // packed fp32 pair: one FFMA2 / FADD2 per two keys
+                const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), scale2, negm2);
+                const float2 pp = make_float2(t2_ex2(x.x), t2_ex2(x.y));
+                lsum = __fadd2_rn(lsum, pp);
+                __nv_bfloat162 b = __floats2bfloat162_rn(pp.x, pp.y);
+                pk[j >> 1] = *reinterpret_cast<uint32_t*>(&b);
+              }
+            } else if (c >= lim_hi) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) pk[j] = 0u;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                const bool v0 = c + j < lim, v1 = c + j + 1 < lim;
+                const float s0 = __uint_as_float(r[j]), s1 = __uint_as_float(r[j + 1]);
+                mx0 = fmaxf(mx0, v0 ? s0 : -INFINITY);
+                mx1 = fmaxf(mx1, v1 ? s1 : -INFINITY);
+                const float p0 = v0 ? t2_ex2(fmaf(s0, scale_log2, negm2.x)) : 0.f;
+                const float p1 = v1 ? t2_ex2(fmaf(s1, scale_log2, negm2.x)) : 0.f;
+                l0 += p0 + p1;
+                __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+                pk[j >> 1] = *reinterpret_cast<uint32_t*>(&b);
+              }
+            }
+          };
+          auto store_p = [&](const uint32_t (&pk)[16], int c) { tmem_st_32x32b_x16(lane_base + T2_P_COL + (c >> 1), pk); };
+          auto reset_sums = [&]() {
+            mx0 = mx1 = -INFINITY;
+            l0 = 0.f;
+            lsum = make_float2(0.f, 0.f);
+            negm2 = make_float2(-m_ref * scale_log2, -m_ref * scale_log2);
+          };
+
+          tmem_ld_32x32b_x32(s_base, ra);
+          tmem_ld_wait_for(ra);
+          if (it == 0) {
+            // first key tile of the row: the reference point is the maximum of its first 32 valid keys
+            float e0 = -INFINITY, e1 = -INFINITY;
+            if (32 <= lim_lo) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                e0 = t2_max3(e0, __uint_as_float(ra[j]), __uint_as_float(ra[j + 1]));
+                e1 = t2_max3(e1, __uint_as_float(ra[j + 2]), __uint_as_float(ra[j + 3]));
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) e0 = fmaxf(e0, (j < lim) ? __uint_as_float(ra[j]) : -INFINITY);
+            }
+            m_ref = fmaxf(e0, e1);
+          }
+          reset_sums();
+          // The load of chunk c + 1 is in flight while chunk c is computed. The first two chunks are held
+          // in registers until P V of the previous step has read the P columns; by then that is normally over.
+          if (n_chunks > 1) tmem_ld_32x32b_x32(s_base + 32, rb);
+          chunk(ra, pa, 0);
+          if (n_chunks > 1) {
+            tmem_ld_wait_for(rb);
+            if (n_chunks > 2) tmem_ld_32x32b_x32(s_base + 64, ra);
+            chunk(rb, pb, 32);
+          }
+          T2_PROF(1);  // first two chunks
+          if (gi > 0 && !__all_sync(0xffffffffu, mbar_wait(bar_pv, (gi - 1) & 1u))) failed = true;
+          T2_PROF(2);  // wait for the previous P V
+          if (!failed) {
+            store_p(pa, 0);
+            if (n_chunks > 1) store_p(pb, 32);
+            if (n_chunks > 2) {
+              tmem_ld_wait_for(ra);
+              if (n_chunks > 3) tmem_ld_32x32b_x32(s_base + 96, rb);
+              chunk(ra, pa, 64);
+              store_p(pa, 64);
+              if (n_chunks > 3) {
+                tmem_ld_wait_for(rb);
+                chunk(rb, pb, 96);
+                store_p(pb, 96);
+              }
+            }
+            float alpha = 1.f;
+            const float mx = fmaxf(mx0, mx1);
+            const bool move_ref = (mx - m_ref) * scale_log2 > T2_LAZY_LOG2;
+            if (__any_sync(0xffffffffu, move_ref)) {
+              // Rare: some row of this warp met a score far above its reference point. Move the reference
+              // to the row maximum, redo this tile's P with it and rescale what O and l hold so far.
+              if (move_ref) {
+                alpha = t2_ex2((m_ref - mx) * scale_log2);
+                m_ref = mx;
+              }
+              reset_sums();
+              for (int c = 0; c < n_eff; c += 32) {
+                tmem_ld_32x32b_x32(s_base + c, ra);
+                tmem_ld_wait_for(ra);
+                chunk(ra, pa, c);
+                store_p(pa, c);
+              }
+              if (it > 0) {
+                // P V of the previous step has finished (waited for above)
+                const float2 alpha2 = make_float2(alpha, alpha);
+#pragma unroll 1
+                for (int c = 0; c < D; c += 32) {
+                  tmem_ld_32x32b_x32(lane_base + T2_O_COL + c, ra);
+                  tmem_ld_wait_for(ra);
+#pragma unroll
+                  for (int j = 0; j < 32; j += 2) {
+                    const float2 o = __fmul2_rn(make_float2(__uint_as_float(ra[j]), __uint_as_float(ra[j + 1])), alpha2);
+                    ra[j] = __float_as_uint(o.x);
+                    ra[j + 1] = __float_as_uint(o.y);
+                  }
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) pa[j] = ra[j];
+                  tmem_st_32x32b_x16(lane_base + T2_O_COL + c, pa);
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) pb[j] = ra[16 + j];
+                  tmem_st_32x32b_x16(lane_base + T2_O_COL + c + 16, pb);
+                }
+              }
+            }
+            l_run = l_run * alpha + (l0 + (lsum.x + lsum.y));
+            T2_PROF(3);  // last two chunks
+            tmem_st_wait();
+          }
+        }
+        T2_PROF(4);  // store wait
+        if (failed) break;  // warp-uniform: set from __all_sync
+        if (out_pending) {
+          write_pending();  // previous item's rows; its O is overwritten only after the arrival below
+          if (failed) break;
+          T2_PROF(5);  // output
+        }
+        tc_fence_before_sync();
+        mbar_arrive(bar_p);  // this thread's P row is in tensor memory and its reads of S are done
+      }
+      if (failed) break;
+      out_pending = true;
+      out_inv = 1.f / l_run;
+      out_rows = warp_active ? min(32, L - (t.q_start + warp * 32)) : 0;
+      out_dst = out + static_cast<size_t>(t.seq_start + t.q_start + warp * 32) * out_stride + h * D;
+    }
+    if (!failed && out_pending) write_pending();
+    T2_PROF_FLUSH(0);
+    if (failed && lane == 0) atomicExch(err_flag, 4);
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, T2_TMEM_COLS);
+  }
+}
+
+#ifdef B2_ATT_PROFILE
+extern "C" int b200emb_debug_att2_prof(long long* out16, int reset) {
+  if (out16) cudaMemcpyFromSymbol(out16, g_att2_prof, sizeof(long long) * 16);
+  if (reset) {
+    long long z[16] = {};
+    cudaMemcpyToSymbol(g_att2_prof, z, sizeof(z));
+  }
+  return 0;
+}
+#endif
+
+template <int D, bool CAUSAL>
+static int t2_init_one() {
+  B2_CUDA_CHECK(cudaFuncSetAttribute(attn_tc2_kernel<D, CAUSAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     T2Cfg<D>::SMEM_BYTES));
+  return B200EMB_OK;
+}
+
+int attention_tc2_init_device() {
+  int rc = t2_init_one<64, false>();
+  if (!rc) rc = t2_init_one<64, true>();
+  if (!rc) rc = t2_init_one<128, false>();
+  if (!rc) rc = t2_init_one<128, true>();
+  return rc;
+}
+
+template <int D, bool CAUSAL>
+static void t2_launch(const CUtensorMap& tm, void* out, const AttnTile* d_tiles, int n_items, int n_heads, int n_kv_heads,
+                      int grid, int* err_flag, cudaStream_t stream) {
+  const float scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(D));
+  attn_tc2_kernel<D, CAUSAL><<<grid, T2_THREADS, T2Cfg<D>::SMEM_BYTES, stream>>>(
+      tm, reinterpret_cast<__nv_bfloat16*>(out), d_tiles, n_items, n_heads, n_kv_heads, scale_log2, err_flag);
+}
+
+int launch_attention_tc2(const void* qkv, void* out, const AttnTile* d_tiles, int n_tiles, int n_tokens, int n_heads,
+                         int n_kv_heads, int head_dim, int causal, int sm_count, int* err_flag, cudaStream_t stream) {
+  if (n_tiles <= 0) return B200EMB_OK;
+  if (head_dim != 64 && head_dim != 128)
+    return set_error(B200EMB_ERR_UNSUPPORTED, "tensor-memory attention is built for head_dim 64 and 128");
+  if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_heads > 65535)
+    return set_error(B200EMB_ERR_INVALID, "attention: bad head counts %d / %d", n_heads, n_kv_heads);
+  CUtensorMap tm;
+  const uint64_t width = static_cast<uint64_t>(n_heads + 2 * n_kv_heads) * head_dim;
+  int rc = make_tmap_bf16_2d(&tm, qkv, static_cast<uint64_t>(n_tokens), width, 128);
+  if (rc) return rc;
+  const long long n_items = static_cast<long long>(n_tiles) * n_heads;
+  if (n_items > 0x7fffffffLL) return set_error(B200EMB_ERR_UNSUPPORTED, "attention: too many tiles");
+  const int grid = static_cast<int>(n_items < sm_count ? n_items : sm_count);
+  const int ni = static_cast<int>(n_items);
+  if (head_dim == 64) {
+    if (causal) t2_launch<64, true>(tm, out, d_tiles, ni, n_heads, n_kv_heads, grid, err_flag, stream);
+    else t2_launch<64, false>(tm, out, d_tiles, ni, n_heads, n_kv_heads, grid, err_flag, stream);
+  } else {
+    if (causal) t2_launch<128, true>(tm, out, d_tiles, ni, n_heads, n_kv_heads, grid, err_flag, stream);
+    else t2_launch<128, false>(tm, out, d_tiles, ni, n_heads, n_kv_heads, grid, err_flag, stream);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "attention launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
+}  // namespace b2

@@ -64,15 +64,21 @@ struct AttnTile {
 // Returns the number of tiles; `tiles` may be null to only count.
 int attention_build_tiles_q(const int32_t* h_cu_seqlens, int n_seqs, int bq, AttnTile* tiles);
 // Query-tile height of the kernel that serves (head_dim, causal): 128 for the tensor-memory
-// kernel (head_dim 64, bidirectional), 64 for the mma.sync kernel.
+// kernels (head_dim 64 and 128), 64 for the mma.sync kernel.
 int attention_tile_rows(int head_dim, int causal);
 int launch_attention(const void* qkv, void* out, const AttnTile* d_tiles, int n_tiles, int n_heads, int n_kv_heads,
                      int head_dim, int causal, cudaStream_t stream);
 int attention_init_device();
-// tensor-memory (tcgen05) kernel, head_dim 64, bidirectional (attention_tc.cu)
+// Tensor-memory (tcgen05) kernels, 128-row query tiles. launch_attention_tc picks the kernel:
+// head_dim 64 bidirectional -> two CTAs per SM (attention_tc.cu); head_dim 128, or causal -> one CTA per
+// SM with double-buffered S (attention_tc2.cu). variant 1 forces the latter for every supported shape.
 int launch_attention_tc(const void* qkv, void* out, const AttnTile* d_tiles, int n_tiles, int n_tokens, int n_heads,
-                        int n_kv_heads, int head_dim, int sm_count, int* err_flag, cudaStream_t stream);
+                        int n_kv_heads, int head_dim, int causal, int variant, int sm_count, int* err_flag,
+                        cudaStream_t stream);
+int launch_attention_tc2(const void* qkv, void* out, const AttnTile* d_tiles, int n_tiles, int n_tokens, int n_heads,
+                         int n_kv_heads, int head_dim, int causal, int sm_count, int* err_flag, cudaStream_t stream);
 int attention_tc_init_device();
+int attention_tc2_init_device();
 
 // ---- block-format weight quantisers (quant.cu) ----
 // w bf16 [rows, cols] -> q (packed elements), scales (one byte per block, row-major [rows, cols / block]);

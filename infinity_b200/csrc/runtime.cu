@@ -43,6 +43,7 @@ int kernels_init_device() {
   int rc = gemm_init_device();
   if (!rc) rc = attention_init_device();
   if (!rc) rc = attention_tc_init_device();
+  if (!rc) rc = attention_tc2_init_device();
   if (!rc) rc = gemm_mxfp8_init_device();
   if (!rc) rc = moe_init_device();
   if (rc) return rc;
@@ -610,7 +611,11 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
       }
       {
         KernelScope ks(c, B200EMB_KCLASS_ATTN);
-        rc = launch_attention(c->qkv, c->ctx, c->d_tiles, n_tiles, d.n_heads, d.n_kv_heads, d.head_dim, 1, c->stream);
+        if (attention_tile_rows(d.head_dim, 1) == 128)
+          rc = launch_attention_tc(c->qkv, c->ctx, c->d_tiles, n_tiles, T, d.n_heads, d.n_kv_heads, d.head_dim, 1, 0,
+                                   c->sm_count, c->d_err, c->stream);
+        else
+          rc = launch_attention(c->qkv, c->ctx, c->d_tiles, n_tiles, d.n_heads, d.n_kv_heads, d.head_dim, 1, c->stream);
         if (rc) return rc;
       }
       rc = gemm(c, d.weight_format, c->ctx, L.o_w, nullptr, c->y, T, H, d.n_heads * d.head_dim, EPI_BIAS);
@@ -646,8 +651,8 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
     {
       KernelScope ks(c, B200EMB_KCLASS_ATTN);
       if (attention_tile_rows(d.head_dim, 0) == 128)
-        rc = launch_attention_tc(c->qkv, c->ctx, c->d_tiles, n_tiles, T, d.n_heads, d.n_kv_heads, d.head_dim, c->sm_count,
-                                 c->d_err, c->stream);
+        rc = launch_attention_tc(c->qkv, c->ctx, c->d_tiles, n_tiles, T, d.n_heads, d.n_kv_heads, d.head_dim, 0, 0,
+                                 c->sm_count, c->d_err, c->stream);
       else
         rc = launch_attention(c->qkv, c->ctx, c->d_tiles, n_tiles, d.n_heads, d.n_kv_heads, d.head_dim, 0, c->stream);
       if (rc) return rc;
@@ -1364,6 +1369,7 @@ int b200emb_op_attention(const void* qkv, void* out, const int32_t* d_cu_seqlens
   if (rc) return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int force_legacy = (causal >> 8) & 1;  // bit 8: use the mma.sync kernel whatever the shape (tests)
+  const int variant = (causal >> 9) & 1;       // bit 9: one-CTA-per-SM tensor-memory kernel whatever the shape
   causal &= 1;
   const bool use_tc = !force_legacy && attention_tile_rows(head_dim, causal) == 128;
   const int bq = use_tc ? 128 : 64;
@@ -1380,7 +1386,9 @@ int b200emb_op_attention(const void* qkv, void* out, const int32_t* d_cu_seqlens
   {
     int sms = 0;
     rc = current_sm_count(&sms);
-    if (!rc) rc = launch_attention_tc(qkv, out, d_tiles, n_tiles, n_tokens, n_heads, n_kv_heads, head_dim, sms, d_err, s);
+    if (!rc)
+      rc = launch_attention_tc(qkv, out, d_tiles, n_tiles, n_tokens, n_heads, n_kv_heads, head_dim, causal, variant, sms,
+                               d_err, s);
   }
   else
     rc = launch_attention(qkv, out, d_tiles, n_tiles, n_heads, n_kv_heads, head_dim, causal, s);

@@ -117,9 +117,10 @@ def _attention_ref(qkv, cu, nh, nkv, d, causal):
 
 
 @pytest.mark.parametrize("d,nh,nkv", [(32, 12, 12), (64, 16, 16), (64, 4, 4), (128, 8, 2), (128, 4, 4)])
-@pytest.mark.parametrize("causal", [0, 1, 0x100])  # 0x100: bidirectional on the mma.sync kernel
+# 0x100: on the mma.sync kernel; 0x200: on the one-CTA-per-SM tensor-memory kernel
+@pytest.mark.parametrize("causal", [0, 1, 0x100, 0x101, 0x200])
 def test_attention_varlen(lib, d, nh, nkv, causal):
-    lens = [1, 7, 64, 65, 128, 200, 63, 512, 33, 300, 129, 16, 17, 384]
+    lens = [1, 7, 64, 65, 128, 200, 63, 512, 33, 300, 129, 16, 17, 384, 1000, 257]
     cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
     T = int(cu[-1])
     g = torch.Generator(device="cuda").manual_seed(d + nh + causal)
@@ -136,12 +137,13 @@ def test_attention_varlen(lib, d, nh, nkv, causal):
 
 
 @pytest.mark.parametrize("kind", ["wide", "rising"])
-def test_attention_wide_score_range(lib, kind):
+@pytest.mark.parametrize("d,flags", [(64, 0), (64, 0x200), (64, 1), (128, 0), (128, 1)])
+def test_attention_wide_score_range(lib, kind, d, flags):
     """Scores far above a row's first keys: the head_dim-64 kernel keeps a per-row reference point
     (maximum of the first 32 keys) and must move it, redo P and rescale O when a later score exceeds
     it by more than 2^10. 'wide' draws scores with a standard deviation of 12; 'rising' makes every
     later key score higher than all earlier ones, so the reference moves on every key tile."""
-    nh, d = 4, 64
+    nh = 4
     lens = [512, 130, 257, 31, 33, 384, 96]
     cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
     T = int(cu[-1])
@@ -160,8 +162,8 @@ def test_attention_wide_score_range(lib, kind):
     d_cu = torch.from_numpy(cu).cuda()
     torch.cuda.synchronize()
     _lib.check(lib.b200emb_op_attention(qkv.data_ptr(), out.data_ptr(), d_cu.data_ptr(), cu.ctypes.data, len(lens), T,
-                                        nh, nh, d, 0, _stream()))
-    ref = _attention_ref(qkv, cu, nh, nh, d, 0)
+                                        nh, nh, d, flags, _stream()))
+    ref = _attention_ref(qkv, cu, nh, nh, d, flags & 1)
     assert not torch.isnan(out.float()).any()
     err = (out.float() - ref).abs().max().item()
     assert err < 3e-2, err
