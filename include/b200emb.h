@@ -57,6 +57,12 @@ extern "C" {
 #define B200EMB_POOL_CLS 0  /* row cu_seqlens[i] */
 #define B200EMB_POOL_MEAN 1 /* mean of rows cu_seqlens[i] .. cu_seqlens[i+1]-1, fp32 accumulation */
 #define B200EMB_POOL_LAST 2 /* row cu_seqlens[i+1]-1 */
+/* No pooling: one fp32 output row per TOKEN, in packed order (sequence i owns rows cu_seqlens[i] ..
+ * cu_seqlens[i+1]-1), the reference's ColBERT mode (sentence_transformer.py:87-90 switches normalisation
+ * off, :125-131 returns token_embeddings + attention_mask, :146-155 drops the padded rows: the ragged
+ * layout has none). The output buffer of b200emb_forward / b200emb_forward_device then has n_tokens rows.
+ * Only with B200EMB_HEAD_NONE. */
+#define B200EMB_POOL_TOKENS 3
 
 /* b200emb_model_desc.head */
 #define B200EMB_HEAD_NONE 0       /* output = pooled (optionally L2-normalised) hidden state, [n_seqs, hidden] */

@@ -15,7 +15,7 @@ N_KCLASS = 8
 KCLASS_NAMES = ["embed", "gemm", "attention", "norm", "pool", "other", "k6", "k7"]
 
 ARCH = {"bert": 0, "xlmr": 1, "moe": 2, "decoder": 3}
-POOL = {"cls": 0, "mean": 1, "last": 2}
+POOL = {"cls": 0, "mean": 1, "last": 2, "tokens": 3}
 HEAD = {"none": 0, "classifier": 1}
 WFMT = {"bf16": 0, "mxfp8": 1, "nvfp4": 2}
 EPI = {"bias": 0, "gelu": 1, "tanh": 2, "swiglu": 3}

@@ -63,8 +63,14 @@ class _B200Backend:
             self._ring[slot] = buf
         return buf[:n_seqs]
 
-    def encode_core(self, features: PackedFeatures) -> np.ndarray:
-        """runs the forward on the GPU(s); returns ``[n_seqs, out_dim]`` float32"""
+    def encode_core(self, features: PackedFeatures):
+        """runs the forward on the GPU(s); returns ``[n_seqs, out_dim]`` float32. In ColBERT mode
+        (``spec.pooling == "tokens"``) returns the token rows together with the sequence offsets,
+        as the reference hands token_embeddings + attention_mask on (sentence_transformer.py:125-131)."""
+        if self.spec.pooling == "tokens":
+            out = self._result_buffer(features.n_tokens)
+            self.model.forward_arrays(features.input_ids, features.cu_seqlens, features.token_type_ids, out=out)
+            return {"token_embeddings": out, "cu_seqlens": np.array(features.cu_seqlens, dtype=np.int64)}
         out = self._result_buffer(features.n_seqs)
         self.model.forward_arrays(features.input_ids, features.cu_seqlens, features.token_type_ids, out=out)
         return out
@@ -120,9 +126,13 @@ class B200Embedder(_B200Backend):
         """tokenises and packs the batch (no padding)"""
         return self.tokenizer.encode(sentences)
 
-    def encode_post(self, embedding: np.ndarray, skip_quanitzation: bool = True) -> np.ndarray:
+    def encode_post(self, embedding, skip_quanitzation: bool = True):
         """float32 rows, already pooled and L2-normalised on the device (the reference does
-        this step on the CPU: sentence_transformer.py:142-145)."""
+        this step on the CPU: sentence_transformer.py:142-145). ColBERT mode: one ``[L_i, D]``
+        array per sequence (sentence_transformer.py:146-155; there are no padded rows to drop)."""
+        if isinstance(embedding, dict):
+            rows, cu = embedding["token_embeddings"], embedding["cu_seqlens"]
+            return [np.array(rows[cu[i]: cu[i + 1]], dtype=np.float32) for i in range(len(cu) - 1)]
         return embedding
 
 

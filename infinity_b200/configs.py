@@ -33,7 +33,7 @@ class ModelSpec:
     n_experts: int = 0
     top_k: int = 0
     moe_every: int = 0
-    pooling: str = "cls"          # cls | mean | last
+    pooling: str = "cls"          # cls | mean | last | tokens (one output row per token: ColBERT mode)
     normalize: bool = True
     head: str = "none"            # none | classifier
     n_labels: int = 0

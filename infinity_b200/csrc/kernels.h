@@ -116,6 +116,9 @@ int launch_widen(const void* x, float* out, size_t n_elems, cudaStream_t stream)
 // rotates the first n_rot_heads heads (queries then keys) of every qkv row in place; cos_sin = [max_pos, head_dim/2] (cos, sin) pairs
 int launch_rope(void* qkv, const int32_t* d_cu, int n_seqs, int n_tokens, int n_rot_heads, int row_width,
                 int head_dim, const float* cos_sin, cudaStream_t stream);
+// no pooling: every bf16 hidden row -> one fp32 output row (optionally L2-normalised)
+int launch_token_rows(const void* x, int n_tokens, int hidden, int normalize, float* out, int64_t out_row_stride,
+                      cudaStream_t stream);
 int launch_pool(const void* x, const int32_t* d_cu, int n_seqs, int hidden, int pooling, int normalize, void* out,
                 int64_t out_row_stride, int out_bf16, cudaStream_t stream);
 // logits[i, l] = dot(x[i, :], W[l, :]) + b[l]; x bf16 [n, hidden], W bf16 [n_labels, hidden], out fp32.

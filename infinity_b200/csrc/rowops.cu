@@ -641,6 +641,61 @@ int launch_rope(void* qkv, const int32_t* d_cu, int n_seqs, int n_tokens, int n_
   return B200EMB_OK;
 }
 
+// One warp per token row: bf16 hidden state -> fp32 output row, optionally divided by max(||row||, 1e-12).
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+token_rows_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int hidden, int normalize,
+                  float* __restrict__ out, int64_t out_row_stride) {
+  const int lane = threadIdx.x & 31;
+  const int n_chunks = hidden >> 3;
+  const int warps_total = gridDim.x * ROW_WARPS;
+  for (int t = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5); t < n_tokens; t += warps_total) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * hidden);
+    float scale = 1.f;
+    if (normalize) {
+      float ss = 0.f;
+      for (int c = lane; c < n_chunks; c += 32) {
+        const uint4 u = __ldg(src + c);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h2[j]);
+          ss += f.x * f.x + f.y * f.y;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      scale = 1.f / fmaxf(sqrtf(ss), 1e-12f);
+    }
+    float* dst = out + static_cast<size_t>(t) * out_row_stride;
+    for (int c = lane; c < n_chunks; c += 32) {
+      const uint4 u = __ldg(src + c);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h2[j]);
+        dst[c * 8 + 2 * j] = f.x * scale;
+        dst[c * 8 + 2 * j + 1] = f.y * scale;
+      }
+    }
+  }
+}
+
+int launch_token_rows(const void* x, int n_tokens, int hidden, int normalize, float* out, int64_t out_row_stride,
+                      cudaStream_t stream) {
+  if (n_tokens <= 0) return B200EMB_OK;
+  if (hidden <= 0 || (hidden % 8) != 0) return set_error(B200EMB_ERR_UNSUPPORTED, "token rows: hidden size %d unsupported", hidden);
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int full = (n_tokens + ROW_WARPS - 1) / ROW_WARPS;
+  const int grid = full < sms * 8 ? full : sms * 8;
+  token_rows_kernel<<<grid, ROW_WARPS * 32, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), n_tokens, hidden,
+                                                         normalize, out, out_row_stride);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "token rows launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
 int launch_pool(const void* x, const int32_t* d_cu, int n_seqs, int hidden, int pooling, int normalize, void* out,
                 int64_t out_row_stride, int out_bf16, cudaStream_t stream) {
   if (n_seqs <= 0) return B200EMB_OK;

@@ -244,17 +244,21 @@ static int ensure_capacity(b200emb_handle* h, DeviceCtx* c, int n_tokens, int n_
     }
     if (!rc) rc = host_alloc(&c->h_ids, T);
     if (!rc) rc = host_alloc(&c->h_types, T);
+    if (d.pooling == B200EMB_POOL_TOKENS) {  // one output row per token
+      if (!rc) rc = dev_alloc(&c->d_out, T * (size_t)h->out_dim);
+      if (!rc) rc = host_alloc(&c->h_out, T * (size_t)h->out_dim);
+    }
     if (rc) return rc;
     c->cap_tokens = (int)T;
   }
   if (n_seqs > c->cap_seqs) {
     const size_t B = (size_t)std::max(n_seqs, 256);
     if (!rc) rc = dev_alloc(&c->d_cu, B + 1);
-    if (!rc) rc = dev_alloc(&c->d_out, B * (size_t)h->out_dim);
+    if (!rc && d.pooling != B200EMB_POOL_TOKENS) rc = dev_alloc(&c->d_out, B * (size_t)h->out_dim);
     if (!rc) rc = dev_alloc(&c->pooled, B * (size_t)d.hidden);
     if (!rc) rc = dev_alloc(&c->head_h, B * (size_t)d.hidden);
     if (!rc) rc = host_alloc(&c->h_cu, B + 1);
-    if (!rc) rc = host_alloc(&c->h_out, B * (size_t)h->out_dim);
+    if (!rc && d.pooling != B200EMB_POOL_TOKENS) rc = host_alloc(&c->h_out, B * (size_t)h->out_dim);
     if (rc) return rc;
     c->cap_seqs = (int)B;
   }
@@ -461,7 +465,9 @@ static int validate_desc(const b200emb_model_desc& d) {
   if (d.head_dim != 32 && d.head_dim != 64 && d.head_dim != 128) return set_error(B200EMB_ERR_UNSUPPORTED, "head_dim %d not in {32, 64, 128}", d.head_dim);
   if (d.n_heads * d.head_dim != d.hidden) return set_error(B200EMB_ERR_INVALID, "n_heads * head_dim must equal hidden");
   if (d.hidden % 8 || d.ffn % 8) return set_error(B200EMB_ERR_UNSUPPORTED, "hidden and ffn must be multiples of 8");
-  if (d.pooling < B200EMB_POOL_CLS || d.pooling > B200EMB_POOL_LAST) return set_error(B200EMB_ERR_INVALID, "unknown pooling %d", d.pooling);
+  if (d.pooling < B200EMB_POOL_CLS || d.pooling > B200EMB_POOL_TOKENS) return set_error(B200EMB_ERR_INVALID, "unknown pooling %d", d.pooling);
+  if (d.pooling == B200EMB_POOL_TOKENS && d.head != B200EMB_HEAD_NONE)
+    return set_error(B200EMB_ERR_INVALID, "per-token outputs need head = none");
   if (d.head == B200EMB_HEAD_CLASSIFIER && d.n_labels <= 0) return set_error(B200EMB_ERR_INVALID, "classifier head needs n_labels > 0");
   if (d.head != B200EMB_HEAD_NONE && d.head != B200EMB_HEAD_CLASSIFIER) return set_error(B200EMB_ERR_INVALID, "unknown head %d", d.head);
   if (d.pos_offset < 0 || d.pos_offset >= d.max_pos) return set_error(B200EMB_ERR_INVALID, "pos_offset out of range");
@@ -636,6 +642,7 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
       if (rc) return rc;
     }
     KernelScope ks(c, B200EMB_KCLASS_POOL);
+    if (d.pooling == B200EMB_POOL_TOKENS) return launch_token_rows(c->x, T, H, d.normalize, d_out, out_row_stride, c->stream);
     return launch_pool(c->x, d_cu, n_seqs, H, d.pooling, d.normalize, d_out, out_row_stride, 0, c->stream);
   }
   {
@@ -739,7 +746,10 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
   }
   if (d.head == B200EMB_HEAD_NONE) {
     KernelScope ks(c, B200EMB_KCLASS_POOL);
-    rc = launch_pool(c->x, d_cu, n_seqs, H, d.pooling, d.normalize, d_out, out_row_stride, 0, c->stream);
+    if (d.pooling == B200EMB_POOL_TOKENS)
+      rc = launch_token_rows(c->x, T, H, d.normalize, d_out, out_row_stride, c->stream);
+    else
+      rc = launch_pool(c->x, d_cu, n_seqs, H, d.pooling, d.normalize, d_out, out_row_stride, 0, c->stream);
     if (rc) return rc;
   } else {
     {
@@ -841,7 +851,8 @@ static void run_shard(b200emb_handle* h, DeviceCtx* c, const int32_t* ids, const
   }
   B2_TRY(cudaEventRecord(c->ev[2], s));
   B2_TRY(cudaMemcpy2DAsync(dst, sizeof(float) * dst_stride, c->d_out, sizeof(float) * h->out_dim,
-                           sizeof(float) * h->out_dim, n_seqs, cudaMemcpyDeviceToHost, s));
+                           sizeof(float) * h->out_dim,
+                           h->desc.pooling == B200EMB_POOL_TOKENS ? n_tokens : n_seqs, cudaMemcpyDeviceToHost, s));
   B2_TRY(cudaMemcpyAsync(c->h_err, c->d_err, sizeof(int), cudaMemcpyDeviceToHost, s));
   B2_TRY(cudaEventRecord(c->ev[3], s));
   B2_TRY(cudaStreamSynchronize(s));
@@ -1159,8 +1170,16 @@ int b200emb_forward(b200emb_handle* h, const int32_t* input_ids, const int32_t* 
         run_shard(h, c, c->h_ids, token_type_ids != nullptr ? c->h_types : nullptr, c->h_cu, (int)mem.size(), tok,
                   c->h_out, h->out_dim, per_kernel, r);
         if (r->rc == 0) {
-          for (size_t k = 0; k < mem.size(); ++k)
-            memcpy(out + (size_t)mem[k] * out_row_stride, c->h_out + k * (size_t)h->out_dim, sizeof(float) * h->out_dim);
+          if (h->desc.pooling == B200EMB_POOL_TOKENS) {
+            // token rows: sequence mem[k] owns batch rows cu_seqlens[i] .. and shard rows h_cu[k] ..
+            for (size_t k = 0; k < mem.size(); ++k)
+              for (int t = 0; t < lens[mem[k]]; ++t)
+                memcpy(out + (size_t)(cu_seqlens[mem[k]] + t) * out_row_stride,
+                       c->h_out + (size_t)(c->h_cu[k] + t) * h->out_dim, sizeof(float) * h->out_dim);
+          } else {
+            for (size_t k = 0; k < mem.size(); ++k)
+              memcpy(out + (size_t)mem[k] * out_row_stride, c->h_out + k * (size_t)h->out_dim, sizeof(float) * h->out_dim);
+          }
         }
       });
     }

@@ -89,15 +89,17 @@ class B200Model:
     def forward_arrays(self, input_ids: np.ndarray, cu_seqlens: np.ndarray,
                        token_type_ids: Optional[np.ndarray] = None, out: Optional[np.ndarray] = None,
                        per_kernel: bool = False) -> np.ndarray:
-        """Host arrays in, ``[n_seqs, out_dim]`` float32 out (row i = sequence i)."""
+        """Host arrays in, ``[n_seqs, out_dim]`` float32 out (row i = sequence i); with
+        ``pooling == "tokens"`` the result is ``[n_tokens, out_dim]`` in packed token order."""
         ids = np.ascontiguousarray(input_ids, dtype=np.int32)
         cu = np.ascontiguousarray(cu_seqlens, dtype=np.int32)
         tt = None if token_type_ids is None else np.ascontiguousarray(token_type_ids, dtype=np.int32)
         n_seqs = len(cu) - 1
         n_tokens = int(len(ids))
+        n_rows = n_tokens if self.spec.pooling == "tokens" else n_seqs
         if out is None:
-            out = np.empty((n_seqs, self.spec.out_dim), dtype=np.float32)
-        assert out.dtype == np.float32 and out.flags.c_contiguous and out.shape == (n_seqs, self.spec.out_dim)
+            out = np.empty((n_rows, self.spec.out_dim), dtype=np.float32)
+        assert out.dtype == np.float32 and out.flags.c_contiguous and out.shape == (n_rows, self.spec.out_dim)
         timing = _lib.Timing()
         timing.per_kernel = 1 if per_kernel else 0
         _lib.check(self._lib.b200emb_forward(

@@ -128,11 +128,36 @@ def forward_padded(spec, W, ids, mask, types=None) -> np.ndarray:
     if spec.head == "classifier":
         c = torch.tanh(h[:, 0] @ W["head.dense.w"].t() + W["head.dense.b"])
         return (c @ W["head.out.w"].t() + W["head.out.b"]).float().numpy()
+    if spec.pooling == "tokens":
+        raise ValueError("token-level outputs are ragged: use forward_tokens")
     pooled = P.POOLERS[spec.pooling](h.numpy(), mask.numpy())
     pooled = pooled.astype(np.float32)  # sentence_transformer.py:142: embeddings go to fp32 first
     if spec.normalize:
         pooled = P.normalize(pooled)
     return pooled.astype(np.float32)
+
+
+@torch.no_grad()
+def forward_tokens(spec, W, batch, batch_size: int = 32) -> np.ndarray:
+    """ColBERT mode (sentence_transformer.py:125-131, 146-155): the final hidden state of every real
+    token, float32, padded rows dropped; returned packed as [n_tokens, hidden] in batch order
+    (sequence i owns rows cu_seqlens[i] .. cu_seqlens[i+1]-1). L2-normalised per token only if
+    ``spec.normalize`` (the reference switches normalisation off in this mode)."""
+    seqs = batch.sequences()
+    cu = batch.cu_seqlens
+    types = None
+    if batch.token_type_ids is not None:
+        types = [batch.token_type_ids[cu[i]: cu[i + 1]] for i in range(batch.n_seqs)]
+    out = np.zeros((int(cu[-1]), spec.hidden), dtype=np.float32)
+    pad_id = 1 if spec.arch == "xlmr" else 0
+    for s in range(0, batch.n_seqs, batch_size):
+        idx = list(range(s, min(s + batch_size, batch.n_seqs)))
+        ids, mask, tt = pad_batch([seqs[i] for i in idx], None if types is None else [types[i] for i in idx], pad_id)
+        h = encoder_hidden(spec, W, ids, mask, tt if types is not None else None).float().numpy()
+        for k, i in enumerate(idx):
+            rows = h[k, : len(seqs[i])]
+            out[cu[i]: cu[i + 1]] = P.normalize(rows) if spec.normalize else rows
+    return out
 
 
 def forward_batch(spec, W, batch, batch_size: int = 32, sort: bool = True) -> np.ndarray:

@@ -46,6 +46,26 @@ def test_embedder_backend_pipeline(tmp_path):
     backend.model.close()
 
 
+def test_embedder_backend_colbert_mode(tmp_path):
+    """ColBERT mode through the backend: encode_post returns one [L_i, hidden] float32 array per
+    sentence, not normalised (sentence_transformer.py:87-90, 146-155)."""
+    spec = cf.tiny_spec("bert", pooling="tokens", normalize=False)
+    path, W = _weights(tmp_path, spec, 53)
+    backend = B200Embedder(spec=spec, weight_path=path, device_ids=(0,))
+    rng = np.random.default_rng(2)
+    lens = (5, 90, 17, 160, 1)
+    sentences = [_sentence(rng, n, spec.vocab) for n in lens]
+    out = backend.encode_post(backend.encode_core(backend.encode_pre(sentences)))
+    assert isinstance(out, list) and [o.shape for o in out] == [(n, spec.hidden) for n in lens]
+    batch = cf.pack([np.array(s.split(), dtype=np.int64) for s in sentences])
+    ref = enc.forward_tokens(spec, W, batch)
+    got = np.concatenate(out, axis=0)
+    assert got.dtype == np.float32 and cosines(got, ref).min() >= 0.999
+    eps, _, _ = backend.warmup(batch_size=4, n_tokens=16)
+    assert eps > 0
+    backend.model.close()
+
+
 def test_cross_encoder_and_classifier_backends(tmp_path):
     spec = cf.tiny_spec("xlmr")
     path, W = _weights(tmp_path, spec, 52)

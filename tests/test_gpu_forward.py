@@ -40,6 +40,31 @@ def test_tiny_encoder_matches_oracle(tmp_path, pooling, hidden, heads, hd):
     model.close()
 
 
+@pytest.mark.parametrize("normalize", [False, True])
+def test_token_level_outputs_match_oracle(tmp_path, normalize):
+    """ColBERT mode: one float32 row per real token, packed in batch order, normalisation off by
+    default as in the reference (sentence_transformer.py:87-90, 125-131, 146-155)."""
+    spec = cf.tiny_spec("bert", hidden=256, n_heads=4, n_kv_heads=4, head_dim=64, ffn=512, pooling="tokens",
+                        normalize=normalize)
+    model, W = build_model(tmp_path, spec, 17, perturb=True)
+    batch = cf.random_batch(spec, [1, 2, 9, 64, 65, 127, 128, 160, 33, 77], 5, with_types=True)
+    got = model.forward(batch)
+    ref = enc.forward_tokens(spec, W, batch)
+    assert got.shape == ref.shape == (batch.n_tokens, 256)
+    cos = cosines(got, ref)
+    assert cos.min() >= 0.999 and np.median(cos) >= COS_TOL, (cos.min(), np.median(cos))
+    if normalize:
+        np.testing.assert_allclose(np.linalg.norm(got, axis=1), 1.0, atol=1e-5)
+    else:
+        # magnitudes too: the rows are LayerNorm outputs rounded to bf16
+        assert np.abs(got - ref).max() <= 0.05 * np.abs(ref).max()
+    # a sequence's token rows do not depend on its neighbours
+    cu = batch.cu_seqlens
+    alone = model.forward(cf.pack([batch.sequences()[3]], [batch.token_type_ids[cu[3]:cu[4]]]))
+    assert np.array_equal(alone, got[cu[3]:cu[4]])
+    model.close()
+
+
 def test_tiny_reranker_matches_oracle(tmp_path):
     spec = cf.tiny_spec("xlmr")
     model, W = build_model(tmp_path, spec, 12, perturb=True)
@@ -183,6 +208,15 @@ def test_multi_device_handle_equals_single_device(tmp_path):
     assert np.array_equal(one[0], a[5])
     single.close()
     multi.close()
+    # token-level outputs: rows return to packed batch order
+    spec_t = cf.tiny_spec("bert", hidden=256, n_heads=4, n_kv_heads=4, head_dim=64, ffn=512, pooling="tokens",
+                          normalize=False)
+    single_t, _ = build_model(tmp_path, spec_t, 41, perturb=True, device_ids=(0,))
+    multi_t, _ = build_model(tmp_path, spec_t, 41, perturb=True, device_ids=tuple(range(n_dev)))
+    at, bt = single_t.forward(batch), multi_t.forward(batch)
+    assert at.shape == (batch.n_tokens, 256) and np.array_equal(at, bt)
+    single_t.close()
+    multi_t.close()
 
 
 def test_invalid_inputs_are_rejected(tmp_path):

@@ -168,3 +168,22 @@ def test_decoder_matches_transformers_qwen2():
     got = dec.decoder_hidden(spec, W, ids, mask)
     m = mask.bool()
     assert (got[m] - ref[m]).abs().max().item() < 5e-5
+
+
+def test_token_level_oracle_is_consistent_with_pooled_oracle():
+    """ColBERT-mode rows (sentence_transformer.py:125-131, 146-155) pooled by the in-tree mean /
+    cls statements give the sentence embeddings of the pooled path: the two oracle entry points
+    restate one forward."""
+    import dataclasses
+    spec = cf.tiny_spec("bert", hidden=64, n_heads=2, n_kv_heads=2, head_dim=32, ffn=128, pooling="mean")
+    W = {k: v.float() for k, v in cf.init_weights(spec, 5, perturb=True).items()}
+    batch = cf.random_batch(spec, [3, 17, 40, 1, 9], 2, with_types=True)
+    tok_spec = dataclasses.replace(spec, pooling="tokens", normalize=False)
+    rows = enc.forward_tokens(tok_spec, W, batch, batch_size=2)
+    assert rows.shape == (batch.n_tokens, 64) and rows.dtype == np.float32
+    for pooling in ("mean", "cls"):
+        pooled = OP.pool_ragged(rows, batch.cu_seqlens, pooling, True)
+        ref = enc.forward_batch(dataclasses.replace(spec, pooling=pooling), W, batch)
+        np.testing.assert_allclose(pooled, ref, atol=2e-6)
+    with pytest.raises(ValueError):
+        enc.forward_batch(tok_spec, W, batch)
