@@ -173,6 +173,37 @@ int b200emb_forward_device(b200emb_handle* h, const int32_t* d_input_ids, const 
                            const int32_t* d_cu_seqlens, const int32_t* h_cu_seqlens, int32_t n_seqs,
                            int32_t n_tokens, float* d_out, int64_t out_row_stride, b200emb_timing* timing);
 
+/* Output embedding precisions (reference: EmbeddingDtype, infinity_emb/primitives.py:145-158, applied by
+ * quant_embedding_decorator around encode_post, infinity_emb/transformer/quantization/interface.py:124-154,
+ * which calls sentence-transformers 3.3.1 quantization.quantize_embeddings). Per row x[0..dim):
+ *   INT8    (int8)  ((x - lo) / ((hi - lo) / 255) - 128), UINT8 (uint8) ((x - lo) / ((hi - lo) / 255)):
+ *           float64 arithmetic, truncation toward zero, then the low 8 bits of the integer;
+ *           lo = ranges[0, :], hi = ranges[1, :] (the calibration ranges, float64 [2, dim])
+ *   UBINARY bit j of byte k = (x[8k + j'] > 0) packed most significant bit first (numpy packbits);
+ *   BINARY  the same byte - 128 as int8. dim must be a multiple of 8. */
+#define B200EMB_EMB_FLOAT32 0
+#define B200EMB_EMB_INT8 1
+#define B200EMB_EMB_UINT8 2
+#define B200EMB_EMB_BINARY 3
+#define B200EMB_EMB_UBINARY 4
+
+/* b200emb_forward with the result rows quantised on the device before they are copied back (the
+ * reference quantises on the host after the copy): `out` receives n_seqs rows (n_tokens rows with
+ * B200EMB_POOL_TOKENS) of dim bytes (INT8 / UINT8) or dim / 8 bytes (BINARY / UBINARY), row stride
+ * out_row_stride_bytes; FLOAT32 gives b200emb_forward's rows (stride in bytes). h_ranges: host float64
+ * [2, dim], needed for INT8 / UINT8 only. The matryoshka slice of the reference (batch_handler.py:65-74)
+ * is applied by its caller to whatever rows come back, so it is not part of this call. */
+int b200emb_forward_quantized(b200emb_handle* h, const int32_t* input_ids, const int32_t* token_type_ids,
+                              const int32_t* cu_seqlens, int32_t n_seqs, int32_t n_tokens, int32_t precision,
+                              const double* h_ranges, void* out, int64_t out_row_stride_bytes,
+                              b200emb_timing* timing);
+
+/* The quantiser alone, on device buffers: x fp32 [n_rows, dim] (row stride x_row_stride floats),
+ * d_ranges device float64 [2, dim] (INT8 / UINT8), out device bytes (row stride out_row_stride_bytes). */
+int b200emb_op_quantize_embeddings(const float* x, int32_t n_rows, int32_t dim, int64_t x_row_stride,
+                                   int32_t precision, const double* d_ranges, void* out,
+                                   int64_t out_row_stride_bytes, void* stream);
+
 /* Token-balanced partition used by b200emb_forward, exposed for tests and for
  * callers that run one process per GPU: assigns sequence i (length lens[i]) to
  * shard_of[i] in [0, n_shards). Deterministic; ties go to the lower index. */

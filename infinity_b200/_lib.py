@@ -16,6 +16,9 @@ KCLASS_NAMES = ["embed", "gemm", "attention", "norm", "pool", "other", "k6", "k7
 
 ARCH = {"bert": 0, "xlmr": 1, "moe": 2, "decoder": 3}
 POOL = {"cls": 0, "mean": 1, "last": 2, "tokens": 3}
+# output embedding precisions (EmbeddingDtype, infinity_emb/primitives.py:145-158)
+EMB = {"float32": 0, "int8": 1, "uint8": 2, "binary": 3, "ubinary": 4}
+EMB_NUMPY = {"float32": "float32", "int8": "int8", "uint8": "uint8", "binary": "int8", "ubinary": "uint8"}
 HEAD = {"none": 0, "classifier": 1}
 WFMT = {"bf16": 0, "mxfp8": 1, "nvfp4": 2}
 EPI = {"bias": 0, "gelu": 1, "tanh": 2, "swiglu": 3}
@@ -71,6 +74,8 @@ SIGNATURES = {
     "b200emb_op_embed_ln": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, C.c_int32, C.c_int32, C.c_float, _P, _P]),
     "b200emb_op_add_ln": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_int32, C.c_float, _P, _P]),
     "b200emb_op_pool": (C.c_int, [_P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, C.c_int64, C.c_int32, _P]),
+    "b200emb_forward_quantized": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32, _P, _P, C.c_int64, C.POINTER(Timing)]),
+    "b200emb_op_quantize_embeddings": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int64, C.c_int32, _P, _P, C.c_int64, _P]),
 }
 
 _lib = None

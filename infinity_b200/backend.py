@@ -67,6 +67,14 @@ class _B200Backend:
         """runs the forward on the GPU(s); returns ``[n_seqs, out_dim]`` float32. In ColBERT mode
         (``spec.pooling == "tokens"``) returns the token rows together with the sequence offsets,
         as the reference hands token_embeddings + attention_mask on (sentence_transformer.py:125-131)."""
+        dtype = getattr(self, "embedding_dtype", "float32")
+        if dtype != "float32":
+            if self.spec.pooling == "tokens":
+                raise ValueError("output quantisation is for sentence embeddings")
+            if dtype in ("int8", "uint8") and self.calibration_ranges is None:
+                raise ValueError("int8 / uint8 embeddings need calibration ranges: call calibrate() first")
+            return self.model.forward_quantized(features.input_ids, features.cu_seqlens, dtype,
+                                                features.token_type_ids, self.calibration_ranges)
         if self.spec.pooling == "tokens":
             out = self._result_buffer(features.n_tokens)
             self.model.forward_arrays(features.input_ids, features.cu_seqlens, features.token_type_ids, out=out)
@@ -116,6 +124,27 @@ def _pinned_empty(rows: int, cols: int) -> np.ndarray:
 
 class B200Embedder(_B200Backend):
     capabilities = {"embed"}
+
+    def __init__(self, *, embedding_dtype: str = "float32", calibration_ranges: Optional[np.ndarray] = None, **kw):
+        """``embedding_dtype``: float32 | int8 | uint8 | binary | ubinary (EmbeddingDtype,
+        primitives.py:145-158). The reference quantises in a decorator around ``encode_post``
+        (quantization/interface.py:124-154) with ranges from a downloaded calibration text
+        (interface.py:73-121); here the rows are quantised on the device inside ``encode_core``,
+        and the ranges for int8 / uint8 come from ``calibration_ranges`` (float64 ``[2, dim]``) or
+        from :meth:`calibrate` on sentences the caller supplies."""
+        super().__init__(**kw)
+        self.embedding_dtype = getattr(embedding_dtype, "value", embedding_dtype)
+        self.calibration_ranges = calibration_ranges
+
+    def calibrate(self, sentences: List[str], batch_size: int = 8, percentile: float = 100) -> np.ndarray:
+        """Ranges as the reference computes them (interface.py:97-121): float32 embeddings of the
+        calibration sentences in batches of 8, then the [100 - p, p] percentiles per dimension."""
+        rows = []
+        for i in range(0, len(sentences), batch_size):
+            f = self.tokenizer.encode(sentences[i: i + batch_size])
+            rows.append(np.array(self.model.forward_arrays(f.input_ids, f.cu_seqlens, f.token_type_ids)))
+        self.calibration_ranges = np.percentile(np.concatenate(rows), [100 - percentile, percentile], axis=0)
+        return self.calibration_ranges
 
     def _warmup_inputs(self, batch_size, n_tokens):
         if isinstance(self.tokenizer, IdStringTokenizer):

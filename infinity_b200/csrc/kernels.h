@@ -116,6 +116,9 @@ int launch_widen(const void* x, float* out, size_t n_elems, cudaStream_t stream)
 // rotates the first n_rot_heads heads (queries then keys) of every qkv row in place; cos_sin = [max_pos, head_dim/2] (cos, sin) pairs
 int launch_rope(void* qkv, const int32_t* d_cu, int n_seqs, int n_tokens, int n_rot_heads, int row_width,
                 int head_dim, const float* cos_sin, cudaStream_t stream);
+// output embedding quantisation (int8 / uint8 with calibration ranges, binary / ubinary bit packing)
+int launch_quantize_embeddings(const float* x, int n_rows, int dim, int64_t x_row_stride, int precision,
+                               const double* d_ranges, void* out, int64_t out_row_stride_bytes, cudaStream_t stream);
 // no pooling: every bf16 hidden row -> one fp32 output row (optionally L2-normalised)
 int launch_token_rows(const void* x, int n_tokens, int hidden, int normalize, float* out, int64_t out_row_stride,
                       cudaStream_t stream);

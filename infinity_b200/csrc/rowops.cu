@@ -713,6 +713,58 @@ int launch_pool(const void* x, const int32_t* d_cu, int n_seqs, int hidden, int 
   return B200EMB_OK;
 }
 
+// Output embedding quantisation. One thread per 8 consecutive elements of a row (one packed byte
+// for the binary formats, eight bytes for the 8-bit formats).
+__global__ void quantize_embeddings_kernel(const float* __restrict__ x, int n_rows, int dim, int64_t x_row_stride,
+                                           int precision, const double* __restrict__ ranges,
+                                           uint8_t* __restrict__ out, int64_t out_row_stride_bytes) {
+  const int groups = dim >> 3;
+  const long long total = static_cast<long long>(n_rows) * groups;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(i / groups), g = static_cast<int>(i % groups);
+    const float* src = x + static_cast<size_t>(row) * x_row_stride + g * 8;
+    uint8_t* dst = out + static_cast<size_t>(row) * out_row_stride_bytes;
+    if (precision == B200EMB_EMB_BINARY || precision == B200EMB_EMB_UBINARY) {
+      unsigned bits = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) bits |= (src[j] > 0.f ? 1u : 0u) << (7 - j);  // most significant bit first
+      dst[g] = static_cast<uint8_t>(precision == B200EMB_EMB_BINARY ? bits - 128u : bits);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int c = g * 8 + j;
+        const double lo = ranges[c], hi = ranges[dim + c];
+        const double step = (hi - lo) / 255.0;
+        double v = (static_cast<double>(src[j]) - lo) / step;
+        if (precision == B200EMB_EMB_INT8) v -= 128.0;
+        // truncation toward zero, then the low 8 bits (what a C cast through a wide integer keeps)
+        const long long t = static_cast<long long>(v);
+        dst[c] = static_cast<uint8_t>(t & 0xff);
+      }
+    }
+  }
+}
+
+int launch_quantize_embeddings(const float* x, int n_rows, int dim, int64_t x_row_stride, int precision,
+                               const double* d_ranges, void* out, int64_t out_row_stride_bytes, cudaStream_t stream) {
+  if (n_rows <= 0) return B200EMB_OK;
+  if (precision < B200EMB_EMB_INT8 || precision > B200EMB_EMB_UBINARY)
+    return set_error(B200EMB_ERR_INVALID, "quantize_embeddings: unknown precision %d", precision);
+  if (dim <= 0 || (dim % 8) != 0) return set_error(B200EMB_ERR_UNSUPPORTED, "quantize_embeddings: dim %d is not a multiple of 8", dim);
+  const bool eight_bit = precision == B200EMB_EMB_INT8 || precision == B200EMB_EMB_UINT8;
+  if (eight_bit && d_ranges == nullptr) return set_error(B200EMB_ERR_INVALID, "quantize_embeddings: int8 / uint8 need calibration ranges");
+  if (x == nullptr || out == nullptr || x_row_stride < dim || out_row_stride_bytes < (eight_bit ? dim : dim / 8))
+    return set_error(B200EMB_ERR_INVALID, "quantize_embeddings: null pointer or row stride too small");
+  const long long total = static_cast<long long>(n_rows) * (dim >> 3);
+  const int grid = static_cast<int>(total / 256 + 1 < 148 * 16 ? total / 256 + 1 : 148 * 16);
+  quantize_embeddings_kernel<<<grid, 256, 0, stream>>>(x, n_rows, dim, x_row_stride, precision, d_ranges,
+                                                       reinterpret_cast<uint8_t*>(out), out_row_stride_bytes);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "quantize_embeddings launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
 int launch_small_proj(const void* x, const void* W, const float* bias, int n_rows, int hidden, int n_labels,
                       float* out, int64_t out_row_stride, cudaStream_t stream) {
   if (n_rows <= 0 || n_labels <= 0) return B200EMB_OK;

@@ -167,6 +167,9 @@ struct DeviceCtx {
   float* hres = nullptr;     // decoder: fp32 residual stream [T, H]
   float* rope_cs = nullptr;  // decoder: (cos, sin) table [max_pos, head_dim / 2]
   float* d_out = nullptr;
+  uint8_t* d_qout = nullptr;   // quantised output rows (b200emb_forward_quantized)
+  size_t d_qout_bytes = 0;
+  double* d_ranges = nullptr;  // calibration ranges [2, out_dim]
   int* d_err = nullptr;
   // pinned host staging
   int32_t *h_ids = nullptr, *h_types = nullptr, *h_cu = nullptr;
@@ -430,6 +433,7 @@ static void destroy_ctx(DeviceCtx* c) {
   cudaFree(c->d_ids); cudaFree(c->d_types); cudaFree(c->d_cu); cudaFree(c->d_tiles);
   cudaFree(c->x); cudaFree(c->x2); cudaFree(c->qkv); cudaFree(c->ctx); cudaFree(c->y); cudaFree(c->ffn);
   cudaFree(c->pooled); cudaFree(c->head_h); cudaFree(c->d_out); cudaFree(c->d_err);
+  cudaFree(c->d_qout); cudaFree(c->d_ranges);
   cudaFree(c->hres); cudaFree(c->rope_cs); cudaFree(c->wscratch); cudaFree(c->act_q); cudaFree(c->act_sf); cudaFree(c->act2_q); cudaFree(c->act2_sf);
   for (uint8_t* p : c->owned_atoms) cudaFree(p);
   cudaFree(c->topk_idx); cudaFree(c->row_of); cudaFree(c->moe_counts); cudaFree(c->moe_cursor); cudaFree(c->tile_expert);
@@ -811,10 +815,22 @@ static void collect_kernel_times(DeviceCtx* c, b200emb_timing* timing) {
   }
 }
 
+// Bytes of one result row at an output precision.
+static size_t out_row_bytes(const b200emb_handle* h, int precision) {
+  switch (precision) {
+    case B200EMB_EMB_INT8:
+    case B200EMB_EMB_UINT8: return (size_t)h->out_dim;
+    case B200EMB_EMB_BINARY:
+    case B200EMB_EMB_UBINARY: return (size_t)h->out_dim / 8;
+  }
+  return sizeof(float) * (size_t)h->out_dim;
+}
+
 // Runs one shard (host inputs, shard-local cu_seqlens) on device context c and leaves the
-// result rows in dst (row stride dst_stride floats).
+// result rows in dst (row stride dst_stride_bytes), quantised on the device when precision is not float32.
 static void run_shard(b200emb_handle* h, DeviceCtx* c, const int32_t* ids, const int32_t* types, const int32_t* cu,
-                      int n_seqs, int n_tokens, float* dst, int64_t dst_stride, bool per_kernel, ShardResult* res) {
+                      int n_seqs, int n_tokens, uint8_t* dst, int64_t dst_stride_bytes, int precision,
+                      const double* h_ranges, bool per_kernel, ShardResult* res) {
   auto fail = [&](int rc) {
     res->rc = rc;
     res->msg = g_err;
@@ -849,10 +865,31 @@ static void run_shard(b200emb_handle* h, DeviceCtx* c, const int32_t* ids, const
     cudaStreamSynchronize(s);
     return fail(rc);
   }
+  const size_t n_rows = h->desc.pooling == B200EMB_POOL_TOKENS ? n_tokens : n_seqs;
+  const size_t row_bytes = out_row_bytes(h, precision);
+  const uint8_t* d_rows = reinterpret_cast<const uint8_t*>(c->d_out);
+  if (precision != B200EMB_EMB_FLOAT32) {
+    if (c->d_qout_bytes < n_rows * row_bytes) {
+      cudaFree(c->d_qout);
+      c->d_qout = nullptr;
+      c->d_qout_bytes = std::max(n_rows * row_bytes, (size_t)1 << 20);
+      B2_TRY(cudaMalloc(reinterpret_cast<void**>(&c->d_qout), c->d_qout_bytes));
+    }
+    if (h_ranges != nullptr) {
+      if (c->d_ranges == nullptr) B2_TRY(cudaMalloc(reinterpret_cast<void**>(&c->d_ranges), sizeof(double) * 2 * h->out_dim));
+      B2_TRY(cudaMemcpyAsync(c->d_ranges, h_ranges, sizeof(double) * 2 * h->out_dim, cudaMemcpyHostToDevice, s));
+    }
+    KernelScope ks(c, B200EMB_KCLASS_POOL);
+    rc = launch_quantize_embeddings(c->d_out, (int)n_rows, h->out_dim, h->out_dim, precision,
+                                    h_ranges != nullptr ? c->d_ranges : nullptr, c->d_qout, (int64_t)row_bytes, s);
+    if (rc) {
+      cudaStreamSynchronize(s);
+      return fail(rc);
+    }
+    d_rows = c->d_qout;
+  }
   B2_TRY(cudaEventRecord(c->ev[2], s));
-  B2_TRY(cudaMemcpy2DAsync(dst, sizeof(float) * dst_stride, c->d_out, sizeof(float) * h->out_dim,
-                           sizeof(float) * h->out_dim,
-                           h->desc.pooling == B200EMB_POOL_TOKENS ? n_tokens : n_seqs, cudaMemcpyDeviceToHost, s));
+  B2_TRY(cudaMemcpy2DAsync(dst, (size_t)dst_stride_bytes, d_rows, row_bytes, row_bytes, n_rows, cudaMemcpyDeviceToHost, s));
   B2_TRY(cudaMemcpyAsync(c->h_err, c->d_err, sizeof(int), cudaMemcpyDeviceToHost, s));
   B2_TRY(cudaEventRecord(c->ev[3], s));
   B2_TRY(cudaStreamSynchronize(s));
@@ -1114,22 +1151,31 @@ int b200emb_destroy(b200emb_handle* h) {
   return B200EMB_OK;
 }
 
-int b200emb_forward(b200emb_handle* h, const int32_t* input_ids, const int32_t* token_type_ids,
-                    const int32_t* cu_seqlens, int32_t n_seqs, int32_t n_tokens, float* out, int64_t out_row_stride,
-                    b200emb_timing* timing) {
+static int forward_impl(b200emb_handle* h, const int32_t* input_ids, const int32_t* token_type_ids,
+                        const int32_t* cu_seqlens, int32_t n_seqs, int32_t n_tokens, int precision,
+                        const double* h_ranges, uint8_t* out, int64_t out_stride_bytes, b200emb_timing* timing) {
   if (h == nullptr) return set_error(B200EMB_ERR_INVALID, "null handle");
   const auto t0 = std::chrono::steady_clock::now();
   int rc = validate_batch(h->desc, input_ids, token_type_ids, cu_seqlens, n_seqs, n_tokens);
   if (rc) return rc;
-  if (n_seqs > 0 && (out == nullptr || out_row_stride < h->out_dim))
-    return set_error(B200EMB_ERR_INVALID, "output buffer missing or row stride %lld < %d", (long long)out_row_stride, h->out_dim);
+  if (precision < B200EMB_EMB_FLOAT32 || precision > B200EMB_EMB_UBINARY)
+    return set_error(B200EMB_ERR_INVALID, "unknown output precision %d", precision);
+  if (precision != B200EMB_EMB_FLOAT32 && h->desc.head != B200EMB_HEAD_NONE)
+    return set_error(B200EMB_ERR_INVALID, "output quantisation applies to embeddings, not to classifier logits");
+  if ((precision == B200EMB_EMB_INT8 || precision == B200EMB_EMB_UINT8) && h_ranges == nullptr)
+    return set_error(B200EMB_ERR_INVALID, "int8 / uint8 outputs need calibration ranges");
+  if (precision != B200EMB_EMB_FLOAT32 && (h->out_dim % 8) != 0)
+    return set_error(B200EMB_ERR_UNSUPPORTED, "output quantisation needs a dimension that is a multiple of 8");
+  const size_t row_bytes = out_row_bytes(h, precision);
+  if (n_seqs > 0 && (out == nullptr || out_stride_bytes < (int64_t)row_bytes))
+    return set_error(B200EMB_ERR_INVALID, "output buffer missing or row stride %lld bytes < %zu", (long long)out_stride_bytes, row_bytes);
   const bool per_kernel = timing != nullptr && timing->per_kernel != 0;
   const int G = (int)h->devs.size();
   std::vector<ShardResult> res(G);
 
   if (G == 1 || n_seqs < 2) {
-    run_shard(h, h->devs[0], input_ids, token_type_ids, cu_seqlens, n_seqs, n_tokens, out, out_row_stride, per_kernel,
-              &res[0]);
+    run_shard(h, h->devs[0], input_ids, token_type_ids, cu_seqlens, n_seqs, n_tokens, out, out_stride_bytes, precision,
+              h_ranges, per_kernel, &res[0]);
   } else {
     // Token-balanced split: whole sequences go to the least-loaded device, most expensive
     // first; each device gets its own packed ids / cu_seqlens; rows return to batch order.
@@ -1167,18 +1213,20 @@ int b200emb_forward(b200emb_handle* h, const int32_t* input_ids, const int32_t* 
           pos += lens[i];
           c->h_cu[k + 1] = pos;
         }
+        // the pinned staging rows are sized for float32, the widest precision
+        uint8_t* stage = reinterpret_cast<uint8_t*>(c->h_out);
         run_shard(h, c, c->h_ids, token_type_ids != nullptr ? c->h_types : nullptr, c->h_cu, (int)mem.size(), tok,
-                  c->h_out, h->out_dim, per_kernel, r);
+                  stage, (int64_t)row_bytes, precision, h_ranges, per_kernel, r);
         if (r->rc == 0) {
           if (h->desc.pooling == B200EMB_POOL_TOKENS) {
             // token rows: sequence mem[k] owns batch rows cu_seqlens[i] .. and shard rows h_cu[k] ..
             for (size_t k = 0; k < mem.size(); ++k)
               for (int t = 0; t < lens[mem[k]]; ++t)
-                memcpy(out + (size_t)(cu_seqlens[mem[k]] + t) * out_row_stride,
-                       c->h_out + (size_t)(c->h_cu[k] + t) * h->out_dim, sizeof(float) * h->out_dim);
+                memcpy(out + (size_t)(cu_seqlens[mem[k]] + t) * out_stride_bytes,
+                       stage + (size_t)(c->h_cu[k] + t) * row_bytes, row_bytes);
           } else {
             for (size_t k = 0; k < mem.size(); ++k)
-              memcpy(out + (size_t)mem[k] * out_row_stride, c->h_out + k * (size_t)h->out_dim, sizeof(float) * h->out_dim);
+              memcpy(out + (size_t)mem[k] * out_stride_bytes, stage + k * row_bytes, row_bytes);
           }
         }
       });
@@ -1207,6 +1255,21 @@ int b200emb_forward(b200emb_handle* h, const int32_t* input_ids, const int32_t* 
     timing->total_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
   }
   return B200EMB_OK;
+}
+
+int b200emb_forward(b200emb_handle* h, const int32_t* input_ids, const int32_t* token_type_ids,
+                    const int32_t* cu_seqlens, int32_t n_seqs, int32_t n_tokens, float* out, int64_t out_row_stride,
+                    b200emb_timing* timing) {
+  return forward_impl(h, input_ids, token_type_ids, cu_seqlens, n_seqs, n_tokens, B200EMB_EMB_FLOAT32, nullptr,
+                      reinterpret_cast<uint8_t*>(out), out_row_stride * (int64_t)sizeof(float), timing);
+}
+
+int b200emb_forward_quantized(b200emb_handle* h, const int32_t* input_ids, const int32_t* token_type_ids,
+                              const int32_t* cu_seqlens, int32_t n_seqs, int32_t n_tokens, int32_t precision,
+                              const double* h_ranges, void* out, int64_t out_row_stride_bytes,
+                              b200emb_timing* timing) {
+  return forward_impl(h, input_ids, token_type_ids, cu_seqlens, n_seqs, n_tokens, precision, h_ranges,
+                      reinterpret_cast<uint8_t*>(out), out_row_stride_bytes, timing);
 }
 
 int b200emb_forward_device(b200emb_handle* h, const int32_t* d_input_ids, const int32_t* d_token_type_ids,
@@ -1436,6 +1499,17 @@ int b200emb_op_add_ln(const void* x, const void* y, const float* gamma, const fl
   if (x == nullptr || gamma == nullptr || beta == nullptr || out == nullptr)
     return set_error(B200EMB_ERR_INVALID, "add_ln: null pointer");
   return launch_add_ln(x, y, gamma, beta, n_rows, hidden, eps, out, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int b200emb_op_quantize_embeddings(const float* x, int32_t n_rows, int32_t dim, int64_t x_row_stride,
+                                   int32_t precision, const double* d_ranges, void* out,
+                                   int64_t out_row_stride_bytes, void* stream) {
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int rc = launch_quantize_embeddings(x, n_rows, dim, x_row_stride, precision, d_ranges, out, out_row_stride_bytes, s);
+  if (rc) return rc;
+  cudaError_t e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "quantize_embeddings: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
 }
 
 int b200emb_op_pool(const void* x, const int32_t* d_cu_seqlens, int32_t n_seqs, int32_t hidden, int32_t pooling,

@@ -109,6 +109,31 @@ class B200Model:
         self._account(n_seqs, n_tokens)
         return out
 
+    def forward_quantized(self, input_ids: np.ndarray, cu_seqlens: np.ndarray, precision: str,
+                          token_type_ids: Optional[np.ndarray] = None, ranges: Optional[np.ndarray] = None) -> np.ndarray:
+        """The same forward with the result rows quantised on the device before the copy back
+        (``precision``: int8 | uint8 | binary | ubinary; ``ranges``: float64 ``[2, dim]`` calibration
+        ranges for the 8-bit formats). Returns int8 / uint8 rows of ``dim`` or ``dim / 8`` bytes."""
+        ids = np.ascontiguousarray(input_ids, dtype=np.int32)
+        cu = np.ascontiguousarray(cu_seqlens, dtype=np.int32)
+        tt = None if token_type_ids is None else np.ascontiguousarray(token_type_ids, dtype=np.int32)
+        n_seqs, n_tokens = len(cu) - 1, int(len(ids))
+        n_rows = n_tokens if self.spec.pooling == "tokens" else n_seqs
+        dim = self.spec.out_dim
+        width = dim // 8 if precision in ("binary", "ubinary") else dim
+        out = np.empty((n_rows, width), dtype=_lib.EMB_NUMPY[precision])
+        rg = None if ranges is None else np.ascontiguousarray(ranges, dtype=np.float64)
+        if rg is not None and rg.shape != (2, dim):
+            raise ValueError(f"ranges must have shape (2, {dim})")
+        timing = _lib.Timing()
+        _lib.check(self._lib.b200emb_forward_quantized(
+            self._handle, ids.ctypes.data, None if tt is None else tt.ctypes.data, cu.ctypes.data, n_seqs, n_tokens,
+            _lib.EMB[precision], None if rg is None else rg.ctypes.data, out.ctypes.data, out.strides[0],
+            C.byref(timing)))
+        self.last_timing = timing_dict(timing)
+        self._account(n_seqs, n_tokens)
+        return out
+
     def forward(self, batch: Batch, **kw) -> np.ndarray:
         return self.forward_arrays(batch.input_ids, batch.cu_seqlens, batch.token_type_ids, **kw)
 

@@ -66,6 +66,30 @@ def test_embedder_backend_colbert_mode(tmp_path):
     backend.model.close()
 
 
+def test_embedder_backend_embedding_dtypes(tmp_path):
+    """EmbeddingDtype on the backend (primitives.py:145-158): rows equal the numpy quantiser applied
+    to the float32 rows, with ranges calibrated on caller-supplied sentences."""
+    from oracle import quant_embeddings as QE
+    spec = cf.tiny_spec("bert")
+    path, _ = _weights(tmp_path, spec, 54)
+    rng = np.random.default_rng(3)
+    sentences = [_sentence(rng, n, spec.vocab) for n in (5, 90, 17, 160, 1)]
+    calib = [_sentence(rng, n, spec.vocab) for n in rng.integers(4, 120, size=20)]
+    plain = B200Embedder(spec=spec, weight_path=path, device_ids=(0,))
+    rows = np.array(plain.encode_post(plain.encode_core(plain.encode_pre(sentences))))
+    for dtype in ("uint8", "binary"):
+        be = B200Embedder(spec=spec, weight_path=path, device_ids=(0,), embedding_dtype=dtype)
+        if dtype == "uint8":
+            with pytest.raises(ValueError):
+                be.encode_core(be.encode_pre(sentences))
+            ranges = be.calibrate(calib)
+            assert ranges.shape == (2, spec.hidden)
+        out = be.encode_post(be.encode_core(be.encode_pre(sentences)))
+        assert np.array_equal(out, QE.quantize_embeddings(rows, dtype, be.calibration_ranges))
+        be.model.close()
+    plain.model.close()
+
+
 def test_cross_encoder_and_classifier_backends(tmp_path):
     spec = cf.tiny_spec("xlmr")
     path, W = _weights(tmp_path, spec, 52)

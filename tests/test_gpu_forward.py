@@ -65,6 +65,27 @@ def test_token_level_outputs_match_oracle(tmp_path, normalize):
     model.close()
 
 
+def test_quantised_output_rows(tmp_path):
+    """b200emb_forward_quantized = the numpy quantiser applied to b200emb_forward's float32 rows, bit for
+    bit, for every EmbeddingDtype; int8 / uint8 with ranges calibrated as the reference does."""
+    from oracle import quant_embeddings as QE
+    spec = cf.tiny_spec("bert", hidden=256, n_heads=4, n_kv_heads=4, head_dim=64, ffn=512)
+    model, _ = build_model(tmp_path, spec, 19, perturb=True)
+    batch = cf.random_batch(spec, [3, 50, 128, 9, 77, 160, 1], 4, with_types=True)
+    rows = np.array(model.forward(batch))
+    calib = np.array(model.forward(cf.random_batch(spec, [20, 40, 60, 80, 100, 120], 6, with_types=True)))
+    ranges = QE.calibration_ranges(calib)
+    for precision in ("int8", "uint8", "binary", "ubinary"):
+        got = model.forward_quantized(batch.input_ids, batch.cu_seqlens, precision, batch.token_type_ids,
+                                      ranges if precision in ("int8", "uint8") else None)
+        ref = QE.quantize_embeddings(rows, precision, ranges if precision in ("int8", "uint8") else None)
+        assert got.dtype == ref.dtype and got.shape == ref.shape
+        assert np.array_equal(got, ref), precision
+    with pytest.raises(RuntimeError, match="calibration ranges"):
+        model.forward_quantized(batch.input_ids, batch.cu_seqlens, "int8", batch.token_type_ids, None)
+    model.close()
+
+
 def test_tiny_reranker_matches_oracle(tmp_path):
     spec = cf.tiny_spec("xlmr")
     model, W = build_model(tmp_path, spec, 12, perturb=True)
@@ -206,6 +227,9 @@ def test_multi_device_handle_equals_single_device(tmp_path):
     cu = batch.cu_seqlens
     one = multi.forward(cf.pack([batch.sequences()[5]], [batch.token_type_ids[cu[5]:cu[6]]]))  # runs on the first device
     assert np.array_equal(one[0], a[5])
+    q1 = single.forward_quantized(batch.input_ids, batch.cu_seqlens, "ubinary", batch.token_type_ids)
+    q2 = multi.forward_quantized(batch.input_ids, batch.cu_seqlens, "ubinary", batch.token_type_ids)
+    assert q1.shape == (97, 32) and np.array_equal(q1, q2)
     single.close()
     multi.close()
     # token-level outputs: rows return to packed batch order

@@ -268,6 +268,24 @@ def test_moe_router_matches_numpy(lib, T, H, E, k):
     assert np.array_equal(np.bincount(got_idx.ravel(), minlength=E), counts.cpu().numpy())
 
 
+@pytest.mark.parametrize("precision", ["int8", "uint8", "binary", "ubinary"])
+@pytest.mark.parametrize("rows,dim", [(1, 8), (33, 384), (1024, 1024), (7, 3584)])
+def test_quantize_embeddings_matches_numpy(lib, precision, rows, dim):
+    """Bit-exact against the numpy statement, values beyond the calibration range included."""
+    from oracle import quant_embeddings as QE
+    rng = np.random.default_rng(rows + dim)
+    x = rng.standard_normal((rows, dim)).astype(np.float32)
+    x[0, : min(dim, 4)] = [0.0, -0.0, 1e-30, -1e-30][: min(dim, 4)]
+    ranges = np.stack([-1.5 + 0.1 * rng.random(dim), 1.5 + 0.1 * rng.random(dim)])  # float64; |x| reaches 4
+    ref = QE.quantize_embeddings(x, precision, ranges if precision in ("int8", "uint8") else None)
+    dx = torch.from_numpy(x).cuda()
+    dr = torch.from_numpy(ranges).cuda()
+    out = torch.zeros(ref.shape, dtype=torch.int8 if ref.dtype == np.int8 else torch.uint8, device="cuda")
+    _lib.check(lib.b200emb_op_quantize_embeddings(dx.data_ptr(), rows, dim, dim, _lib.EMB[precision], dr.data_ptr(),
+                                                  out.data_ptr(), ref.shape[1], _stream()))
+    assert np.array_equal(out.cpu().numpy(), ref)
+
+
 def test_bounded_wait_gives_up_and_context_survives(lib):
     """Failure detection without a fault: a wait on a barrier nothing signals runs into its limit,
     the host sees B200EMB_ERR_DEVICE_WAIT, and the next kernel on the same context works."""

@@ -187,3 +187,26 @@ def test_token_level_oracle_is_consistent_with_pooled_oracle():
         np.testing.assert_allclose(pooled, ref, atol=2e-6)
     with pytest.raises(ValueError):
         enc.forward_batch(tok_spec, W, batch)
+
+
+def test_output_quantisation_known_answers():
+    """Hand-computed vectors for the restated sentence-transformers quantize_embeddings
+    (called from infinity_emb/transformer/quantization/interface.py:147-151)."""
+    from oracle import quant_embeddings as QE
+    x = np.array([[0.5, -0.1, 0.0, 2.0, -3.0, 0.2, 0.3, -0.4, 1, 1, 1, 1, 1, 1, 1, 1]], dtype=np.float32)
+    # bits (x > 0), most significant first: 1001 0110 = 150, 1111 1111 = 255
+    assert QE.quantize_embeddings(x, "ubinary").tolist() == [[150, 255]]
+    assert QE.quantize_embeddings(x, "binary").tolist() == [[22, 127]]
+    assert QE.quantize_embeddings(x, "binary").dtype == np.int8
+    r = np.array([[-1.0] * 16, [1.0] * 16])
+    # (x + 1) / (2 / 255), truncated: 0.5 -> 191, -0.1 -> 114, 0 -> 127, in range
+    u = QE.quantize_embeddings(x, "uint8", r)
+    assert u.dtype == np.uint8 and u[0, :3].tolist() == [191, 114, 127] and u[0, 5:8].tolist() == [153, 165, 76]
+    i = QE.quantize_embeddings(x, "int8", r)
+    assert i.dtype == np.int8 and i[0, :3].tolist() == [63, -13, 0] and i[0, 5:8].tolist() == [25, 37, -51]
+    # without ranges the batch's own min / max are used, in the embeddings' float32: the step 1/255 rounds
+    # up in float32, so the maximum lands just below 255 and truncates to 254
+    y = np.array([[0.0, 1.0], [1.0, 0.0], [0.25, 0.5]], dtype=np.float32)
+    assert QE.quantize_embeddings(y, "uint8").tolist() == [[0, 254], [254, 0], [63, 127]]
+    rng = QE.calibration_ranges(y)
+    assert rng.shape == (2, 2) and rng.dtype == np.float64 and rng.tolist() == [[0.0, 0.0], [1.0, 1.0]]
