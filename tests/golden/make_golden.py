@@ -2,7 +2,7 @@
 
 Run where the reference tree is mounted:
 
-    python tests/golden/make_golden.py /root/reference/libs/infinity_emb
+    python tests/golden/make_golden.py <reference checkout>/libs/infinity_emb
 
 It imports (never copies) the reference's pure-Python modules with two import-time shims
 (no file of the reference is modified): ``importlib.metadata.version("infinity_emb")``
@@ -55,7 +55,9 @@ def import_reference(ref_root: str):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/libs/infinity_emb"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("INFINITY_EMB_SOURCE", "")
+    if not ref_root:
+        raise SystemExit("usage: make_golden.py <reference checkout>/libs/infinity_emb")
     import_reference(ref_root)
     from infinity_emb.transformer import utils_optimum as uo
 

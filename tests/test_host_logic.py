@@ -15,7 +15,9 @@ from infinity_b200 import packing as pk
 from infinity_b200 import weights as wt
 from infinity_b200.backend import B200Classifier, B200CrossEncoder, B200Embedder
 
-REF = Path("/root/reference/libs/infinity_emb")
+# the reference's Python sources, when a checkout is mounted next to this repository (the tests that drive its
+# batcher are skipped otherwise)
+REF = Path(os.environ.get("INFINITY_EMB_SOURCE", str(Path(__file__).resolve().parents[2] / "reference" / "libs" / "infinity_emb")))
 
 
 def test_weight_file_round_trip(tmp_path):
