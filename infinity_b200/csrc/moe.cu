@@ -128,6 +128,109 @@ moe_router_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__
   if (counts != nullptr && threadIdx.x < n_experts && cnt_s[threadIdx.x] > 0) atomicAdd(counts + threadIdx.x, cnt_s[threadIdx.x]);
 }
 
+// Router for up to 8 experts, eight tokens per warp step.
+//  * the router matrix sits in shared memory as [expert][half][chunk] float4 (chunk = 8 consecutive
+//    hidden elements, half = its first / last four), so that a warp's 16-byte reads are consecutive;
+//    one pass over it serves eight tokens;
+//  * every lane accumulates the 8 x 8 (token, expert) partial dot products over its chunks; a
+//    reduce-scatter over the warp (32 + 16 + 8 + 4 + 2 shuffles instead of 64 x 5 for a butterfly per
+//    value) leaves lane l with token l / 4, experts 2 (l % 4) and 2 (l % 4) + 1;
+//  * the four lanes of a token exchange their pairs and each computes softmax and top-k (same
+//    instructions in all lanes, no divergence); the first of them writes.
+__global__ void __launch_bounds__(MOE_WARPS * 32)
+moe_router8_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wr, const float* __restrict__ br,
+                   int n_tokens, int hidden, int n_experts, int top_k, int32_t* __restrict__ topk_idx,
+                   float* __restrict__ topk_w, int32_t* __restrict__ counts) {
+  constexpr int E = 8, TPW = 8;
+  extern __shared__ float4 wr4_s[];  // [E][2][n_chunks]
+  __shared__ int32_t cnt_s[E];
+  const int n_chunks = hidden >> 3;
+  for (int i = threadIdx.x; i < E * 2 * n_chunks; i += blockDim.x) {
+    const int e = i / (2 * n_chunks), half = (i / n_chunks) & 1, c = i % n_chunks;
+    wr4_s[i] = e < n_experts ? *reinterpret_cast<const float4*>(wr + static_cast<size_t>(e) * hidden + c * 8 + half * 4)
+                             : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (threadIdx.x < E) cnt_s[threadIdx.x] = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warps_total = gridDim.x * MOE_WARPS;
+  for (int t0 = (blockIdx.x * MOE_WARPS + (threadIdx.x >> 5)) * TPW; t0 < n_tokens; t0 += warps_total * TPW) {
+    float acc[TPW * E];  // index token * 8 + expert
+#pragma unroll
+    for (int i = 0; i < TPW * E; ++i) acc[i] = 0.f;
+    for (int c = lane; c < n_chunks; c += 32) {
+      uint4 raw[TPW];
+#pragma unroll
+      for (int j = 0; j < TPW; ++j)
+        raw[j] = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(min(t0 + j, n_tokens - 1)) * hidden + c * 8);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const float4 w0 = wr4_s[(e * 2) * n_chunks + c];
+        const float4 w1 = wr4_s[(e * 2 + 1) * n_chunks + c];
+#pragma unroll
+        for (int j = 0; j < TPW; ++j) {
+          float v[8];
+          unpack8m(raw[j], v);
+          acc[j * E + e] += v[0] * w0.x + v[1] * w0.y + v[2] * w0.z + v[3] * w0.w + v[4] * w1.x + v[5] * w1.y +
+                            v[6] * w1.z + v[7] * w1.w;
+        }
+      }
+    }
+    // reduce-scatter: at each stage a lane keeps the half of its values chosen by one bit of its index
+    // and adds the partner's copy of that half
+#pragma unroll
+    for (int stage = 0; stage < 5; ++stage) {
+      const int mask = 16 >> stage, half = (TPW * E / 2) >> stage;
+      const bool upper = (lane & mask) != 0;
+#pragma unroll
+      for (int k = 0; k < half; ++k) {
+        const float send = upper ? acc[k] : acc[k + half];
+        const float keep = upper ? acc[k + half] : acc[k];
+        acc[k] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
+      }
+    }
+    // lane l: token t0 + l / 4, experts 2 (l % 4) and 2 (l % 4) + 1; gather the token's eight logits
+    float a[E];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      a[2 * q] = __shfl_sync(0xffffffffu, acc[0], (lane & ~3) + q);
+      a[2 * q + 1] = __shfl_sync(0xffffffffu, acc[1], (lane & ~3) + q);
+    }
+    const int t = t0 + (lane >> 2);
+    float mx = -INFINITY;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      a[e] = e < n_experts ? a[e] + (br != nullptr ? br[e] : 0.f) : -INFINITY;
+      mx = fmaxf(mx, a[e]);
+    }
+    float den = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      a[e] = expf(a[e] - mx);  // 0 for the experts that do not exist
+      den += a[e];
+    }
+    uint32_t taken = 0;
+    for (int k = 0; k < top_k; ++k) {
+      int best = 0;
+      float bv = -1.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e)
+        if (e < n_experts && !((taken >> e) & 1u) && a[e] > bv) {  // strict >: a tie keeps the lower index
+          bv = a[e];
+          best = e;
+        }
+      taken |= 1u << best;
+      if ((lane & 3) == 0 && t < n_tokens) {
+        topk_idx[static_cast<size_t>(t) * top_k + k] = best;
+        topk_w[static_cast<size_t>(t) * top_k + k] = bv / den;
+        atomicAdd(&cnt_s[best], 1);
+      }
+    }
+  }
+  __syncthreads();
+  if (counts != nullptr && threadIdx.x < n_experts && cnt_s[threadIdx.x] > 0) atomicAdd(counts + threadIdx.x, cnt_s[threadIdx.x]);
+}
+
 // counts[e] -> seg_off[e] (row offset of expert e's segment, multiples of 128), cursor[e] = seg_off[e],
 // tile_expert[row block] = expert or -1.
 __global__ void moe_offsets_kernel(const int32_t* __restrict__ counts, int n_experts, int max_blocks,
@@ -203,39 +306,64 @@ moe_scatter_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __r
     const int my_row = base + rank;
     if (s < n_slots) row_of[s] = my_row;
     const int n_here = min(32, n_slots - s0);
-    for (int j = 0; j < n_here; ++j) {
-      const size_t row = static_cast<size_t>(__shfl_sync(0xffffffffu, my_row, j));
-      const __nv_bfloat16* src = x + static_cast<size_t>((s0 + j) / top_k) * hidden;
-      for (int b = lane; b < kblocks; b += 32) {
-        float v[32];
+    // The top_k slots of a token are consecutive: its row is loaded and quantised once and written to
+    // each of its destinations; the next token's loads are in flight meanwhile.
+    for (int b0 = 0; b0 < kblocks; b0 += 32) {
+      const int b = b0 + lane;
+      const bool active = b < kblocks;
+      uint4 nxt[4];
+      auto prefetch = [&](int tok) {
+        if (active) {
+          const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(tok) * hidden + b * 32);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) unpack8m(*reinterpret_cast<const uint4*>(src + b * 32 + i * 8), reinterpret_cast<float(&)[8]>(v[i * 8]));
-        float amax = 0.f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
-        int ex = -127;
-        if (amax > 0.f) {
-          ex = ilogbf(amax) - 8;
-          ex = ex < -127 ? -127 : (ex > 127 ? 127 : ex);
+          for (int i = 0; i < 4; ++i) nxt[i] = src[i];
         }
-        const float inv = ex == -127 ? 0.f : exp2f(static_cast<float>(-ex));
-        uint32_t out[8];
+      };
+      int cur_tok = -1;
+      uint32_t out[8];
+      int ex = -127;
+      prefetch(s0 / top_k);
+      for (int j = 0; j < n_here; ++j) {
+        const size_t row = static_cast<size_t>(__shfl_sync(0xffffffffu, my_row, j));
+        const int tok = (s0 + j) / top_k;
+        if (tok != cur_tok) {  // warp-uniform
+          cur_tok = tok;
+          float v[32];
+          if (active) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          uint32_t word = 0;
-#pragma unroll
-          for (int k = 0; k < 4; k += 2) {
-            const uint32_t two = __nv_cvt_float2_to_fp8x2(make_float2(v[i * 4 + k] * inv, v[i * 4 + k + 1] * inv),
-                                                          __NV_SATFINITE, __NV_E4M3);
-            word |= (two & 0xffffu) << (8 * k);
+            for (int i = 0; i < 4; ++i) unpack8m(nxt[i], reinterpret_cast<float(&)[8]>(v[i * 8]));
           }
-          out[i] = word;
+          if ((tok + 1) * top_k < s0 + n_here) prefetch(tok + 1);
+          if (active) {
+            float amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+            ex = -127;
+            if (amax > 0.f) {
+              ex = ilogbf(amax) - 8;
+              ex = ex < -127 ? -127 : (ex > 127 ? 127 : ex);
+            }
+            const float inv = ex == -127 ? 0.f : exp2f(static_cast<float>(-ex));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              uint32_t word = 0;
+#pragma unroll
+              for (int k = 0; k < 4; k += 2) {
+                const uint32_t two = __nv_cvt_float2_to_fp8x2(make_float2(v[i * 4 + k] * inv, v[i * 4 + k + 1] * inv),
+                                                              __NV_SATFINITE, __NV_E4M3);
+                word |= (two & 0xffffu) << (8 * k);
+              }
+              out[i] = word;
+            }
+          }
         }
-        uint4* dst = reinterpret_cast<uint4*>(xq + row * hidden + b * 32);
-        dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
-        dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
-        sf_atoms[((row >> 7) * kgroups + (b >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (b & 3)] =
-            static_cast<uint8_t>(ex + 127);
+        if (active) {
+          uint4* dst = reinterpret_cast<uint4*>(xq + row * hidden + b * 32);
+          dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
+          dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
+          sf_atoms[((row >> 7) * kgroups + (b >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (b & 3)] =
+              static_cast<uint8_t>(ex + 127);
+        }
       }
     }
   }
@@ -313,6 +441,7 @@ moe_combine_ln_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
 
 int moe_init_device() {
   B2_CUDA_CHECK(cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+  B2_CUDA_CHECK(cudaFuncSetAttribute(moe_router8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
   return B200EMB_OK;
 }
 
@@ -333,6 +462,16 @@ int launch_moe_router(const void* x, const float* wr, const float* br, int n_tok
   const size_t smem = static_cast<size_t>(n_experts) * hidden * sizeof(float);
   if (smem > 96 * 1024) return set_error(B200EMB_ERR_UNSUPPORTED, "router: n_experts * hidden too large for shared memory");
   if (counts != nullptr) B2_CUDA_CHECK(cudaMemsetAsync(counts, 0, sizeof(int32_t) * n_experts, stream));
+  if (n_experts <= 8) {
+    const size_t smem8 = static_cast<size_t>(8) * hidden * sizeof(float);
+    if (smem8 <= 96 * 1024) {
+      moe_router8_kernel<<<persistent_grid((n_tokens + 7) / 8), MOE_WARPS * 32, smem8, stream>>>(
+          reinterpret_cast<const __nv_bfloat16*>(x), wr, br, n_tokens, hidden, n_experts, top_k, topk_idx, topk_w, counts);
+      cudaError_t e8 = cudaGetLastError();
+      if (e8 != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "router launch: %s", cudaGetErrorString(e8));
+      return B200EMB_OK;
+    }
+  }
   moe_router_kernel<<<persistent_grid((n_tokens + 3) / 4), MOE_WARPS * 32, smem, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), wr, br, n_tokens, hidden, n_experts, top_k, topk_idx, topk_w, counts);
   cudaError_t e = cudaGetLastError();
