@@ -25,6 +25,9 @@
 #include <stdint.h>
 
 #include "kernels.h"
+// mbarrier waits here are short and on the critical chain softmax -> MMA -> softmax: plain polling
+// (no suspend-time hint) measured 3-7 % faster than letting the hardware park the waiting thread
+#define B2_MBAR_SUSPEND_NS 0
 #include "ptx.cuh"
 
 namespace b2 {
