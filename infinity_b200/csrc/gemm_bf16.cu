@@ -119,7 +119,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   uint64_t* drain_bar = acc_empty_bar + 2;  // error path only: MMAs in flight before TMEM is freed
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // warp-uniform in the compiler's view too
   const int lane = threadIdx.x & 31;
   const int m_tiles = (M + TILE_M - 1) / TILE_M;
   const int n_tiles = (N + BN - 1) / BN;
@@ -212,52 +212,63 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0 && cta_rank == 0) {  // pair: the leader issues the MMAs of both CTAs
+    // All 32 lanes walk the loops (warp-uniform code: descriptors and addresses stay in uniform registers)
+    // and one elected lane issues each tcgen05 instruction. Issued from divergent single-thread code an
+    // MMA costs about 90 cycles of operand moves, which leaves no slack against the 128 cycles a
+    // 128 x 256 x 16 MMA takes to execute.
+    if (cta_rank == 0) {  // pair: the leader issues the MMAs of both CTAs
       constexpr uint32_t idesc = make_idesc_bf16_f32(TILE_M, BN);
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+      const uint32_t smem_base = smem_u32(smem);
+      auto wait_all = [](uint64_t* bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbar_wait(bar, parity)); };
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int local_tile = 0;
       for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
-        if (tile_expert != nullptr && __ldg(tile_expert + tile / n_tiles) < 0) continue;
+        if (tile_expert != nullptr && __shfl_sync(0xffffffffu, __ldg(tile_expert + tile / n_tiles), 0) < 0) continue;
         const int lt = local_tile++;
         const int acc = lt & 1;
         const uint32_t acc_phase = (lt >> 1) & 1u;
-        if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1u)) {
+        if (!wait_all(&acc_empty_bar[acc], acc_phase ^ 1u)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_u + acc * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase)) {
+          if (!wait_all(&full_bar[stage], phase)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t a_addr = smem_base + stage * Cfg::STAGE_BYTES;
           const uint32_t b_addr = a_addr + Cfg::A_BYTES;
           const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
           const uint64_t b_desc = make_kmajor_sw128_desc(b_addr);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advancing 16 elements along K inside the 128-byte swizzle span = +32 bytes = +2 encoded
-            if (PAIR) tc_mma_f16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-            else tc_mma_f16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (elect_one()) {
+              if (PAIR) tc_mma_f16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              else tc_mma_f16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
           }
           // slot is free once these MMAs have read it (pair: in both CTAs)
-          if (PAIR) {
-            tc_commit_pair(mapa_shared(smem_u32(&empty_bar[stage]), 0));
-            tc_commit_pair(mapa_shared(smem_u32(&empty_bar[stage]), 1));
-          } else {
-            tc_commit(&empty_bar[stage]);
+          if (elect_one()) {
+            if (PAIR) {
+              tc_commit_pair(mapa_shared(smem_u32(&empty_bar[stage]), 0));
+              tc_commit_pair(mapa_shared(smem_u32(&empty_bar[stage]), 1));
+            } else {
+              tc_commit(&empty_bar[stage]);
+            }
           }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) {  // accumulator complete
+        if (ok && elect_one()) {  // accumulator complete
           if (PAIR) {
             tc_commit_pair(mapa_shared(smem_u32(&acc_full_bar[acc]), 0));
             tc_commit_pair(mapa_shared(smem_u32(&acc_full_bar[acc]), 1));
@@ -267,10 +278,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
       }
       if (!ok) {
-        atomicExch(err_flag, 2);
+        if (lane == 0) atomicExch(err_flag, 2);
         // MMAs already issued must finish before the accumulators are freed
-        if (PAIR) tc_commit_pair(mapa_shared(smem_u32(drain_bar), 0));
-        else tc_commit(drain_bar);
+        if (elect_one()) {
+          if (PAIR) tc_commit_pair(mapa_shared(smem_u32(drain_bar), 0));
+          else tc_commit(drain_bar);
+        }
         mbar_wait(drain_bar, 0);
       }
     }

@@ -131,7 +131,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   uint64_t* drain_bar = acc_empty_bar + 2;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // warp-uniform in the compiler's view too
+  const int lane = threadIdx.x & 31;
   const int m_tiles = (M + F8_BM - 1) / F8_BM;
   const int n_tiles = (N + F8_BN - 1) / F8_BN;
   const int total_tiles = m_tiles * n_tiles;
@@ -203,50 +204,62 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // MMA issuer: all 32 lanes walk the loops (warp-uniform code keeps descriptors and addresses in uniform
+    // registers), one elected lane issues each tcgen05 instruction. A stage is two scale-factor copies and
+    // four 128 x 128 x 32 MMAs of 64 cycles each; issued from divergent single-thread code every one of the
+    // six instructions costs about 90 cycles of operand moves, which made the issuer the bottleneck.
+    {
       constexpr uint32_t idesc = make_idesc_mxf8(F8_BM, F8_BN);
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+      const uint32_t a_base = smem_u32(a_tiles), w_base = smem_u32(w_tiles);
+      const uint32_t sfa_base = smem_u32(sfa_s), sfw_base = smem_u32(sfw_s);
+      auto wait_all = [](uint64_t* bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbar_wait(bar, parity)); };
       int stage = 0, local_tile = 0;
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        if (tile_expert != nullptr && __ldg(tile_expert + tile / n_tiles) < 0) continue;
+        if (tile_expert != nullptr && __shfl_sync(0xffffffffu, __ldg(tile_expert + tile / n_tiles), 0) < 0) continue;
         const int lt = local_tile++;
         const int acc = lt & 1;
-        if (!mbar_wait(&acc_empty_bar[acc], ((lt >> 1) & 1u) ^ 1u)) {
+        if (!wait_all(&acc_empty_bar[acc], ((lt >> 1) & 1u) ^ 1u)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * F8_BN;
+        const uint32_t d_tmem = tmem_u + acc * F8_BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase)) {
+          if (!wait_all(&full_bar[stage], phase)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t sfa_t = tmem_base + F8_SF_COL + stage * 8;
+          const uint32_t sfa_t = tmem_u + F8_SF_COL + stage * 8;
           const uint32_t sfw_t = sfa_t + 4;
-          tc_copy_sf(sfa_t, make_sf_desc(smem_u32(sfa_s + stage * F8_SF_BYTES)));
-          tc_copy_sf(sfw_t, make_sf_desc(smem_u32(sfw_s + stage * F8_SF_BYTES)));
-          const uint64_t a_desc = make_kmajor_sw128_desc(smem_u32(a_tiles + stage * F8_TILE_BYTES));
-          const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(w_tiles + stage * F8_TILE_BYTES));
+          const uint64_t sfa_desc = make_sf_desc(sfa_base + stage * F8_SF_BYTES);
+          const uint64_t sfw_desc = make_sf_desc(sfw_base + stage * F8_SF_BYTES);
+          const uint64_t a_desc = make_kmajor_sw128_desc(a_base + stage * F8_TILE_BYTES);
+          const uint64_t b_desc = make_kmajor_sw128_desc(w_base + stage * F8_TILE_BYTES);
+          if (elect_one()) {
+            tc_copy_sf(sfa_t, sfa_desc);
+            tc_copy_sf(sfw_t, sfw_desc);
+          }
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             // K block k of this stage: 32 bytes further along the swizzled row; scale byte k of each 32-bit word
             const uint32_t id = idesc | (static_cast<uint32_t>(k) << 29) | (static_cast<uint32_t>(k) << 4);
-            tc_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, id, sfa_t, sfw_t, (kb | k) != 0 ? 1u : 0u);
+            if (elect_one()) tc_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, id, sfa_t, sfw_t, (kb | k) != 0 ? 1u : 0u);
           }
-          tc_commit(&empty_bar[stage]);
+          if (elect_one()) tc_commit(&empty_bar[stage]);
           if (++stage == F8_STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) tc_commit(&acc_full_bar[acc]);
+        if (ok && elect_one()) tc_commit(&acc_full_bar[acc]);
       }
       if (!ok) {
-        atomicExch(err_flag, 2);
-        tc_commit(drain_bar);
+        if (lane == 0) atomicExch(err_flag, 2);
+        if (elect_one()) tc_commit(drain_bar);
         mbar_wait(drain_bar, 0);
       }
     }
