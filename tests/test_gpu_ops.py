@@ -136,13 +136,14 @@ def test_attention_varlen(lib, d, nh, nkv, causal):
     assert err < 2e-2, err  # P and the output are rounded to bf16 (values are O(1))
 
 
-@pytest.mark.parametrize("kind", ["wide", "rising"])
+@pytest.mark.parametrize("kind", ["wide", "rising", "extreme"])
 @pytest.mark.parametrize("d,flags", [(64, 0), (64, 0x200), (64, 1), (128, 0), (128, 1)])
 def test_attention_wide_score_range(lib, kind, d, flags):
     """Scores far above a row's first keys: the head_dim-64 kernel keeps a per-row reference point
     (maximum of the first 32 keys) and must move it, redo P and rescale O when a later score exceeds
     it by more than 2^10. 'wide' draws scores with a standard deviation of 12; 'rising' makes every
-    later key score higher than all earlier ones, so the reference moves on every key tile."""
+    later key score higher than all earlier ones, so the reference moves on every key tile; 'extreme'
+    makes the first pass overflow."""
     nh = 4
     lens = [512, 130, 257, 31, 33, 384, 96]
     cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
@@ -151,6 +152,10 @@ def test_attention_wide_score_range(lib, kind, d, flags):
     qkv = torch.randn(T, 3 * nh * d, generator=g, device="cuda")
     if kind == "wide":
         qkv[:, : nh * d] *= 12.0
+    elif kind == "extreme":
+        # scores of a few hundred: exp2 of (score - reference) overflows fp32 in the first pass wherever the
+        # reference has to move, and the second pass must leave no trace of it
+        qkv[:, : nh * d] *= 150.0
     else:
         # k_j = (j / 8) * u + noise, q_i = 8 * u + noise: score grows by about one unit per key
         u = torch.nn.functional.normalize(torch.randn(nh, d, generator=g, device="cuda"), dim=1)
