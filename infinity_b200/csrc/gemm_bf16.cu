@@ -49,8 +49,10 @@ struct GemmCfg {
   static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // two accumulator buffers
   static constexpr int CBUF_BYTES = BM * 64 * 2;  // one 128x64 bf16 output sub-tile
   static constexpr int BIAS_BYTES = 256 * 4;
-  static constexpr int BAR_BYTES = 128;
+  static constexpr int BAR_BYTES = 256;  // up to 2 x 8 stage barriers + 5 others + the TMEM address word
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * CBUF_BYTES + BIAS_BYTES + BAR_BYTES + 1024;  // + alignment slack
+  static_assert((2 * STAGES + 5) * 8 + 4 <= BAR_BYTES, "barrier area");
+  static_assert(SMEM_BYTES <= 232448, "shared memory per block");
 };
 
 __device__ __forceinline__ float rcp_approx(float x) {
