@@ -231,6 +231,117 @@ moe_router8_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   if (counts != nullptr && threadIdx.x < n_experts && cnt_s[threadIdx.x] > 0) atomicAdd(counts + threadIdx.x, cnt_s[threadIdx.x]);
 }
 
+// Router for up to 8 experts on the warp-level tensor-core instruction (mma.sync m16n8k16, bf16 x bf16 ->
+// fp32): 16 tokens x 8 experts per warp step, which makes the kernel memory-bound (x is read once).
+//  * The fp32 router matrix is split into two bf16 matrices, W = hi + lo (|W - hi - lo| <= 2^-17 |W|), and
+//    both are multiplied: the activations are bf16 already, so the products are exact and the logits keep
+//    fp32 accuracy.
+//  * The contraction index is permuted so that one 16-byte load per lane and row feeds two MMAs: within a
+//    32-column block, the lane with quad index q holds columns 8q .. 8q+7 of its two rows (g and g + 8);
+//    pairs (0,1), (2,3) go to the first MMA's k slots (2q, 2q+1), (2q+8, 2q+9), pairs (4,5), (6,7) to the
+//    second MMA's. The B fragments are laid out once per CTA in shared memory in the same permuted order
+//    ([block][lane] -> 16 bytes hi, 16 bytes lo), so consecutive lanes read consecutive 16-byte words.
+//  * The accumulator fragment leaves lane (g, q) with experts 2q, 2q+1 of tokens g and g + 8: the four
+//    lanes of a quad exchange them and compute softmax / top-k for both tokens; lane q = 0 writes.
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(MOE_WARPS * 32)
+moe_router_mma_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ wr, const float* __restrict__ br,
+                      int n_tokens, int hidden, int n_experts, int top_k, int32_t* __restrict__ topk_idx,
+                      float* __restrict__ topk_w, int32_t* __restrict__ counts) {
+  constexpr int E = 8;
+  extern __shared__ uint4 wfrag_s[];  // [hidden / 32][32 lanes][2]: hi fragment words, lo fragment words
+  __shared__ int32_t cnt_s[E];
+  const int n_blocks = hidden >> 5;
+  for (int i = threadIdx.x; i < n_blocks * 32; i += blockDim.x) {
+    const int kb = i >> 5, l = i & 31, n = l >> 2, q = l & 3;
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {  // column pairs (0,1), (2,3), (4,5), (6,7) of this lane's eight columns
+      float w0 = 0.f, w1 = 0.f;
+      if (n < n_experts) {
+        w0 = wr[static_cast<size_t>(n) * hidden + kb * 32 + q * 8 + 2 * p];
+        w1 = wr[static_cast<size_t>(n) * hidden + kb * 32 + q * 8 + 2 * p + 1];
+      }
+      const __nv_bfloat16 h0 = __float2bfloat16_rn(w0), h1 = __float2bfloat16_rn(w1);
+      const __nv_bfloat162 hh = __halves2bfloat162(h0, h1);
+      const __nv_bfloat162 ll = __floats2bfloat162_rn(w0 - __bfloat162float(h0), w1 - __bfloat162float(h1));
+      hi[p] = *reinterpret_cast<const uint32_t*>(&hh);
+      lo[p] = *reinterpret_cast<const uint32_t*>(&ll);
+    }
+    wfrag_s[2 * i] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    wfrag_s[2 * i + 1] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+  }
+  if (threadIdx.x < E) cnt_s[threadIdx.x] = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+  const int warps_total = gridDim.x * MOE_WARPS;
+  for (int t0 = (blockIdx.x * MOE_WARPS + (threadIdx.x >> 5)) * 16; t0 < n_tokens; t0 += warps_total * 16) {
+    const __nv_bfloat16* r0 = x + static_cast<size_t>(min(t0 + g, n_tokens - 1)) * hidden + q * 8;
+    const __nv_bfloat16* r1 = x + static_cast<size_t>(min(t0 + g + 8, n_tokens - 1)) * hidden + q * 8;
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+    for (int kb = 0; kb < n_blocks; ++kb) {
+      const uint4 u0 = *reinterpret_cast<const uint4*>(r0 + kb * 32);
+      const uint4 u1 = *reinterpret_cast<const uint4*>(r1 + kb * 32);
+      const uint4 wh = wfrag_s[2 * (kb * 32 + lane)];
+      const uint4 wl = wfrag_s[2 * (kb * 32 + lane) + 1];
+      const uint32_t a_first[4] = {u0.x, u1.x, u0.y, u1.y};   // (row g, row g+8) x (pair 0, pair 1)
+      const uint32_t a_second[4] = {u0.z, u1.z, u0.w, u1.w};  // pairs 2 and 3
+      mma_bf16_16816(c, a_first, wh.x, wh.y);
+      mma_bf16_16816(c, a_first, wl.x, wl.y);
+      mma_bf16_16816(c, a_second, wh.z, wh.w);
+      mma_bf16_16816(c, a_second, wl.z, wl.w);
+    }
+    // lane (g, q): c[0], c[1] = experts 2q, 2q+1 of token t0 + g; c[2], c[3] = the same of token t0 + g + 8
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      float a[E];
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        a[2 * s] = __shfl_sync(0xffffffffu, c[2 * half], (lane & ~3) + s);
+        a[2 * s + 1] = __shfl_sync(0xffffffffu, c[2 * half + 1], (lane & ~3) + s);
+      }
+      const int t = t0 + g + 8 * half;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        a[e] = e < n_experts ? a[e] + (br != nullptr ? br[e] : 0.f) : -INFINITY;
+        mx = fmaxf(mx, a[e]);
+      }
+      float den = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        a[e] = expf(a[e] - mx);  // 0 for the experts that do not exist
+        den += a[e];
+      }
+      uint32_t taken = 0;
+      for (int k = 0; k < top_k; ++k) {
+        int best = 0;
+        float bv = -1.f;
+#pragma unroll
+        for (int e = 0; e < E; ++e)
+          if (e < n_experts && !((taken >> e) & 1u) && a[e] > bv) {  // strict >: a tie keeps the lower index
+            bv = a[e];
+            best = e;
+          }
+        taken |= 1u << best;
+        if (q == 0 && t < n_tokens) {
+          topk_idx[static_cast<size_t>(t) * top_k + k] = best;
+          topk_w[static_cast<size_t>(t) * top_k + k] = bv / den;
+          atomicAdd(&cnt_s[best], 1);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (counts != nullptr && threadIdx.x < n_experts && cnt_s[threadIdx.x] > 0) atomicAdd(counts + threadIdx.x, cnt_s[threadIdx.x]);
+}
+
 // counts[e] -> seg_off[e] (row offset of expert e's segment, multiples of 128), cursor[e] = seg_off[e],
 // tile_expert[row block] = expert or -1.
 __global__ void moe_offsets_kernel(const int32_t* __restrict__ counts, int n_experts, int max_blocks,
@@ -442,6 +553,7 @@ moe_combine_ln_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
 int moe_init_device() {
   B2_CUDA_CHECK(cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
   B2_CUDA_CHECK(cudaFuncSetAttribute(moe_router8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+  B2_CUDA_CHECK(cudaFuncSetAttribute(moe_router_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
   return B200EMB_OK;
 }
 
@@ -462,6 +574,13 @@ int launch_moe_router(const void* x, const float* wr, const float* br, int n_tok
   const size_t smem = static_cast<size_t>(n_experts) * hidden * sizeof(float);
   if (smem > 96 * 1024) return set_error(B200EMB_ERR_UNSUPPORTED, "router: n_experts * hidden too large for shared memory");
   if (counts != nullptr) B2_CUDA_CHECK(cudaMemsetAsync(counts, 0, sizeof(int32_t) * n_experts, stream));
+  if (n_experts <= 8 && hidden % 32 == 0 && static_cast<size_t>(hidden) * 32 <= 96 * 1024) {
+    moe_router_mma_kernel<<<persistent_grid((n_tokens + 15) / 16), MOE_WARPS * 32, static_cast<size_t>(hidden) * 32, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x), wr, br, n_tokens, hidden, n_experts, top_k, topk_idx, topk_w, counts);
+    cudaError_t em = cudaGetLastError();
+    if (em != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "router launch: %s", cudaGetErrorString(em));
+    return B200EMB_OK;
+  }
   if (n_experts <= 8) {
     const size_t smem8 = static_cast<size_t>(8) * hidden * sizeof(float);
     if (smem8 <= 96 * 1024) {
