@@ -101,6 +101,21 @@ __device__ __forceinline__ uint32_t epilogue_pack2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&p);
 }
 
+// Tile order: groups of TILE_GROUP_M row tiles; inside a group the column tiles advance slowest, so the
+// CTAs that run at the same time share a few W tiles and a few A tiles (about sqrt(#CTAs) of each) instead
+// of one A tile and every W tile. With W larger than the L2 (a 37888 x 3584 gate/up matrix is 271 MB) the
+// plain row-major order streams all of W from HBM once per row tile.
+static constexpr int TILE_GROUP_M = 8;
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& mt, int& nt) {
+  const int group_tiles = TILE_GROUP_M * n_tiles;
+  const int group = tile / group_tiles;
+  const int first_m = group * TILE_GROUP_M;
+  const int rows_here = min(TILE_GROUP_M, m_tiles - first_m);
+  const int r = tile - group * group_tiles;
+  mt = first_m + r % rows_here;
+  nt = r / rows_here;
+}
+
 template <int BN, int EPI, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
@@ -170,11 +185,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       uint32_t issued = 0;  // slots filled so far (for draining on the error path)
       // pair: both CTAs' loads complete on the leader's full barrier, which expects both stages' bytes
       for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
-        const int m0 = (tile / n_tiles) * TILE_M + static_cast<int>(cta_rank) * BM;
-        const int n0 = (tile % n_tiles) * BN;
+        int mt, nt;
+        tile_coords(tile, m_tiles, n_tiles, mt, nt);
+        const int m0 = mt * TILE_M + static_cast<int>(cta_rank) * BM;
+        const int n0 = nt * BN;
         // grouped mode: row block m0/BM belongs to expert e (its weights are rows [e*N, e*N + N) of W);
         // e < 0 marks an unused row block, skipped by every role alike
-        const int expert = tile_expert != nullptr ? __ldg(tile_expert + tile / n_tiles) : 0;
+        const int expert = tile_expert != nullptr ? __ldg(tile_expert + mt) : 0;
         if (expert < 0) continue;
         const int w_row0 = expert * N + n0 + static_cast<int>(cta_rank) * Cfg::B_ROWS * (PAIR ? 1 : 0);
         for (int kb = 0; kb < k_blocks; ++kb) {
@@ -228,7 +245,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       bool ok = true;
       int local_tile = 0;
       for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
-        if (tile_expert != nullptr && __shfl_sync(0xffffffffu, __ldg(tile_expert + tile / n_tiles), 0) < 0) continue;
+        if (tile_expert != nullptr) {
+          int mt, nt;
+          tile_coords(tile, m_tiles, n_tiles, mt, nt);
+          if (__shfl_sync(0xffffffffu, __ldg(tile_expert + mt), 0) < 0) continue;
+        }
         const int lt = local_tile++;
         const int acc = lt & 1;
         const uint32_t acc_phase = (lt >> 1) & 1u;
@@ -303,11 +324,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     bool ok = true;
     int local_tile = 0;
     for (int tile = first_tile; tile < total_tiles; tile += tile_step) {
-      const int expert = tile_expert != nullptr ? __ldg(tile_expert + tile / n_tiles) : 0;
+      int mt, nt;
+      tile_coords(tile, m_tiles, n_tiles, mt, nt);
+      const int expert = tile_expert != nullptr ? __ldg(tile_expert + mt) : 0;
       if (expert < 0) continue;
       const int lt = local_tile++;
-      const int m0 = (tile / n_tiles) * TILE_M + static_cast<int>(cta_rank) * BM;
-      const int n0 = (tile % n_tiles) * BN;
+      const int m0 = mt * TILE_M + static_cast<int>(cta_rank) * BM;
+      const int n0 = nt * BN;
       const int acc = lt & 1;
       const uint32_t acc_phase = (lt >> 1) & 1u;
       named_barrier_sync(1, 32 * N_EPI_WARPS);  // everyone is done with the previous tile's bias
