@@ -319,7 +319,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     constexpr int SUBS = BN / 64;                               // 64-column sub-tiles per tile
     constexpr int SUBS_PER_GROUP = (SUBS >= 2) ? SUBS / 2 : 1;  // BN = 64: group 1 has none
     uint8_t* cbuf = cstage + grp * Cfg::CBUF_BYTES;
-    const bool store_thread = (ew & 3) == 0 && lane == 0;
+    // each epilogue warp stages and stores its own 32 rows (TMA box of 32 x 64): no barrier between warps
+    const bool store_thread = lane == 0;
+    const int warp_row0 = quarter * 32;
     bool ok = true;
     int local_tile = 0;
     for (int tile = first_tile; tile < total_tiles; tile += tile_step) {
@@ -346,8 +348,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         const int out_col0 = (n0 >> 1) + grp * 64;
         const bool have = (grp * 64 < BN / 2) && out_col0 < (N >> 1);  // uniform within the group
         if (have) {
-          if (store_thread) tma_store_wait_read();
-          named_barrier_sync(2 + grp, 128);
+          if (store_thread) tma_store_wait_read();  // this warp's previous store has read its rows
+          __syncwarp();
         }
         uint8_t* rowp = cbuf + row_in_tile * 128;
 #pragma unroll
@@ -388,9 +390,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
         if (have) {
           fence_proxy_async_smem();
-          named_barrier_sync(2 + grp, 128);
-          if (store_thread) {
-            tma_store_2d(&tmap_c, cbuf, out_col0, m0);
+          __syncwarp();
+          if (store_thread && m0 + warp_row0 < M) {
+            tma_store_2d(&tmap_c, cbuf + warp_row0 * 128, out_col0, m0 + warp_row0);
             tma_store_commit();
           }
         }
@@ -414,8 +416,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           }
         }
         if (sub < SUBS && n0 + sub * 64 < N) {  // uniform within the group
-          if (store_thread) tma_store_wait_read();  // the previous store out of this buffer has read it
-          named_barrier_sync(2 + grp, 128);
+          if (store_thread) tma_store_wait_read();  // this warp's previous store has read its rows
+          __syncwarp();
           const float* bsub = bias_s + sub * 64;
           uint8_t* rowp = cbuf + row_in_tile * 128;
 #pragma unroll
@@ -438,9 +440,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             *reinterpret_cast<uint4*>(rowp + ((c ^ (row_in_tile & 7)) << 4)) = packed;
           }
           fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA (async proxy)
-          named_barrier_sync(2 + grp, 128);
-          if (store_thread) {
-            tma_store_2d(&tmap_c, cbuf, n0 + sub * 64, m0);
+          __syncwarp();
+          if (store_thread && m0 + warp_row0 < M) {
+            tma_store_2d(&tmap_c, cbuf + warp_row0 * 128, n0 + sub * 64, m0 + warp_row0);
             tma_store_commit();
           }
         }
@@ -636,7 +638,7 @@ int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, i
   rc = make_tmap_bf16_2d(&tw, W, (uint64_t)N * (tile_expert != nullptr ? n_experts : 1), (uint64_t)K,
                          (uint32_t)(pair ? bn / 2 : bn));
   if (rc) return rc;
-  rc = make_tmap_bf16_2d(&tc, C, (uint64_t)M, (uint64_t)n_out, BM);
+  rc = make_tmap_bf16_2d(&tc, C, (uint64_t)M, (uint64_t)n_out, 32);  // one epilogue warp's rows per store
   if (rc) return rc;
   switch (bn) {
     case 256: return launch_epi<256>(epi, ta, tw, tc, bias, alpha, M, N, K, tile_expert, sm_count, err_flag, stream, pair);
