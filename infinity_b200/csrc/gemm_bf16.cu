@@ -55,41 +55,32 @@ struct GemmCfg {
   static_assert(SMEM_BYTES <= 232448, "shared memory per block");
 };
 
-__device__ __forceinline__ float rcp_approx(float x) {
+__device__ __forceinline__ float tanh_approx(float x) {
   float y;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-// Exact (erf) GELU for a pair of values: gelu(x) = x * Phi(x) with Phi(x) = 1 - erfc(|x|/sqrt2)/2 for
-// x >= 0 and erfc(|x|/sqrt2)/2 for x < 0, erfc from the rational form of Abramowitz & Stegun 7.1.26
-// (|error| < 1.5e-7): erfc(z) = t (a1 + t (a2 + t (a3 + t (a4 + t a5)))) exp(-z^2), t = 1 / (1 + p z).
-// Absolute error of the result < 5e-7, far below bf16 resolution; about half the instructions of erff(),
-// most of them packed fp32 pairs.
+// erf GELU for a pair of values with ONE MUFU operation per value: gelu(x) = x * Phi(x) and
+// Phi(x) = (1 + erf(x / sqrt2)) / 2 = (1 + tanh(h(x))) / 2 with h = atanh(erf(x / sqrt2)), an odd function that
+// a cubic in x^2 follows closely: h(x) = x (c0 + c1 u + c2 u^2 + c3 u^3), u = min(x^2, 25) (beyond |x| = 5 the
+// tanh is 1 to fp32 anyway). Fit error of the result < 1.2e-5 absolute; tanh.approx.f32 adds a relative error
+// of 2^-11 on tanh, i.e. < 2.5e-4 |x| on the result: a few per cent of a bf16 ulp of the output. (The earlier
+// form, erfc from Abramowitz-Stegun 7.1.26, needed a reciprocal and an exponential per value and twice the
+// instructions; the GELU epilogue, not the tensor pipe, bounds the FFN up-projection.)
 __device__ __forceinline__ float2 gelu_erf2(float2 x) {
-  const float2 z = make_float2(fabsf(x.x) * 0.70710678118654752f, fabsf(x.y) * 0.70710678118654752f);
-  const float2 d = __ffma2_rn(z, make_float2(0.3275911f, 0.3275911f), make_float2(1.f, 1.f));
-  const float2 t = make_float2(rcp_approx(d.x), rcp_approx(d.y));
-  // coefficients pre-multiplied by 1/2
-  float2 poly = make_float2(0.5f * 1.061405429f, 0.5f * 1.061405429f);
-  poly = __ffma2_rn(poly, t, make_float2(0.5f * -1.453152027f, 0.5f * -1.453152027f));
-  poly = __ffma2_rn(poly, t, make_float2(0.5f * 1.421413741f, 0.5f * 1.421413741f));
-  poly = __ffma2_rn(poly, t, make_float2(0.5f * -0.284496736f, 0.5f * -0.284496736f));
-  poly = __ffma2_rn(poly, t, make_float2(0.5f * 0.254829592f, 0.5f * 0.254829592f));
-  poly = __fmul2_rn(poly, t);
-  const float2 q = __fmul2_rn(__fmul2_rn(z, z), make_float2(-1.4426950408889634f, -1.4426950408889634f));
-  const float2 h = __fmul2_rn(poly, make_float2(ex2_approx(q.x), ex2_approx(q.y)));  // erfc(z) / 2
-  // Phi = 0.5 + copysign(0.5 - h, x)
-  const float2 r = __fadd2_rn(make_float2(0.5f, 0.5f), make_float2(-h.x, -h.y));
-  const float2 phi = __fadd2_rn(make_float2(0.5f, 0.5f), make_float2(copysignf(r.x, x.x), copysignf(r.y, x.y)));
+  const float2 xx = __fmul2_rn(x, x);
+  const float2 u = make_float2(fminf(xx.x, 25.f), fminf(xx.y, 25.f));
+  float2 p = __ffma2_rn(u, make_float2(-8.666443136e-06f, -8.666443136e-06f), make_float2(-2.5449786335e-04f, -2.5449786335e-04f));
+  p = __ffma2_rn(p, u, make_float2(3.672922030e-02f, 3.672922030e-02f));
+  p = __ffma2_rn(p, u, make_float2(7.976911068e-01f, 7.976911068e-01f));
+  const float2 h = __fmul2_rn(p, x);
+  const float2 t = make_float2(tanh_approx(h.x), tanh_approx(h.y));
+  const float2 phi = __ffma2_rn(t, make_float2(0.5f, 0.5f), make_float2(0.5f, 0.5f));
   return __fmul2_rn(x, phi);
 }
 
-__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+// silu(x) = x * sigmoid(x) = x * (1 + tanh(x / 2)) / 2: one MUFU operation
+__device__ __forceinline__ float silu_f(float x) { return x * fmaf(tanh_approx(0.5f * x), 0.5f, 0.5f); }
 
 // epilogue function on a pair of accumulators, rounded to two bf16
 template <int EPI>

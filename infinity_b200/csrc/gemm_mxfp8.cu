@@ -67,31 +67,22 @@ __host__ __device__ constexpr uint32_t make_idesc_mxf8(int m, int n) {
   return (static_cast<uint32_t>(n >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
-__device__ __forceinline__ float f8_rcp(float x) {
+// erf GELU, same formulation as the bf16 kernel: x (1 + tanh(h(x))) / 2 with h(x) = x * cubic(min(x^2, 25)),
+// one tanh.approx.f32 per value
+__device__ __forceinline__ float f8_tanh(float x) {
   float y;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ float f8_ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-// erf GELU, same formulation as the bf16 kernel (Abramowitz-Stegun 7.1.26 erfc, |error| < 5e-7)
 __device__ __forceinline__ float2 f8_gelu2(float2 x) {
-  const float2 z = make_float2(fabsf(x.x) * 0.70710678118654752f, fabsf(x.y) * 0.70710678118654752f);
-  const float2 d = __ffma2_rn(z, make_float2(0.3275911f, 0.3275911f), make_float2(1.f, 1.f));
-  const float2 t = make_float2(f8_rcp(d.x), f8_rcp(d.y));
-  float2 poly = make_float2(0.5f * 1.061405429f, 0.5f * 1.061405429f);
-  poly = __ffma2_rn(poly, t, make_float2(0.5f * -1.453152027f, 0.5f * -1.453152027f));
-  poly = __ffma2_rn(poly, t, make_float2(0.5f * 1.421413741f, 0.5f * 1.421413741f));
-  poly = __ffma2_rn(poly, t, make_float2(0.5f * -0.284496736f, 0.5f * -0.284496736f));
-  poly = __ffma2_rn(poly, t, make_float2(0.5f * 0.254829592f, 0.5f * 0.254829592f));
-  poly = __fmul2_rn(poly, t);
-  const float2 q = __fmul2_rn(__fmul2_rn(z, z), make_float2(-1.4426950408889634f, -1.4426950408889634f));
-  const float2 h = __fmul2_rn(poly, make_float2(f8_ex2(q.x), f8_ex2(q.y)));
-  const float2 r = __fadd2_rn(make_float2(0.5f, 0.5f), make_float2(-h.x, -h.y));
-  const float2 phi = __fadd2_rn(make_float2(0.5f, 0.5f), make_float2(copysignf(r.x, x.x), copysignf(r.y, x.y)));
+  const float2 xx = __fmul2_rn(x, x);
+  const float2 u = make_float2(fminf(xx.x, 25.f), fminf(xx.y, 25.f));
+  float2 p = __ffma2_rn(u, make_float2(-8.666443136e-06f, -8.666443136e-06f), make_float2(-2.5449786335e-04f, -2.5449786335e-04f));
+  p = __ffma2_rn(p, u, make_float2(3.672922030e-02f, 3.672922030e-02f));
+  p = __ffma2_rn(p, u, make_float2(7.976911068e-01f, 7.976911068e-01f));
+  const float2 h = __fmul2_rn(p, x);
+  const float2 t = make_float2(f8_tanh(h.x), f8_tanh(h.y));
+  const float2 phi = __ffma2_rn(t, make_float2(0.5f, 0.5f), make_float2(0.5f, 0.5f));
   return __fmul2_rn(x, phi);
 }
 __device__ __forceinline__ size_t sf_atom_offset(size_t row, int kblock, int k_groups) {

@@ -80,6 +80,27 @@ def test_gemm_swiglu_epilogue(lib, M, F, K):
     assert st == -1
 
 
+def test_gemm_gelu_epilogue_accuracy(lib):
+    """The GELU epilogue against the exact erf GELU, value by value: W = identity, so C = gelu(A + bias).
+    The kernel evaluates Phi through one tanh.approx.f32 per value; the result must stay within bf16 rounding
+    plus 5e-4 |x| of the exact function over the whole range, tails included."""
+    K = N = 256
+    M = 4096
+    x = torch.linspace(-9.0, 9.0, M * K, device="cuda").reshape(M, K)
+    a = x.to(torch.bfloat16)
+    w = torch.eye(N, K, device="cuda").to(torch.bfloat16)
+    bias = torch.zeros(N, device="cuda")
+    c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    _lib.check(lib.b200emb_op_gemm_bf16(a.data_ptr(), w.data_ptr(), bias.data_ptr(), c.data_ptr(), M, N, K, _lib.EPI["gelu"],
+                                        _stream()))
+    xa = a.double()
+    ref = xa * 0.5 * (1.0 + torch.erf(xa / math.sqrt(2.0)))
+    got = c.double()
+    tol = ref.abs() * 2.0 ** -8 + 5e-4 * xa.abs() + 2e-5
+    assert ((got - ref).abs() <= tol).all(), ((got - ref).abs() - tol).max().item()
+    assert (got[xa > 6] == xa[xa > 6]).all() and (got[xa < -8.5].abs() < 1e-6).all()
+
+
 def test_gemm_no_bias_and_identity(lib):
     # W = I picks out A exactly: checks the K-slice / swizzle addressing bit for bit.
     K = N = 256
