@@ -7,8 +7,9 @@
 //   softmax        128 threads, one TMEM lane (= one query row) each, ONE pass over the row in
 //                  32-key chunks whose loads run one chunk ahead of the math: p = exp2(s - m_ref)
 //                  against a per-row reference point that is the maximum of the row's first 32 keys
-//                  and is moved (with a second pass and a rescale of O) only when a later score
-//                  exceeds it by more than 2^10; no cross-thread reduction; P is rounded to bf16
+//                  and is moved (with a second pass and a rescale of O) only when a tile's row sum of
+//                  these exponentials exceeds 2^16 or overflows, so the pass tracks no maximum; no
+//                  cross-thread reduction; P is rounded to bf16
 //                  and written back to tensor memory (two keys per 32-bit column)
 //   O += P V       tcgen05.mma with the A operand read from tensor memory and V as an MN-major
 //                  shared-memory operand (no transpose of V anywhere); O accumulates in tensor
@@ -45,7 +46,7 @@ static constexpr int TC_SMEM_BYTES = TC_N_TILES * TC_TILE_BYTES + TC_STAGE_BYTES
 static constexpr int TC_THREADS = 192;         // 4 softmax warps + TMA producer warp + MMA warp
 static constexpr uint32_t TC_TMEM_COLS = 256;  // S 128 | P 64 | O 64
 static constexpr uint32_t TC_S_COL = 0, TC_P_COL = 128, TC_O_COL = 192;
-static constexpr float TC_LAZY_LOG2 = 10.f;  // how far (log2 units) a score may exceed the row's reference point
+static constexpr float TC_LAZY_SUM = 65536.f;  // a tile's row sum of exp2(score - reference) above this moves the reference
 
 #ifdef B2_ATT_PROFILE
 // Phase timing of CTA 0 / thread 0 (development aid; not part of normal builds).
@@ -369,9 +370,9 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
       // a warp whose 32 query rows all lie past the end of the sequence has nothing to compute
       const bool warp_active = t.q_start + warp * 32 < L;
       // Softmax reference point of this row (raw score units) and running denominator. The reference is
-      // NOT the running maximum: it is only moved when a score exceeds it by more than TC_LAZY_LOG2 (in
-      // log2 units), so nearly every step leaves O in tensor memory untouched; exp2 then yields values up
-      // to 2^TC_LAZY_LOG2, which numerator and denominator share.
+      // NOT the running maximum: it is only moved when a tile's sum of exp2(score - reference) exceeds
+      // TC_LAZY_SUM (or is not finite), so nearly every step leaves O in tensor memory untouched and the pass
+      // tracks no maximum at all; numerator and denominator share whatever scale the reference implies.
       float m_ref = 0.f, l_run = 0.f;
 
       for (int it = 0; it < n_kv; ++it, ++gi) {
@@ -388,18 +389,13 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
         if (warp_active) {
           uint32_t ra[32], rb[32];
           uint32_t pa[16], pb[16];
-          float mx0, mx1, l0;
+          float l0;
           float2 lsum;
           float2 negm2;
-          // One 32-key chunk: p = exp2(s * scale - m_ref * scale) as bf16 pairs; also tracks the true row
-          // maximum. Only the last, partial chunk needs masking.
+          // One 32-key chunk: p = exp2(s * scale - m_ref * scale) as bf16 pairs and their sum. Only the last,
+          // partial chunk needs masking.
           auto chunk = [&](const uint32_t (&r)[32], uint32_t (&pk)[16], int c) {
             if (c + 32 <= n_valid) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                mx0 = max3f(mx0, __uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-                mx1 = max3f(mx1, __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-              }
 #pragma unroll
               for (int j = 0; j < 32; j += 2) {
                 // packed fp32 pair: one FFMA2 / FADD2 per two keys
@@ -414,8 +410,6 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
               for (int j = 0; j < 32; j += 2) {
                 const bool v0 = c + j < n_valid, v1 = c + j + 1 < n_valid;
                 const float s0 = __uint_as_float(r[j]), s1 = __uint_as_float(r[j + 1]);
-                mx0 = fmaxf(mx0, v0 ? s0 : -INFINITY);
-                mx1 = fmaxf(mx1, v1 ? s1 : -INFINITY);
                 const float p0 = v0 ? ex2f(fmaf(s0, scale_log2, negm2.x)) : 0.f;
                 const float p1 = v1 ? ex2f(fmaf(s1, scale_log2, negm2.x)) : 0.f;
                 l0 += p0 + p1;
@@ -426,7 +420,6 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
           };
           auto store_p = [&](const uint32_t (&pk)[16], int c) { tmem_st_32x32b_x16(lane_base + TC_P_COL + (c >> 1), pk); };
           auto reset_sums = [&]() {
-            mx0 = mx1 = -INFINITY;
             l0 = 0.f;
             lsum = make_float2(0.f, 0.f);
             negm2 = make_float2(-m_ref * scale_log2, -m_ref * scale_log2);
@@ -477,14 +470,21 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
             }
             B2_PROF(3);  // softmax pass
             float alpha = 1.f;
-            const float mx = fmaxf(mx0, mx1);
-            const bool move_ref = (mx - m_ref) * scale_log2 > TC_LAZY_LOG2;
+            const bool move_ref = !(l0 + (lsum.x + lsum.y) <= TC_LAZY_SUM);  // also true for inf / NaN
             if (__any_sync(0xffffffffu, move_ref)) {
-              // Rare: some row of this warp met a score far above its reference point. Move the reference
-              // to the row maximum, redo this tile's P with it and rescale what O and l hold so far.
+              // Rare: some row of this warp met scores far above its reference point. Move the reference to
+              // the row maximum of this tile, redo the tile's P with it and rescale what O and l hold so far.
+              float mx = -INFINITY;
+              for (int c = 0; c < n_eff; c += 32) {
+                tmem_ld_32x32b_x32(lane_base + TC_S_COL + c, ra);
+                tmem_ld_wait_for(ra);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) mx = fmaxf(mx, c + j < n_valid ? __uint_as_float(ra[j]) : -INFINITY);
+              }
               if (move_ref) {
-                alpha = ex2f((m_ref - mx) * scale_log2);
-                m_ref = mx;
+                const float m_new = fmaxf(m_ref, mx);  // fmaxf drops a NaN maximum (rows past the sequence end)
+                alpha = ex2f((m_ref - m_new) * scale_log2);
+                m_ref = m_new;
               }
               reset_sums();
               for (int c = 0; c < n_eff; c += 32) {

@@ -11,8 +11,9 @@
 //   softmax        128 threads, one TMEM lane (= one query row) each, one pass over the row in
 //                  32-key chunks whose loads run one chunk ahead of the math: p = exp2(s - m_ref)
 //                  against a per-row reference point that is the maximum of the row's first 32 valid
-//                  keys and is moved (second pass + rescale of O) only when a later score exceeds it
-//                  by more than 2^10. Causal masking touches only the diagonal key tile. P is rounded
+//                  keys and is moved (second pass + rescale of O) only when a tile's row sum of these
+//                  exponentials exceeds 2^16 or overflows, so the pass tracks no maximum.
+//                  Causal masking touches only the diagonal key tile. P is rounded
 //                  to bf16 and written to tensor memory (two keys per 32-bit column).
 //   O += P V       tcgen05.mma with A = P from tensor memory and V as an MN-major shared-memory
 //                  operand; O accumulates in tensor memory and is read once per query tile, during the
@@ -39,7 +40,7 @@ static constexpr int T2_BOX_BYTES = 128 * 64 * 2;  // one TMA box: 128 rows x 64
 static constexpr int T2_THREADS = 224;
 static constexpr uint32_t T2_TMEM_COLS = 512;
 static constexpr uint32_t T2_S_COL = 0, T2_P_COL = 256, T2_O_COL = 320;
-static constexpr float T2_LAZY_LOG2 = 10.f;  // how far (log2 units) a score may exceed the row's reference point
+static constexpr float T2_LAZY_SUM = 65536.f;  // a tile's row sum of exp2(score - reference) above this moves the reference
 
 #ifdef B2_ATT_PROFILE
 // Phase timing of CTA 0 (development aid; not part of normal builds).
@@ -414,9 +415,9 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __r
       // a warp whose 32 query rows all lie past the end of the sequence has nothing to compute
       const bool warp_active = t.q_start + warp * 32 < L;
       // Softmax reference point of this row (raw score units) and running denominator. The reference is
-      // NOT the running maximum: it is only moved when a score exceeds it by more than T2_LAZY_LOG2 (in
-      // log2 units), so nearly every step leaves O in tensor memory untouched; exp2 then yields values up
-      // to 2^T2_LAZY_LOG2, which numerator and denominator share.
+      // NOT the running maximum: it is only moved when a tile's sum of exp2(score - reference) exceeds
+      // T2_LAZY_SUM (or is not finite), so nearly every step leaves O in tensor memory untouched and the pass
+      // tracks no maximum at all; numerator and denominator share whatever scale the reference implies.
       float m_ref = 0.f, l_run = 0.f;
 
       for (int it = 0; it < n_kv; ++it, ++gi) {
@@ -443,19 +444,13 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __r
         if (warp_active) {
           uint32_t ra[32], rb[32];
           uint32_t pa[16], pb[16];
-          float mx0, mx1, l0;
+          float l0;
           float2 lsum;
           float2 negm2;
-          // One 32-key chunk: p = exp2(s * scale - m_ref * scale) as bf16 pairs; also tracks the true row
-          // maximum. Chunks that are valid for the whole warp take the unmasked path, chunks past every
+          // One 32-key chunk: p = exp2(s * scale - m_ref * scale) as bf16 pairs and their sum. Chunks that are valid for the whole warp take the unmasked path, chunks past every
           // row's limit are zeros.
           auto chunk = [&](const uint32_t (&r)[32], uint32_t (&pk)[16], int c) {
             if (c + 32 <= lim_lo) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                mx0 = t2_max3(mx0, __uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-                mx1 = t2_max3(mx1, __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-              }
 #pragma unroll
               for (int j = 0; j < 32; j += 2) {
                 // packed fp32 pair: one FFMA2 / FADD2 per two keys
@@ -473,8 +468,6 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __r
               for (int j = 0; j < 32; j += 2) {
                 const bool v0 = c + j < lim, v1 = c + j + 1 < lim;
                 const float s0 = __uint_as_float(r[j]), s1 = __uint_as_float(r[j + 1]);
-                mx0 = fmaxf(mx0, v0 ? s0 : -INFINITY);
-                mx1 = fmaxf(mx1, v1 ? s1 : -INFINITY);
                 const float p0 = v0 ? t2_ex2(fmaf(s0, scale_log2, negm2.x)) : 0.f;
                 const float p1 = v1 ? t2_ex2(fmaf(s1, scale_log2, negm2.x)) : 0.f;
                 l0 += p0 + p1;
@@ -485,7 +478,6 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __r
           };
           auto store_p = [&](const uint32_t (&pk)[16], int c) { tmem_st_32x32b_x16(lane_base + T2_P_COL + (c >> 1), pk); };
           auto reset_sums = [&]() {
-            mx0 = mx1 = -INFINITY;
             l0 = 0.f;
             lsum = make_float2(0.f, 0.f);
             negm2 = make_float2(-m_ref * scale_log2, -m_ref * scale_log2);
@@ -536,14 +528,21 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __r
               }
             }
             float alpha = 1.f;
-            const float mx = fmaxf(mx0, mx1);
-            const bool move_ref = (mx - m_ref) * scale_log2 > T2_LAZY_LOG2;
+            const bool move_ref = !(l0 + (lsum.x + lsum.y) <= T2_LAZY_SUM);  // also true for inf / NaN
             if (__any_sync(0xffffffffu, move_ref)) {
-              // Rare: some row of this warp met a score far above its reference point. Move the reference
-              // to the row maximum, redo this tile's P with it and rescale what O and l hold so far.
+              // Rare: some row of this warp met scores far above its reference point. Move the reference to
+              // the row maximum of this tile, redo the tile's P with it and rescale what O and l hold so far.
+              float mx = -INFINITY;
+              for (int c = 0; c < n_eff; c += 32) {
+                tmem_ld_32x32b_x32(s_base + c, ra);
+                tmem_ld_wait_for(ra);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) mx = fmaxf(mx, c + j < lim ? __uint_as_float(ra[j]) : -INFINITY);
+              }
               if (move_ref) {
-                alpha = t2_ex2((m_ref - mx) * scale_log2);
-                m_ref = mx;
+                const float m_new = fmaxf(m_ref, mx);  // fmaxf drops a NaN maximum (rows past the sequence end)
+                alpha = t2_ex2((m_ref - m_new) * scale_log2);
+                m_ref = m_new;
               }
               reset_sums();
               for (int c = 0; c < n_eff; c += 32) {
