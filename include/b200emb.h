@@ -105,7 +105,12 @@ typedef struct b200emb_model_desc {
   int32_t n_labels;
   int32_t weight_format;
   int32_t max_tokens; /* workspace sizing hint (tokens per device per call); workspaces grow when exceeded */
-  int32_t reserved[8];
+  /* 1 (classifier head only): the output rows are scores instead of raw logits, computed on the device:
+   * softmax over the n_labels logits, the logistic function when n_labels == 1. The reference does this
+   * on the host after the copy (text-classification pipeline behind classifier/torch.py:38-46, 74-80;
+   * rerank scores: batch_handler.py:207-210). */
+  int32_t label_scores;
+  int32_t reserved[7]; /* zero */
 } b200emb_model_desc;
 
 /* Wall and device times of one b200emb_forward call. Device times come from

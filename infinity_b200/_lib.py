@@ -32,7 +32,7 @@ class ModelDesc(C.Structure):
         ("norm_eps", C.c_float), ("rope_theta", C.c_float), ("n_experts", C.c_int32), ("top_k", C.c_int32),
         ("moe_every", C.c_int32), ("pooling", C.c_int32), ("normalize", C.c_int32), ("head", C.c_int32),
         ("n_labels", C.c_int32), ("weight_format", C.c_int32), ("max_tokens", C.c_int32),
-        ("reserved", C.c_int32 * 8),
+        ("label_scores", C.c_int32), ("reserved", C.c_int32 * 7),
     ]
 
 

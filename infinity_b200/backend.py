@@ -18,6 +18,7 @@ them propagates, as in the reference (batch_handler.py:556-558, 586-588, 622-624
 """
 from __future__ import annotations
 
+import dataclasses
 import threading
 from time import perf_counter
 from typing import Any, Dict, List, Optional, Sequence, Tuple
@@ -184,7 +185,11 @@ class B200CrossEncoder(_B200Backend):
 class B200Classifier(_B200Backend):
     capabilities = {"classify"}
 
-    def __init__(self, *, labels: Optional[Sequence[str]] = None, **kw):
+    def __init__(self, *, labels: Optional[Sequence[str]] = None, device_scores: bool = False, **kw):
+        """``device_scores``: the softmax / sigmoid over the labels runs on the GPU behind the head
+        (``ModelSpec.label_scores``) and ``encode_post`` only sorts and names the rows."""
+        if device_scores:
+            kw["spec"] = dataclasses.replace(kw["spec"], label_scores=True)
         super().__init__(**kw)
         n = self.spec.n_labels
         self.labels = list(labels) if labels is not None else [f"LABEL_{i}" for i in range(n)]
@@ -204,7 +209,9 @@ class B200Classifier(_B200Backend):
         (classifier/torch.py:38-46, 74-80): per input, one dict per label sorted by score
         descending; softmax over the labels, or a sigmoid for a single-label head."""
         x = np.asarray(logits, dtype=np.float64)
-        if x.shape[1] == 1:
+        if self.spec.label_scores:
+            scores = x
+        elif x.shape[1] == 1:
             scores = 1.0 / (1.0 + np.exp(-x))
         else:
             z = x - x.max(axis=1, keepdims=True)

@@ -37,6 +37,7 @@ class ModelSpec:
     normalize: bool = True
     head: str = "none"            # none | classifier
     n_labels: int = 0
+    label_scores: bool = False    # classifier head: softmax (sigmoid for one label) applied on the device
     weight_format: str = "bf16"
     weight_dtype: str = "bf16"    # storage precision the oracle sees: "fp32" or "bf16"
     max_len: int = 512            # longest sequence the model accepts (tokens)

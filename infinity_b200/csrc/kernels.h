@@ -127,5 +127,7 @@ int launch_pool(const void* x, const int32_t* d_cu, int n_seqs, int hidden, int 
 // logits[i, l] = dot(x[i, :], W[l, :]) + b[l]; x bf16 [n, hidden], W bf16 [n_labels, hidden], out fp32.
 int launch_small_proj(const void* x, const void* W, const float* bias, int n_rows, int hidden, int n_labels,
                       float* out, int64_t out_row_stride, cudaStream_t stream);
+// softmax over each row's n_labels logits (logistic function when n_labels == 1), in place
+int launch_label_scores(float* logits, int n_rows, int n_labels, int64_t row_stride, cudaStream_t stream);
 
 }  // namespace b2

@@ -522,6 +522,29 @@ small_proj_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
   if (lane == 0) out[static_cast<size_t>(row) * out_row_stride + label] = acc + (bias != nullptr ? bias[label] : 0.f);
 }
 
+// Scores of a classification head, in place on its fp32 logits: softmax over the labels of a row, or the
+// logistic function when the head has one output. One warp per row; labels are strided over the lanes.
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+label_scores_kernel(float* __restrict__ logits, int n_rows, int n_labels, int64_t row_stride) {
+  const int row = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const int lane = threadIdx.x & 31;
+  float* r = logits + static_cast<size_t>(row) * row_stride;
+  if (n_labels == 1) {
+    if (lane == 0) r[0] = 1.f / (1.f + expf(-r[0]));
+    return;
+  }
+  float mx = -INFINITY;
+  for (int j = lane; j < n_labels; j += 32) mx = fmaxf(mx, r[j]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+  for (int j = lane; j < n_labels; j += 32) sum += expf(r[j] - mx);
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  for (int j = lane; j < n_labels; j += 32) r[j] = expf(r[j] - mx) * inv;
+}
+
 // ---- launchers ------------------------------------------------------------------
 
 static int check_hidden(int hidden, int max_chunks_per_lane) {
@@ -776,6 +799,15 @@ int launch_small_proj(const void* x, const void* W, const float* bias, int n_row
                                                          hidden, n_labels, out, out_row_stride);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "small_proj launch: %s", cudaGetErrorString(e));
+  return B200EMB_OK;
+}
+
+int launch_label_scores(float* logits, int n_rows, int n_labels, int64_t row_stride, cudaStream_t stream) {
+  if (n_rows <= 0 || n_labels <= 0) return B200EMB_OK;
+  const int grid = (n_rows + ROW_WARPS - 1) / ROW_WARPS;
+  label_scores_kernel<<<grid, ROW_WARPS * 32, 0, stream>>>(logits, n_rows, n_labels, row_stride);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "label_scores launch: %s", cudaGetErrorString(e));
   return B200EMB_OK;
 }
 

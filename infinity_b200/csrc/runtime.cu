@@ -474,6 +474,8 @@ static int validate_desc(const b200emb_model_desc& d) {
     return set_error(B200EMB_ERR_INVALID, "per-token outputs need head = none");
   if (d.head == B200EMB_HEAD_CLASSIFIER && d.n_labels <= 0) return set_error(B200EMB_ERR_INVALID, "classifier head needs n_labels > 0");
   if (d.head != B200EMB_HEAD_NONE && d.head != B200EMB_HEAD_CLASSIFIER) return set_error(B200EMB_ERR_INVALID, "unknown head %d", d.head);
+  if (d.label_scores != 0 && (d.label_scores != 1 || d.head != B200EMB_HEAD_CLASSIFIER))
+    return set_error(B200EMB_ERR_INVALID, "label_scores is 0 or 1 and needs the classifier head");
   if (d.pos_offset < 0 || d.pos_offset >= d.max_pos) return set_error(B200EMB_ERR_INVALID, "pos_offset out of range");
   return B200EMB_OK;
 }
@@ -768,6 +770,10 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
       rc = launch_small_proj(c->head_h, w.head_out_w, w.head_out_b, n_seqs, H, d.n_labels, d_out, out_row_stride,
                              c->stream);
       if (rc) return rc;
+      if (d.label_scores) {
+        rc = launch_label_scores(d_out, n_seqs, d.n_labels, out_row_stride, c->stream);
+        if (rc) return rc;
+      }
     }
   }
   return B200EMB_OK;

@@ -30,6 +30,7 @@ def make_desc(spec: ModelSpec, max_tokens: int = 0) -> _lib.ModelDesc:
     d.normalize = 1 if spec.normalize else 0
     d.head = _lib.HEAD[spec.head]
     d.n_labels = spec.n_labels
+    d.label_scores = 1 if spec.label_scores else 0
     d.weight_format = _lib.WFMT[spec.weight_format]
     d.max_tokens = max_tokens
     return d

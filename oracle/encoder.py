@@ -121,13 +121,26 @@ def pad_batch(seqs, types=None, pad_id: int = 0):
     return ids, mask, tt
 
 
+def label_scores(logits: np.ndarray) -> np.ndarray:
+    """Raw logits [B, n_labels] -> scores: softmax over the labels, the logistic function for a
+    single-output head -- what the text-classification pipeline behind the reference's classifier
+    applies (infinity_emb/transformer/classifier/torch.py:38-46, 74-80) and what its batcher applies to
+    rerank logits (infinity_emb/inference/batch_handler.py:207-210). float64 arithmetic, float32 result."""
+    x = np.asarray(logits, dtype=np.float64)
+    if x.shape[1] == 1:
+        return (1.0 / (1.0 + np.exp(-x))).astype(np.float32)
+    e = np.exp(x - x.max(axis=1, keepdims=True))
+    return (e / e.sum(axis=1, keepdims=True)).astype(np.float32)
+
+
 @torch.no_grad()
 def forward_padded(spec, W, ids, mask, types=None) -> np.ndarray:
     """One padded batch -> [B, out_dim] float32 (embeddings, or raw logits for classifier heads)."""
     h = encoder_hidden(spec, W, ids, mask, types)
     if spec.head == "classifier":
         c = torch.tanh(h[:, 0] @ W["head.dense.w"].t() + W["head.dense.b"])
-        return (c @ W["head.out.w"].t() + W["head.out.b"]).float().numpy()
+        logits = (c @ W["head.out.w"].t() + W["head.out.b"]).float().numpy()
+        return label_scores(logits) if getattr(spec, "label_scores", False) else logits
     if spec.pooling == "tokens":
         raise ValueError("token-level outputs are ragged: use forward_tokens")
     pooled = P.POOLERS[spec.pooling](h.numpy(), mask.numpy())

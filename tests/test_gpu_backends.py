@@ -117,3 +117,9 @@ def test_cross_encoder_and_classifier_backends(tmp_path):
         assert [d["label"] for d in row] == [["neg", "neu", "pos"][j] for j in np.argsort(-p)]
         assert abs(row[0]["score"] - p.max()) < 1e-2
     clf.model.close()
+    dev = B200Classifier(spec=spec3, weight_path=path3, device_ids=(0,), labels=["neg", "neu", "pos"], device_scores=True)
+    res_dev = dev.encode_post(dev.encode_core(dev.encode_pre(sentences)))
+    for row, row_dev in zip(res, res_dev):
+        assert [d["label"] for d in row] == [d["label"] for d in row_dev]
+        assert max(abs(a["score"] - b["score"]) for a, b in zip(row, row_dev)) < 1e-5
+    dev.model.close()

@@ -97,6 +97,34 @@ def test_tiny_reranker_matches_oracle(tmp_path):
     model.close()
 
 
+@pytest.mark.parametrize("n_labels", [1, 3, 40])
+def test_label_scores_on_the_device(tmp_path, n_labels):
+    """softmax over the labels (sigmoid for one label) behind the classifier head equals the oracle's
+    float64 softmax of its own logits; rows of a multi-label head sum to 1"""
+    import dataclasses
+    spec = dataclasses.replace(cf.tiny_spec("xlmr", n_labels=n_labels), label_scores=True)
+    model, W = build_model(tmp_path, spec, 15 + n_labels, perturb=True)
+    batch = cf.random_batch(spec, [4, 30, 99, 158, 64, 1], 7)
+    got = model.forward(batch)
+    ref = enc.forward_batch(spec, W, batch)
+    raw = enc.forward_batch(dataclasses.replace(spec, label_scores=False), W, batch)
+    assert got.shape == (6, n_labels) and ref.shape == got.shape
+    assert np.allclose(ref, enc.label_scores(raw), atol=1e-7)
+    assert np.abs(got - ref).max() <= LOGIT_TOL, (got, ref)
+    assert (got >= 0).all() and (got <= 1).all()
+    if n_labels > 1:
+        assert np.abs(got.sum(1) - 1.0).max() <= 1e-5
+    model.close()
+
+
+def test_label_scores_need_a_classifier_head(tmp_path):
+    import dataclasses
+    from infinity_b200._lib import B200EmbError
+    spec = dataclasses.replace(cf.tiny_spec("bert"), label_scores=True)
+    with pytest.raises(B200EmbError, match="label_scores"):
+        build_model(tmp_path, spec, 16, perturb=False)
+
+
 def _oracle_forward(spec, W, batch):
     if spec.arch == "decoder":
         from oracle import decoder as dec

@@ -10,6 +10,7 @@ import numpy as np
 import pytest
 import torch
 
+from infinity_b200 import batching as bt
 from infinity_b200 import configs as cf
 from infinity_b200 import packing as pk
 from infinity_b200 import weights as wt
@@ -110,6 +111,46 @@ def test_classifier_post_processing():
     assert abs(single.encode_post(np.array([[0.0]], dtype=np.float32))[0][0]["score"] - 0.5) < 1e-7
     with pytest.raises(ValueError):
         B200Classifier(spec=spec, model=FakeDeviceModel(3), labels=["a"])
+
+
+def test_classifier_with_device_scores_only_sorts():
+    spec = cf.tiny_spec("xlmr", n_labels=3)
+    clf = B200Classifier(spec=spec, model=FakeDeviceModel(3), labels=["neg", "neu", "pos"], device_scores=True)
+    assert clf.spec.label_scores and not spec.label_scores
+    out = clf.encode_post(np.array([[0.2, 0.7, 0.1]], dtype=np.float32))
+    assert [(d["label"], round(d["score"], 6)) for d in out[0]] == [("neu", 0.7), ("neg", 0.2), ("pos", 0.1)]
+
+
+def test_count_batches_restates_the_reference_cut():
+    lengths = [9, 3, 7, 1, 5, 8, 2]
+    # more items than one batch: sorted by length, then cut every `size`
+    assert bt.count_batches(lengths, 3) == [[3, 6, 1], [4, 2, 5], [0]]
+    # a single batch keeps arrival order
+    assert bt.count_batches(lengths, 8) == [list(range(7))]
+    assert bt.count_batches([], 4) == []
+
+
+def test_token_budget_batches():
+    rng = np.random.default_rng(0)
+    lengths = rng.integers(1, 513, size=1000).tolist()
+    batches = bt.token_budget_batches(lengths, 8192, max_seqs=64)
+    assert sorted(i for b in batches for i in b) == list(range(1000))
+    for b in batches:
+        assert len(b) <= 64 and sum(lengths[i] for i in b) <= 8192
+    flat = [lengths[i] for b in batches for i in b]
+    assert flat == sorted(lengths)
+    # no batch could have taken the first item of the next one
+    for b, nxt in zip(batches, batches[1:]):
+        assert len(b) == 64 or sum(lengths[i] for i in b) + lengths[nxt[0]] > 8192
+    # a huge budget leaves the count limit alone: the reference's cut
+    assert bt.token_budget_batches(lengths, 10 ** 9, max_seqs=32) == bt.count_batches(lengths, 32, sort=True)
+    # an item above the budget is a batch of its own
+    assert bt.token_budget_batches([5, 100, 6], 20) == [[0, 2], [1]]
+    # the quadratic term makes long sequences dearer
+    assert len(bt.token_budget_batches([100] * 8, 400)) == 2
+    assert len(bt.token_budget_batches([100] * 8, 400, quadratic_weight=0.01)) == 4
+    with pytest.raises(ValueError):
+        bt.token_budget_batches([1], 0)
 
 
 def test_backend_warmup_contract():

@@ -210,3 +210,16 @@ def test_output_quantisation_known_answers():
     assert QE.quantize_embeddings(y, "uint8").tolist() == [[0, 254], [254, 0], [63, 127]]
     rng = QE.calibration_ranges(y)
     assert rng.shape == (2, 2) and rng.dtype == np.float64 and rng.tolist() == [[0.0, 0.0], [1.0, 1.0]]
+
+
+def test_label_scores_match_the_text_classification_pipeline():
+    """The reference's classifier is a transformers text-classification pipeline with top_k=None
+    (classifier/torch.py:38-46): its post-processing functions are the pin for the oracle's scores."""
+    tc = pytest.importorskip("transformers.pipelines.text_classification")
+    rng = np.random.default_rng(5)
+    logits = (rng.standard_normal((7, 5)) * 4).astype(np.float32)
+    assert np.allclose(enc.label_scores(logits), tc.softmax(logits), atol=1e-7)
+    single = (rng.standard_normal((7, 1)) * 4).astype(np.float32)
+    assert np.allclose(enc.label_scores(single), tc.sigmoid(single), atol=1e-7)
+    assert np.allclose(enc.label_scores(np.array([[0.0]], dtype=np.float32)), [[0.5]])
+    assert np.allclose(enc.label_scores(np.array([[1000.0, 0.0]], dtype=np.float32)), [[1.0, 0.0]])
