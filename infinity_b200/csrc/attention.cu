@@ -83,6 +83,8 @@ attn_varlen_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restr
   __nv_bfloat16* Ks = Qs + ATT_BQ * LD;
   __nv_bfloat16* Vs = Ks + 2 * ATT_BKV * LD;
 
+  pdl_wait();  // qkv is the previous kernel's result
+  pdl_launch_dependents();
   const AttnTile t = tiles[blockIdx.x];
   const int h = blockIdx.y;
   const int hk = h / (n_heads / n_kv_heads);
@@ -294,13 +296,13 @@ static int launch_d(const void* qkv, void* out, const AttnTile* d_tiles, int n_t
   dim3 grid(n_tiles, n_heads);
   const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(qkv);
   __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
+  cudaError_t e;
   if (causal)
-    attn_varlen_kernel<D, true><<<grid, ATT_THREADS, att_smem_bytes<D>(), stream>>>(q, o, d_tiles, n_heads,
-                                                                                     n_kv_heads, scale_log2);
+    e = launch_pdl(attn_varlen_kernel<D, true>, grid, dim3(ATT_THREADS), att_smem_bytes<D>(), stream, q, o, d_tiles,
+                   n_heads, n_kv_heads, scale_log2);
   else
-    attn_varlen_kernel<D, false><<<grid, ATT_THREADS, att_smem_bytes<D>(), stream>>>(q, o, d_tiles, n_heads,
-                                                                                      n_kv_heads, scale_log2);
-  cudaError_t e = cudaGetLastError();
+    e = launch_pdl(attn_varlen_kernel<D, false>, grid, dim3(ATT_THREADS), att_smem_bytes<D>(), stream, q, o, d_tiles,
+                   n_heads, n_kv_heads, scale_log2);
   if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "attention launch: %s", cudaGetErrorString(e));
   return B200EMB_OK;
 }

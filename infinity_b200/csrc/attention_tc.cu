@@ -100,6 +100,7 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
   static_assert((2 * TC_QSLOTS + 2 * TC_KSLOTS + 2 * TC_VSLOTS + 3) * 8 + 4 <= TC_BAR_BYTES, "barrier area");
   // shared memory too small once aligned: report and leave before anything is initialised (uniform per CTA)
   if (smem + TC_N_TILES * TC_TILE_BYTES + TC_STAGE_BYTES + TC_BAR_BYTES > att_raw + TC_SMEM_BYTES) {
+    pdl_wait();
     if (threadIdx.x == 0) atomicExch(err_flag, 6);
     return;
   }
@@ -133,6 +134,8 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // The set-up above touched no global memory: it may overlap the tail of the previous kernel in the stream.
+  pdl_wait();
 
   if (warp == 4) {
     // ---------------- TMA producer ----------------
@@ -185,6 +188,7 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
           }
         }
       }
+      pdl_launch_dependents();  // every load of this CTA is issued: the next kernel may start its set-up
       if (!ok) {
         atomicExch(err_flag, 5);
         // let the copies still in flight land before shared memory is released (bounded)
@@ -587,10 +591,9 @@ int launch_attention_tc(const void* qkv, void* out, const AttnTile* d_tiles, int
   const long long n_items = static_cast<long long>(n_tiles) * n_heads;
   if (n_items > 0x7fffffffLL) return set_error(B200EMB_ERR_UNSUPPORTED, "attention: too many tiles");
   const int grid = static_cast<int>(n_items < 2LL * sm_count ? n_items : 2LL * sm_count);
-  attn_tc_d64_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(tm, reinterpret_cast<__nv_bfloat16*>(out), d_tiles,
-                                                                 static_cast<int>(n_items), n_heads, n_kv_heads,
-                                                                 scale_log2, err_flag);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(attn_tc_d64_kernel, dim3(grid), dim3(TC_THREADS), TC_SMEM_BYTES, stream, tm,
+                             reinterpret_cast<__nv_bfloat16*>(out), d_tiles, static_cast<int>(n_items), n_heads,
+                             n_kv_heads, scale_log2, err_flag);
   if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "attention launch: %s", cudaGetErrorString(e));
   return B200EMB_OK;
 }

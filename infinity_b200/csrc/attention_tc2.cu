@@ -151,6 +151,8 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __r
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // The set-up above touched no global memory: it may overlap the tail of the previous kernel in the stream.
+  pdl_wait();
 
   if (warp == 4) {
     // ---------------- TMA producer: Q and K ----------------
@@ -196,6 +198,7 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __r
           }
         }
       }
+      pdl_launch_dependents();  // every Q / K load of this CTA is issued: the next kernel may start its set-up
       if (!ok) {
         atomicExch(err_flag, 5);
         // let the copies still in flight land before shared memory is released (bounded)
@@ -637,8 +640,8 @@ template <int D, bool CAUSAL>
 static void t2_launch(const CUtensorMap& tm, void* out, const AttnTile* d_tiles, int n_items, int n_heads, int n_kv_heads,
                       int grid, int* err_flag, cudaStream_t stream) {
   const float scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(D));
-  attn_tc2_kernel<D, CAUSAL><<<grid, T2_THREADS, T2Cfg<D>::SMEM_BYTES, stream>>>(
-      tm, reinterpret_cast<__nv_bfloat16*>(out), d_tiles, n_items, n_heads, n_kv_heads, scale_log2, err_flag);
+  launch_pdl(attn_tc2_kernel<D, CAUSAL>, dim3(grid), dim3(T2_THREADS), T2Cfg<D>::SMEM_BYTES, stream, tm,
+             reinterpret_cast<__nv_bfloat16*>(out), d_tiles, n_items, n_heads, n_kv_heads, scale_log2, err_flag);
 }
 
 int launch_attention_tc2(const void* qkv, void* out, const AttnTile* d_tiles, int n_tiles, int n_tokens, int n_heads,

@@ -197,11 +197,14 @@ add_ln_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   extern __shared__ float ln_smem[];  // gamma[hidden], beta[hidden]
   float* g_s = ln_smem;
   float* b_s = ln_smem + hidden;
+  // gamma and beta are weights, which no kernel writes: they are staged while the previous kernel in the
+  // stream may still be running; x and y are its results and are read only after pdl_wait().
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     g_s[i] = gamma[i];
     b_s[i] = beta[i];
   }
   __syncthreads();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int n_chunks = hidden >> 3;
   const int warps_total = gridDim.x * ROW_WARPS;
@@ -238,6 +241,7 @@ add_ln_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
     }
     const int next = row + warps_total;
     if (next < n_rows) load_row(next);  // in flight while this row is reduced and stored
+    else pdl_launch_dependents();       // last row of this warp: the next kernel may start its set-up
     layernorm_store<NCH>(v, lane, n_chunks, hidden, g_s, b_s, eps, out + static_cast<size_t>(row) * hidden);
     row = next;
   }
@@ -606,10 +610,10 @@ int launch_add_ln(const void* x, const void* y, const float* gamma, const float*
   const int full = (n_rows + ROW_WARPS - 1) / ROW_WARPS;
   const int grid = full < sms * 4 ? full : sms * 4;  // persistent: a few CTAs per SM walk all rows
   const size_t ln_smem = 2 * static_cast<size_t>(hidden) * sizeof(float);
-  B2_DISPATCH_NCH(nch, (add_ln_kernel<NCH><<<grid, ROW_WARPS * 32, ln_smem, stream>>>(
-                           reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(y),
-                           gamma, beta, n_rows, hidden, eps, reinterpret_cast<__nv_bfloat16*>(out))));
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = cudaSuccess;
+  B2_DISPATCH_NCH(nch, (e = launch_pdl(add_ln_kernel<NCH>, dim3(grid), dim3(ROW_WARPS * 32), ln_smem, stream,
+                                       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(y),
+                                       gamma, beta, n_rows, hidden, eps, reinterpret_cast<__nv_bfloat16*>(out))));
   if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "add_ln launch: %s", cudaGetErrorString(e));
   return B200EMB_OK;
 }

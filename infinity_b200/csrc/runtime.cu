@@ -24,6 +24,20 @@ namespace b2 {
 // ---- errors -----------------------------------------------------------------------
 static thread_local char g_err[512] = "";
 
+// B200EMB_PDL: unset = by batch size (pdl_for_tokens), 0 = never, 1 = always.
+static int pdl_env() {
+  static const int mode = [] {
+    const char* v = getenv("B200EMB_PDL");
+    return v == nullptr ? -1 : (v[0] == '0' ? 0 : 1);
+  }();
+  return mode;
+}
+static thread_local bool g_pdl_small_batch = true;
+
+bool pdl_enabled() { return pdl_env() < 0 ? g_pdl_small_batch : pdl_env() == 1; }
+
+void pdl_for_tokens(int n_tokens) { g_pdl_small_batch = n_tokens <= PDL_MAX_TOKENS; }
+
 int set_error(int code, const char* fmt, ...) {
   va_list ap;
   va_start(ap, fmt);
@@ -594,6 +608,7 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
   const int H = d.hidden, F = d.ffn, T = n_tokens;
   const int QKV = (d.n_heads + 2 * d.n_kv_heads) * d.head_dim;
   int rc;
+  pdl_for_tokens(T);
   if (d.arch == B200EMB_ARCH_DECODER) {
     // pre-RMSNorm decoder block (Qwen2): h is the fp32 residual stream
     {

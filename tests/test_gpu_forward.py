@@ -117,6 +117,19 @@ def test_label_scores_on_the_device(tmp_path, n_labels):
     model.close()
 
 
+def test_repeated_small_forwards_are_bit_identical(tmp_path):
+    """Small batches run with programmatic dependent launch (each kernel's set-up overlaps its predecessor's
+    tail): a kernel that touched its inputs before the predecessor finished would show as run-to-run noise."""
+    spec = cf.tiny_spec("bert", hidden=128, n_heads=2, n_kv_heads=2, head_dim=64, ffn=256, max_pos=256)
+    model, W = build_model(tmp_path, spec, 21, perturb=True)
+    batch = cf.random_batch(spec, [5, 130, 64, 17, 200, 1, 33], 9)
+    first = model.forward(batch).copy()
+    assert cosines(first, enc.forward_batch(spec, W, batch)).min() >= COS_TOL
+    for _ in range(40):
+        assert np.array_equal(model.forward(batch), first)
+    model.close()
+
+
 def test_label_scores_need_a_classifier_head(tmp_path):
     import dataclasses
     from infinity_b200._lib import B200EmbError
