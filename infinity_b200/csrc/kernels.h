@@ -30,13 +30,14 @@ int set_error(int code, const char* fmt, ...);
 // prefetch) overlaps the predecessor's tail. Such a kernel executes pdl_wait() (ptx.cuh) in every thread before
 // its first access to global memory; the wait returns when the predecessor grid has completed and its writes
 // are visible. The overlap is worth about 2 us per launch: 14 % of a 7.7 k-token bge-small-shape forward
-// (86 launches, 1.44 -> 1.24 ms), while a 167 k-token BERT-large-shape forward (105 ms) measured 1 % SLOWER
-// with it than without. The forward therefore switches it on per call for batches of at most PDL_MAX_TOKENS
-// tokens per device (thread-local: one thread drives one device); single-kernel entry points keep it on.
-// B200EMB_PDL=0 / 1 in the environment forces it off / on (for comparisons).
-constexpr int PDL_MAX_TOKENS = 32768;
+// (86 launches, 1.44 -> 1.24 ms) and 2.7 % of a 9 k-token BERT-large-shape forward; at 19 k tokens of that
+// shape it is neutral, and from 38 k tokens on the forward measured 1-2 % SLOWER with it than without. The
+// forward therefore switches it on per call while n_tokens x hidden <= PDL_MAX_WORK (thread-local: one thread
+// drives one device); single-kernel entry points keep it on. B200EMB_PDL=0 / 1 in the environment forces it
+// off / on (for comparisons).
+constexpr long long PDL_MAX_WORK = 12ll << 20;
 bool pdl_enabled();
-void pdl_for_tokens(int n_tokens);
+void pdl_for_batch(int n_tokens, int hidden);
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem_bytes, cudaStream_t stream,

@@ -24,7 +24,7 @@ namespace b2 {
 // ---- errors -----------------------------------------------------------------------
 static thread_local char g_err[512] = "";
 
-// B200EMB_PDL: unset = by batch size (pdl_for_tokens), 0 = never, 1 = always.
+// B200EMB_PDL: unset = by batch size (pdl_for_batch), 0 = never, 1 = always.
 static int pdl_env() {
   static const int mode = [] {
     const char* v = getenv("B200EMB_PDL");
@@ -36,7 +36,7 @@ static thread_local bool g_pdl_small_batch = true;
 
 bool pdl_enabled() { return pdl_env() < 0 ? g_pdl_small_batch : pdl_env() == 1; }
 
-void pdl_for_tokens(int n_tokens) { g_pdl_small_batch = n_tokens <= PDL_MAX_TOKENS; }
+void pdl_for_batch(int n_tokens, int hidden) { g_pdl_small_batch = static_cast<long long>(n_tokens) * hidden <= PDL_MAX_WORK; }
 
 int set_error(int code, const char* fmt, ...) {
   va_list ap;
@@ -608,7 +608,7 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
   const int H = d.hidden, F = d.ffn, T = n_tokens;
   const int QKV = (d.n_heads + 2 * d.n_kv_heads) * d.head_dim;
   int rc;
-  pdl_for_tokens(T);
+  pdl_for_batch(T, H);
   if (d.arch == B200EMB_ARCH_DECODER) {
     // pre-RMSNorm decoder block (Qwen2): h is the fp32 residual stream
     {
