@@ -46,9 +46,11 @@ class _B200Backend:
             tokenizer = IdStringTokenizer(limit)
         self.tokenizer = tokenizer
         self.model = model if model is not None else B200Model(spec, weight_path, device_ids)
-        # Results travel through two bounded queues (depth 3 and 5, batch_handler.py:499-500)
-        # before the batcher hands rows out, so up to ~9 batches are alive per replica:
-        # result buffers come from a ring of ring_size reusable arrays.
+        # The device-to-host copy of a result lands in page-locked memory, which is slow to
+        # allocate, so encode_core writes into a ring of ring_size reusable pinned arrays.
+        # A slot must outlive its trip through the bounded queue between the inference and
+        # the post-processing thread (depth 5, batch_handler.py:500); encode_post copies the
+        # rows out of the ring, so what the caller receives is never overwritten.
         self._ring: List[Optional[np.ndarray]] = [None] * ring_size
         self._ring_pos = 0
         self._lock = threading.Lock()
@@ -159,11 +161,15 @@ class B200Embedder(_B200Backend):
     def encode_post(self, embedding, skip_quanitzation: bool = True):
         """float32 rows, already pooled and L2-normalised on the device (the reference does
         this step on the CPU: sentence_transformer.py:142-145). ColBERT mode: one ``[L_i, D]``
-        array per sequence (sentence_transformer.py:146-155; there are no padded rows to drop)."""
+        array per sequence (sentence_transformer.py:146-155; there are no padded rows to drop).
+        The result is a fresh array the caller owns, as the reference's ``.numpy()`` of a new
+        tensor is (sentence_transformer.py:156-157): the batcher hands row views of it to the
+        request futures (batch_handler.py:445-447), which may keep them for any time, while
+        ``encode_core`` reuses its pinned buffer a few batches later."""
         if isinstance(embedding, dict):
             rows, cu = embedding["token_embeddings"], embedding["cu_seqlens"]
             return [np.array(rows[cu[i]: cu[i + 1]], dtype=np.float32) for i in range(len(cu) - 1)]
-        return embedding
+        return np.array(embedding)
 
 
 class B200CrossEncoder(_B200Backend):
@@ -178,8 +184,9 @@ class B200CrossEncoder(_B200Backend):
         return self.tokenizer.encode_pairs(queries_docs)
 
     def encode_post(self, out_features: np.ndarray) -> np.ndarray:
-        """flat float32 raw logits (crossencoder/torch.py:110-111); the batcher applies the sigmoid"""
-        return np.ascontiguousarray(out_features, dtype=np.float32).reshape(-1)
+        """flat float32 raw logits (crossencoder/torch.py:110-111) in a fresh array the caller
+        owns (not a view of the recycled pinned buffer); the batcher applies the sigmoid"""
+        return np.array(out_features, dtype=np.float32).reshape(-1)
 
 
 class B200Classifier(_B200Backend):

@@ -36,14 +36,61 @@ def test_embedder_backend_pipeline(tmp_path):
     assert out.shape == (5, spec.hidden) and out.dtype == np.float32
     ref = enc.forward_batch(spec, W, cf.pack([np.array(s.split(), dtype=np.int64) for s in sentences]))
     assert cosines(out, ref).min() >= 0.9999
-    # the ring hands out distinct buffers for consecutive batches (results stay valid while queued)
-    again = backend.encode_core(feats)
+    # encode_post hands out memory of its own: later batches leave earlier results alone
+    again = backend.encode_post(backend.encode_core(feats))
     assert again.ctypes.data != out.ctypes.data and np.array_equal(again, out)
     eps, secs, log = backend.warmup(batch_size=8, n_tokens=64)
     assert eps > 0 and "ms inference" in log
     st = backend.model.stats
     assert st["calls"] == 3 and st["sequences"] == 5 + 5 + 8 and st["tokens"] == 2 * 273 + 8 * 64 and st["launches"] > 0
     backend.model.close()
+
+
+def test_three_thread_pipeline_keeps_every_row(tmp_path):
+    """The CUDA model behind the call pattern of the reference's ModelWorker (batch_handler.py:499-514):
+    encode_pre, encode_core and encode_post on three threads joined by queues of depth 3 and 5.
+    Thirty batches go through, every returned row is kept (as a view, the way the batcher stores
+    results[i] in a future, batch_handler.py:445-447) and compared with the oracle at the end:
+    rows that aliased a recycled result buffer would have been overwritten by then."""
+    from infinity_b200.worker import ThreeStageWorker
+    spec = cf.tiny_spec("bert")
+    path, W = _weights(tmp_path, spec, 55)
+    backend = B200Embedder(spec=spec, weight_path=path, device_ids=(0,))
+    rng = np.random.default_rng(7)
+    batches = [[_sentence(rng, int(n), spec.vocab) for n in rng.integers(1, 120, size=int(b))]
+               for b in rng.integers(1, 12, size=30)]
+    kept = {}
+
+    def deliver(index, batch, results):
+        for i in range(len(batch)):
+            kept[(index, i)] = results[i]
+
+    ThreeStageWorker(backend, deliver).run(batches)
+    assert len(kept) == sum(len(b) for b in batches)
+    worst = 1.0
+    for index, batch in enumerate(batches):
+        ref = enc.forward_batch(spec, W, cf.pack([np.array(s.split(), dtype=np.int64) for s in batch]))
+        got = np.stack([kept[(index, i)] for i in range(len(batch))])
+        worst = min(worst, float(cosines(got, ref).min()))
+    assert worst >= 0.9999, worst
+    assert backend.model.stats["calls"] == 30
+    backend.model.close()
+
+    # the reranker's flat logits are the caller's too
+    xspec = cf.tiny_spec("xlmr")
+    xpath, XW = _weights(tmp_path, xspec, 56)
+    ce = B200CrossEncoder(spec=xspec, weight_path=xpath, device_ids=(0,),
+                          tokenizer=IdStringTokenizer(xspec.max_pos - xspec.pos_offset))
+    pair_batches = [[(_sentence(rng, int(q), xspec.vocab), _sentence(rng, int(d), xspec.vocab))
+                     for q, d in zip(rng.integers(2, 20, size=int(b)), rng.integers(2, 80, size=int(b)))]
+                    for b in rng.integers(1, 8, size=14)]
+    logits = {}
+    ThreeStageWorker(ce, lambda index, batch, res: logits.__setitem__(index, res)).run(pair_batches)
+    for index, batch in enumerate(pair_batches):
+        f = ce.encode_pre(batch)
+        ref = enc.forward_batch(xspec, XW, cf.Batch(f.input_ids, f.cu_seqlens))
+        assert logits[index].shape == (len(batch),) and np.abs(logits[index] - ref[:, 0]).max() <= 1e-2
+    ce.model.close()
 
 
 def test_embedder_backend_colbert_mode(tmp_path):

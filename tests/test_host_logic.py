@@ -100,6 +100,54 @@ class FakeDeviceModel:
         return out
 
 
+def test_result_rows_are_caller_owned():
+    """encode_core reuses a ring of pinned buffers; what encode_post returns must not alias it
+    (the reference returns a fresh array per batch, sentence_transformer.py:135-157, and the
+    batcher gives row views of it to the request futures, batch_handler.py:445-447)."""
+    spec = cf.tiny_spec("bert")
+    emb = B200Embedder(spec=spec, model=FakeDeviceModel(spec.hidden), ring_size=4)
+    ce = B200CrossEncoder(spec=cf.tiny_spec("xlmr"), model=FakeDeviceModel(1), ring_size=4)
+    kept, kept_ce = [], []
+    for r in range(13):
+        sentences = [" ".join(["7"] * (r + 1 + j)) for j in range(3)]
+        kept.append(emb.encode_post(emb.encode_core(emb.encode_pre(sentences))))
+        kept_ce.append(ce.encode_post(ce.encode_core(ce.encode_pre([(s, "1") for s in sentences]))))
+    for r in range(13):
+        assert kept[r][:, 0].tolist() == [r + 1, r + 2, r + 3]
+        assert kept_ce[r].tolist() == [r + 1 + j + 1 + 4 for j in range(3)]
+    assert len({k.ctypes.data for k in kept}) == 13
+
+
+def test_three_stage_worker_keeps_row_order_and_rows():
+    """The repository's own pre / core / post threads (queue depths 3 and 5 as in
+    batch_handler.py:499-500): every row reaches its item, also when the post-processing side
+    holds on to all results until the end."""
+    from infinity_b200.worker import ThreeStageWorker
+    spec = cf.tiny_spec("bert")
+    backend = B200Embedder(spec=spec, model=FakeDeviceModel(spec.hidden), ring_size=10)
+    rng = np.random.default_rng(5)
+    batches = [[" ".join(map(str, rng.integers(1, 900, size=int(L)))) for L in rng.integers(1, 60, size=int(n))]
+               for n in rng.integers(1, 9, size=40)]
+    got = {}
+
+    def deliver(index, batch, results):
+        for i, s in enumerate(batch):
+            got[(index, i)] = results[i]          # row views, kept
+
+    ThreeStageWorker(backend, deliver).run(batches)
+    assert len(got) == sum(len(b) for b in batches)
+    for (index, i), row in got.items():
+        toks = [int(x) for x in batches[index][i].split()]
+        assert row[0] == len(toks) and row[1] == float(sum(toks))
+
+    class Boom(FakeDeviceModel):
+        def forward_arrays(self, *a, **k):
+            raise RuntimeError("device error")
+
+    with pytest.raises(ValueError):
+        ThreeStageWorker(B200Embedder(spec=spec, model=Boom(spec.hidden)), deliver).run(batches)
+
+
 def test_classifier_post_processing():
     spec = cf.tiny_spec("xlmr", n_labels=3)
     clf = B200Classifier(spec=spec, model=FakeDeviceModel(3), labels=["neg", "neu", "pos"])
@@ -179,7 +227,8 @@ def test_embed_through_the_reference_batch_handler(reference):
     spec = cf.tiny_spec("bert")
     backend = B200Embedder(spec=spec, model=FakeDeviceModel(spec.hidden))
     rng = np.random.default_rng(0)
-    sentences = [" ".join(map(str, rng.integers(1, 900, size=int(L)))) for L in rng.integers(1, 120, size=100)]
+    # 400 sentences in batches of 16: 25 batches, more than the backend's ring of result buffers
+    sentences = [" ".join(map(str, rng.integers(1, 900, size=int(L)))) for L in rng.integers(1, 120, size=400)]
 
     async def run():
         bh = BatchHandler(model_replicas=[backend], max_batch_size=16, lengths_via_tokenize=True)
