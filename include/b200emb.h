@@ -215,6 +215,13 @@ int b200emb_op_quantize_embeddings(const float* x, int32_t n_rows, int32_t dim, 
 int b200emb_partition(const int32_t* lens, int32_t n_seqs, int32_t n_shards, double cost_linear,
                       double cost_quadratic, int32_t* shard_of);
 
+/* The coefficients b200emb_forward uses for that partition on a model of this description:
+ * cost of a sequence of L tokens = *cost_linear * L + *cost_quadratic * L * L (GEMM flops per
+ * token, averaged over dense and routed layers, and attention flops per token pair weighted by
+ * the attention kernels' measured time per flop relative to the GEMMs'). A process-per-GPU driver
+ * that passes them to b200emb_partition cuts a batch exactly as a multi-device handle does. */
+int b200emb_cost_model(const b200emb_model_desc* desc, double* cost_linear, double* cost_quadratic);
+
 /* Thread-local message of the last failure on the calling thread ("" if none). */
 const char* b200emb_last_error(void);
 
@@ -226,6 +233,12 @@ int b200emb_device_count(void);
  * B200EMB_ERR_DEVICE_WAIT after about limit_ms, with the context still usable. No GPU fault,
  * trap or endless loop is involved. */
 int b200emb_selftest_bounded_wait(int32_t limit_ms);
+
+/* Host-side failure injection for tests of the allocation paths: the next `after` workspace
+ * allocations of any handle go through, then n report failure (status B200EMB_ERR_CUDA) without
+ * calling the allocator; n = 0 switches it off. Nothing on the GPU is touched. No counterpart in
+ * the reference. */
+int b200emb_test_fail_allocs(int32_t after, int32_t n);
 
 /* ---- single kernels on device buffers (used by the parity tests) -------------
  * Pointers are DEVICE pointers on the current device; `stream` is a

@@ -61,6 +61,8 @@ SIGNATURES = {
     "b200emb_forward": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_int32, _P, C.c_int64, C.POINTER(Timing)]),
     "b200emb_forward_device": (C.c_int, [_P, _P, _P, _P, _P, C.c_int32, C.c_int32, _P, C.c_int64, C.POINTER(Timing)]),
     "b200emb_partition": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_double, C.c_double, _P]),
+    "b200emb_cost_model": (C.c_int, [C.POINTER(ModelDesc), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "b200emb_test_fail_allocs": (C.c_int, [C.c_int32, C.c_int32]),
     "b200emb_last_error": (C.c_char_p, []),
     "b200emb_device_count": (C.c_int, []),
     "b200emb_selftest_bounded_wait": (C.c_int, [C.c_int32]),

@@ -210,6 +210,21 @@ struct b200emb_handle {
 
 namespace b2 {
 
+// Host-side fault injection for the allocation paths (tests only; no device fault is involved):
+// b200emb_test_fail_allocs(after, n) lets `after` workspace allocations through, then makes n report failure.
+static std::mutex g_fail_mu;
+static int g_fail_after = 0, g_fail_allocs = 0;
+static bool alloc_fault_injected() {
+  std::lock_guard<std::mutex> lk(g_fail_mu);
+  if (g_fail_allocs <= 0) return false;
+  if (g_fail_after > 0) {
+    --g_fail_after;
+    return false;
+  }
+  --g_fail_allocs;
+  return true;
+}
+
 template <typename T>
 static int dev_alloc(T** p, size_t count) {
   if (*p != nullptr) {
@@ -217,6 +232,7 @@ static int dev_alloc(T** p, size_t count) {
     *p = nullptr;
   }
   if (count == 0) count = 1;
+  if (alloc_fault_injected()) return set_error(B200EMB_ERR_CUDA, "cudaMalloc: injected failure");
   B2_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(p), count * sizeof(T)));
   return B200EMB_OK;
 }
@@ -234,7 +250,11 @@ static int host_alloc(T** p, size_t count) {
 static int ensure_capacity(b200emb_handle* h, DeviceCtx* c, int n_tokens, int n_seqs, int n_tiles) {
   const b200emb_model_desc& d = h->desc;
   int rc = 0;
+  // A capacity is set to 0 before its buffers are freed and to the new size only after every
+  // allocation of the group succeeded: after a failed allocation the next call allocates again
+  // instead of launching kernels on freed or null buffers.
   if (n_tokens > c->cap_tokens) {
+    c->cap_tokens = 0;
     const size_t T = (size_t)std::max(n_tokens, std::max(d.max_tokens, 1024));
     const size_t H = d.hidden, QKV = (size_t)(d.n_heads + 2 * d.n_kv_heads) * d.head_dim;
     if (!rc) rc = dev_alloc(&c->d_ids, T);
@@ -269,6 +289,7 @@ static int ensure_capacity(b200emb_handle* h, DeviceCtx* c, int n_tokens, int n_
     c->cap_tokens = (int)T;
   }
   if (n_seqs > c->cap_seqs) {
+    c->cap_seqs = 0;
     const size_t B = (size_t)std::max(n_seqs, 256);
     if (!rc) rc = dev_alloc(&c->d_cu, B + 1);
     if (!rc && d.pooling != B200EMB_POOL_TOKENS) rc = dev_alloc(&c->d_out, B * (size_t)h->out_dim);
@@ -280,6 +301,7 @@ static int ensure_capacity(b200emb_handle* h, DeviceCtx* c, int n_tokens, int n_
     c->cap_seqs = (int)B;
   }
   if (n_tiles > c->cap_tiles) {
+    c->cap_tiles = 0;
     const size_t NT = (size_t)std::max(n_tiles, 1024);
     if (!rc) rc = dev_alloc(&c->d_tiles, NT);
     if (!rc) rc = host_alloc(&c->h_tiles, NT);
@@ -522,34 +544,27 @@ static int gemm(DeviceCtx* c, const void* A, const void* W, const float* bias, v
   return launch_gemm_bf16(A, W, bias, C, M, N, K, epi, c->sm_count, c->d_err, c->stream, 0);
 }
 
-// Quantises the activation operand [rows, K] to MXFP8 into the context's buffers (grown on demand).
-static int quantize_activation(DeviceCtx* c, const void* A, int rows_padded, int K) {
-  const size_t qb = (size_t)rows_padded * K, sb = mxfp8_sf_atoms_bytes(rows_padded, K);
-  if (qb > c->act_q_bytes) {
-    cudaFree(c->act_q);
-    c->act_q = nullptr;
-    B2_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&c->act_q), qb));
-    c->act_q_bytes = qb;
-  }
-  if (sb > c->act_sf_bytes) {
-    cudaFree(c->act_sf);
-    c->act_sf = nullptr;
-    B2_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&c->act_sf), sb));
-    B2_CUDA_CHECK(cudaMemset(c->act_sf, 0, sb));
-    c->act_sf_bytes = sb;
-  }
-  KernelScope ks(c, B200EMB_KCLASS_OTHER);
-  return launch_quant_act_mxfp8(A, rows_padded, K, c->act_q, c->act_sf, c->stream);
-}
-
+// Grows a byte buffer; *have is 0 while the buffer is invalid, so a failed allocation is retried by the next call.
 static int grow_bytes(uint8_t** p, size_t* have, size_t want, bool zero) {
   if (want <= *have) return B200EMB_OK;
+  *have = 0;
   cudaFree(*p);
   *p = nullptr;
+  if (alloc_fault_injected()) return set_error(B200EMB_ERR_CUDA, "cudaMalloc: injected failure ");
   B2_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(p), want));
   if (zero) B2_CUDA_CHECK(cudaMemset(*p, 0, want));
   *have = want;
   return B200EMB_OK;
+}
+
+// Quantises the activation operand [rows, K] to MXFP8 into the context's buffers (grown on demand).
+static int quantize_activation(DeviceCtx* c, const void* A, int rows_padded, int K) {
+  const size_t qb = (size_t)rows_padded * K, sb = mxfp8_sf_atoms_bytes(rows_padded, K);
+  int rc = grow_bytes(&c->act_q, &c->act_q_bytes, qb, false);
+  if (!rc) rc = grow_bytes(&c->act_sf, &c->act_sf_bytes, sb, true);
+  if (rc) return rc;
+  KernelScope ks(c, B200EMB_KCLASS_OTHER);
+  return launch_quant_act_mxfp8(A, rows_padded, K, c->act_q, c->act_sf, c->stream);
 }
 
 static bool use_block_scaled(int wfmt, const Mat& W, int epi) {
@@ -926,6 +941,27 @@ static void run_shard(b200emb_handle* h, DeviceCtx* c, const int32_t* ids, const
   }
 }
 
+// Cost of a sequence of length L on one device, up to a common factor: a * L + b * L * L.
+// a = GEMM flops per token averaged over the layers (a routed layer runs top_k experts plus the
+// router); b = attention flops per token pair times ATTN_TIME_PER_FLOP, the measured ratio of the
+// attention kernels' time per flop to the GEMMs' (the GEMMs run near the tensor peak, attention does
+// not: weighting both by flops alone under-weights long sequences and leaves the shards uneven in time).
+static constexpr double ATTN_TIME_PER_FLOP = 4.0;
+static void cost_model(const b200emb_model_desc& d, double* a, double* b) {
+  const double H = d.hidden, F = d.ffn;
+  const double QKV = (double)(d.n_heads + 2 * d.n_kv_heads) * d.head_dim;
+  const bool dec = d.arch == B200EMB_ARCH_DECODER;
+  double ffn = (dec ? 6.0 : 4.0) * H * F;
+  if (d.arch == B200EMB_ARCH_MOE && d.moe_every > 0 && d.n_layers > 0) {
+    int routed = 0;
+    for (int l = 0; l < d.n_layers; ++l) routed += (l % d.moe_every) == d.moe_every - 1;
+    const double moe = d.top_k * 4.0 * H * F + 2.0 * H * d.n_experts;
+    ffn = (routed * moe + (d.n_layers - routed) * ffn) / d.n_layers;
+  }
+  *a = 2.0 * H * QKV + 2.0 * H * H + ffn;
+  *b = (dec ? 2.0 : 4.0) * H * ATTN_TIME_PER_FLOP;
+}
+
 static void partition_lpt(const int32_t* lens, int n, int n_shards, double a, double b, int32_t* shard_of) {
   std::vector<int> order(n);
   for (int i = 0; i < n; ++i) order[i] = i;
@@ -968,6 +1004,20 @@ int b200emb_partition(const int32_t* lens, int32_t n_seqs, int32_t n_shards, dou
   return B200EMB_OK;
 }
 
+int b200emb_cost_model(const b200emb_model_desc* desc, double* cost_linear, double* cost_quadratic) {
+  if (desc == nullptr || cost_linear == nullptr || cost_quadratic == nullptr)
+    return set_error(B200EMB_ERR_INVALID, "cost_model: null argument");
+  cost_model(*desc, cost_linear, cost_quadratic);
+  return B200EMB_OK;
+}
+
+int b200emb_test_fail_allocs(int32_t after, int32_t n) {
+  std::lock_guard<std::mutex> lk(g_fail_mu);
+  g_fail_after = after < 0 ? 0 : after;
+  g_fail_allocs = n < 0 ? 0 : n;
+  return B200EMB_OK;
+}
+
 int b200emb_create(const b200emb_model_desc* desc, const char* weight_path, const int32_t* device_ids,
                    int32_t n_devices, b200emb_handle** out) {
   if (desc == nullptr || weight_path == nullptr || out == nullptr || n_devices <= 0 || device_ids == nullptr)
@@ -988,13 +1038,7 @@ int b200emb_create(const b200emb_model_desc* desc, const char* weight_path, cons
   b200emb_handle* h = new b200emb_handle();
   h->desc = *desc;
   h->out_dim = desc->head == B200EMB_HEAD_CLASSIFIER ? desc->n_labels : desc->hidden;
-  {
-    const double H = desc->hidden, F = desc->ffn;
-    const double QKV = (double)(desc->n_heads + 2 * desc->n_kv_heads) * desc->head_dim;
-    const bool dec = desc->arch == B200EMB_ARCH_DECODER;
-    h->cost_a = 2.0 * H * QKV + 2.0 * H * H + (dec ? 6.0 : 4.0) * H * F;  // GEMM flops per token per layer
-    h->cost_b = (dec ? 2.0 : 4.0) * H;                                     // attention flops per token pair per layer
-  }
+  cost_model(*desc, &h->cost_a, &h->cost_b);
   for (int i = 0; i < n_devices && !rc; ++i) {
     DeviceCtx* c = new DeviceCtx();
     h->devs.push_back(c);

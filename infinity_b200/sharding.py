@@ -7,8 +7,9 @@ through a shared queue (infinity_emb/inference/batch_handler.py:111, 130-141;
 infinity_emb/inference/select_model.py:80-83).
 
 The assignment is the C library's partitioner (longest processing time first on the cost
-``a*L + b*L^2``), so one process driving several GPUs and several processes driving one
-GPU each (torchrun) cut a batch identically.
+``a*L + b*L^2``) with the coefficients the library itself derives from the model description
+(``b200emb_cost_model``), so one process driving several GPUs through one handle and several
+processes driving one GPU each (torchrun) cut a batch identically for every architecture.
 """
 from __future__ import annotations
 
@@ -16,15 +17,19 @@ from typing import List, Sequence, Tuple
 
 import numpy as np
 
+import ctypes as C
+
+from . import _lib
 from .configs import ModelSpec
-from .engine import partition
+from .engine import make_desc, partition
 
 
 def cost_coefficients(spec: ModelSpec) -> Tuple[float, float]:
-    """Per-layer flops per token (GEMMs) and per token pair (attention)."""
-    H, F = spec.hidden, spec.ffn
-    qkv = (spec.n_heads + 2 * spec.n_kv_heads) * spec.head_dim
-    return 2.0 * H * qkv + 2.0 * H * H + 4.0 * H * F, 4.0 * H
+    """The library's cost model for this architecture: (cost per token, cost per token pair)."""
+    desc = make_desc(spec)
+    a, b = C.c_double(), C.c_double()
+    _lib.check(_lib.load().b200emb_cost_model(C.byref(desc), C.byref(a), C.byref(b)))
+    return a.value, b.value
 
 
 def shard_indices(lengths: Sequence[int], n_shards: int, spec: ModelSpec) -> List[np.ndarray]:

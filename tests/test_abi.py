@@ -67,6 +67,29 @@ def test_partition_is_token_balanced_and_deterministic(lib):
     assert partition([], 4).tolist() == []
 
 
+def test_cost_model_follows_the_architecture(lib):
+    """sharding.cost_coefficients asks the library, so a process-per-GPU driver and a multi-device
+    handle cut a batch identically: 6 H F for the gated decoder FFN, top_k experts in routed layers."""
+    from infinity_b200 import configs as cf
+    from infinity_b200.sharding import cost_coefficients
+    bert = cf.tiny_spec("bert")
+    a, b = cost_coefficients(bert)
+    H, F = bert.hidden, bert.ffn
+    assert a == 2.0 * H * 3 * H + 2.0 * H * H + 4.0 * H * F and b > 0
+    dec = cf.tiny_spec("decoder")
+    a_d, b_d = cost_coefficients(dec)
+    qkv = (dec.n_heads + 2 * dec.n_kv_heads) * dec.head_dim
+    assert a_d == 2.0 * dec.hidden * qkv + 2.0 * dec.hidden ** 2 + 6.0 * dec.hidden * dec.ffn
+    assert b_d / dec.hidden == 0.5 * b / H            # causal attention: half the pairs
+    moe = cf.tiny_spec("moe")
+    a_m, _ = cost_coefficients(moe)
+    Hm, Fm = moe.hidden, moe.ffn
+    routed = sum(1 for l in range(moe.n_layers) if l % moe.moe_every == moe.moe_every - 1)
+    ffn = (routed * (moe.top_k * 4.0 * Hm * Fm + 2.0 * Hm * moe.n_experts) + (moe.n_layers - routed) * 4.0 * Hm * Fm) / moe.n_layers
+    assert abs(a_m - (2.0 * Hm * 3 * Hm + 2.0 * Hm * Hm + ffn)) < 1e-6 * a_m
+    assert lib.b200emb_cost_model(None, None, None) == -1
+
+
 def test_partition_rejects_bad_arguments(lib):
     assert lib.b200emb_partition(None, 3, 2, 1.0, 0.0, None) == -1
     assert "partition" in _lib.last_error()

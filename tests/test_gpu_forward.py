@@ -284,6 +284,32 @@ def test_multi_device_handle_equals_single_device(tmp_path):
     multi_t.close()
 
 
+def test_failed_workspace_growth_leaves_the_handle_usable(tmp_path):
+    """A workspace allocation that fails part-way (the failure is injected on the host; the
+    allocator is not called and no device fault is involved) must give a clean status, and the
+    next, smaller batch must run on freshly allocated buffers, not on freed ones."""
+    from infinity_b200 import _lib
+    from infinity_b200._lib import B200EmbError
+    spec = cf.tiny_spec("bert")
+    model, _ = build_model(tmp_path, spec, 15, perturb=True)
+    lib = _lib.load()
+    small = cf.random_batch(spec, [40, 3, 77], 5)
+    want = model.forward(small)
+    big = cf.random_batch(spec, [150] * 20, 6)      # 3000 tokens: beyond the initial 1024-token workspaces
+    try:
+        for after in (0, 3, 7):                     # fail the first, a middle and a late allocation of the group
+            lib.b200emb_test_fail_allocs(after, 1)
+            with pytest.raises(B200EmbError, match="injected"):
+                model.forward(big)
+            lib.b200emb_test_fail_allocs(0, 0)
+            assert np.array_equal(model.forward(small), want)
+    finally:
+        lib.b200emb_test_fail_allocs(0, 0)
+    got_big = model.forward(big)
+    assert np.isfinite(got_big).all() and np.array_equal(model.forward(small), want)
+    model.close()
+
+
 def test_invalid_inputs_are_rejected(tmp_path):
     from infinity_b200._lib import B200EmbError
     spec = cf.tiny_spec("bert")
