@@ -110,9 +110,25 @@ def global_batch(n_gpus: int):
     return seqs
 
 
-def cpu_reference_sample(budget_s: float, max_seqs: int):
+def reference_batches(seqs, size: int = 32):
+    """The batches the reference's queue forms from the first window of the workload: it pops
+    size x 8 items, sorts them by length and cuts every `size` (infinity_emb/inference/queue.py:57-76).
+    Returned in an order that alternates short and long batches, so that a prefix of the list
+    is a fair sample of the window."""
+    window = sorted(seqs[: size * 8], key=len)
+    batches = [window[i: i + size] for i in range(0, len(window), size)]
+    order, lo, hi = [], 0, len(batches) - 1
+    while lo <= hi:
+        order.append(lo)
+        if hi != lo:
+            order.append(hi)
+        lo, hi = lo + 1, hi - 1
+    return [batches[i] for i in order]
+
+
+def cpu_reference_sample(budget_s: float, max_batches: int):
     """Times the oracle (the reference's CPU recipe: fp32 torch, padded length-sorted batches
-    of 32, all host threads) on the first sequences of the workload until the budget is used."""
+    of 32, all host threads) on batches of the workload's first window until the budget is used."""
     import torch
     from infinity_b200 import configs as cf
     from oracle import encoder as enc
@@ -120,21 +136,85 @@ def cpu_reference_sample(budget_s: float, max_seqs: int):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     W = cf.oracle_tensors(spec, cf.init_weights(spec, cf.SEEDS[CFG][2]))
-    batch = cf.synth_batch(CFG, SEQS_PER_GPU)
-    seqs = batch.sequences()
+    seqs = cf.synth_batch(CFG, SEQS_PER_GPU).sequences()
     enc.forward_batch(spec, W, cf.pack(seqs[:2]))  # warm-up (thread pool, allocator)
-    done_tokens, done_seqs, t_used = 0, 0, 0.0
-    while done_seqs < max_seqs and t_used < budget_s:
-        chunk = seqs[done_seqs: done_seqs + 32]
+    done_tokens, done_seqs, done_batches, t_used = 0, 0, 0, 0.0
+    for chunk in reference_batches(seqs)[:max_batches]:
+        if t_used >= budget_s:
+            break
         b = cf.pack(chunk)
         t0 = time.perf_counter()
         enc.forward_batch(spec, W, b, batch_size=32)
         t_used += time.perf_counter() - t0
         done_tokens += b.n_tokens
         done_seqs += len(chunk)
+        done_batches += 1
     return {"value": done_tokens / t_used, "unit": "tokens/s", "cores": cores, "kind": "port",
-            "sample": f"first {done_seqs} of the {SEQS_PER_GPU} sequences ({done_tokens} tokens), "
-                      f"fp32 torch {torch.__version__}, padded batches of 32, {t_used:.1f} s"}, t_used, done_tokens
+            "sample": f"{done_batches} of the 8 length-sorted batches of 32 that the reference's queue cuts from the first "
+                      f"256 of the {SEQS_PER_GPU} sequences, short and long batches alternating ({done_seqs} sequences, "
+                      f"{done_tokens} tokens), fp32 torch {torch.__version__}, {t_used:.1f} s"}, t_used, done_tokens
+
+
+def gpu_torch_sample(passes: int = 2):
+    """The reference's own GPU recipe on this GPU, as a stated baseline (never on the product path):
+    transformers BertModel in bf16 with SDPA attention (loading_strategy.py:81-88 picks bf16 on CUDA,
+    sentence_transformer.py:117-133 runs the padded batch and copies the result back), random-init
+    weights of the same shape, the workload's 1024 sequences length-sorted and cut into padded
+    batches of 32 (the engine's default batch size), ids copied to the device and pooled rows
+    copied back inside the timed region."""
+    import torch
+    from transformers import BertConfig, BertModel
+    from infinity_b200 import configs as cf
+    spec = cf.SPECS[CFG]
+    cfg = BertConfig(vocab_size=spec.vocab, hidden_size=spec.hidden, num_hidden_layers=spec.n_layers,
+                     num_attention_heads=spec.n_heads, intermediate_size=spec.ffn, max_position_embeddings=spec.max_pos,
+                     type_vocab_size=max(spec.type_vocab, 1), layer_norm_eps=spec.norm_eps, hidden_act="gelu",
+                     hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    try:
+        cfg._attn_implementation = "sdpa"
+    except Exception:
+        pass
+    torch.manual_seed(0)
+    model = BertModel(cfg, add_pooling_layer=False).eval().to(device="cuda", dtype=torch.bfloat16)
+    seqs = sorted(cf.synth_batch(CFG, SEQS_PER_GPU).sequences(), key=len)
+    batches = []
+    for i in range(0, len(seqs), 32):
+        chunk = seqs[i: i + 32]
+        L = max(len(x) for x in chunk)
+        ids = torch.zeros(len(chunk), L, dtype=torch.int64)
+        mask = torch.zeros(len(chunk), L, dtype=torch.int64)
+        for r, x in enumerate(chunk):
+            ids[r, : len(x)] = torch.from_numpy(np.asarray(x, dtype=np.int64))
+            mask[r, : len(x)] = 1
+        batches.append((ids.pin_memory(), mask.pin_memory()))
+    tokens = sum(len(x) for x in seqs)
+
+    def one_pass():
+        rows = []
+        with torch.inference_mode():
+            for ids, mask in batches:
+                ids_d, mask_d = ids.cuda(non_blocking=True), mask.cuda(non_blocking=True)
+                h = model(input_ids=ids_d, attention_mask=mask_d).last_hidden_state
+                m = mask_d.unsqueeze(-1).to(h.dtype)
+                pooled = (h * m).sum(1) / m.sum(1).clamp(min=1e-9)
+                rows.append(torch.nn.functional.normalize(pooled.float(), p=2, dim=1).cpu())
+        return rows
+
+    one_pass()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(passes):
+        one_pass()
+    torch.cuda.synchronize()
+    secs = (time.perf_counter() - t0) / passes
+    padded = sum(int(ids.numel()) for ids, _ in batches)
+    del model
+    torch.cuda.empty_cache()
+    import transformers
+    return {"value": tokens / secs, "unit": "tokens/s", "ms_per_pass": secs * 1e3,
+            "what": f"transformers {transformers.__version__} BertModel, torch {torch.__version__}, bf16, SDPA attention, "
+                    f"{len(batches)} length-sorted padded batches of 32 ({padded} padded positions for {tokens} tokens), "
+                    "host ids in, host fp32 rows out; a baseline on the same GPU, not part of this library's path"}
 
 
 def run_reference(args):
@@ -144,7 +224,7 @@ def run_reference(args):
     per_step = []
     base = None
     for i in range(args.warmup + args.steps):
-        base, secs, toks = cpu_reference_sample(budget_s=8.0, max_seqs=64)
+        base, secs, toks = cpu_reference_sample(budget_s=8.0, max_batches=2)
         if i >= args.warmup:
             per_step.append((secs, toks))
     secs = sum(s for s, _ in per_step)
@@ -161,6 +241,56 @@ def run_reference(args):
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+def one_handle_run(spec, wpath, n_dev, seqs, lens, gathered, args):
+    """Rank 0 only: one B200Model over devices 0..n_dev-1. Checks that the rows of the global batch
+    equal, bit for bit, the rows the ranks computed one process per GPU, then times the global batch
+    (`handle_e2e`, weak scaling like `value`) and ONE 1024-sequence batch split over the GPUs
+    (`strong`), both through b200emb_forward with host buffers."""
+    import torch
+    from infinity_b200 import configs as cf
+    from infinity_b200.engine import B200Model
+    batch = cf.pack(seqs)
+    model = B200Model(spec, wpath, tuple(range(n_dev)), max_tokens=int(lens.sum()) // n_dev + 8192)
+    h_ids = torch.from_numpy(batch.input_ids).pin_memory().numpy()
+    h_cu = torch.from_numpy(batch.cu_seqlens).pin_memory().numpy()
+    h_out = torch.empty(batch.n_seqs, spec.out_dim, dtype=torch.float32).pin_memory().numpy()
+    model.forward_arrays(h_ids, h_cu, out=h_out)
+    want = np.empty_like(h_out)
+    for idx, rows in gathered:
+        want[idx] = rows
+    if not np.array_equal(h_out, want):
+        raise SystemExit("one handle over all GPUs and one process per GPU disagree on the result rows")
+    for _ in range(2):
+        model.forward_arrays(h_ids, h_cu, out=h_out)
+    ms = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        model.forward_arrays(h_ids, h_cu, out=h_out)
+        ms.append((time.perf_counter() - t0) * 1e3)
+    total = float(sum(ms))
+    out = {"handle_e2e": {"value": batch.n_tokens * len(ms) / (total / 1e3), "unit": "tokens/s",
+                          "ms_per_step": total / len(ms), "batch_latency_p50_ms": statistics.median(ms),
+                          "sequences_per_step": batch.n_seqs, "rows_equal_per_rank_run": True,
+                          "what": "one handle (one process, one host thread per GPU) over all GPUs, host buffers, "
+                                  "token-balanced split and host gather inside the call"}}
+    one = cf.synth_batch(CFG, SEQS_PER_GPU)
+    s_ids = torch.from_numpy(one.input_ids).pin_memory().numpy()
+    s_cu = torch.from_numpy(one.cu_seqlens).pin_memory().numpy()
+    s_out = torch.empty(one.n_seqs, spec.out_dim, dtype=torch.float32).pin_memory().numpy()
+    for _ in range(3):
+        model.forward_arrays(s_ids, s_cu, out=s_out)
+    ms1 = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        model.forward_arrays(s_ids, s_cu, out=s_out)
+        ms1.append((time.perf_counter() - t0) * 1e3)
+    out["strong"] = {"batch_latency_p50_ms": statistics.median(ms1), "tokens_per_s": one.n_tokens / (statistics.median(ms1) / 1e3),
+                     "sequences": one.n_seqs, "tokens": one.n_tokens,
+                     "what": f"one {SEQS_PER_GPU}-sequence batch split over {n_dev} GPUs through the same handle"}
+    model.close()
+    return out
 
 
 def run_ours(args):
@@ -273,13 +403,33 @@ def run_ours(args):
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)
     p50_ms = max_over_ranks(statistics.median(step_ms))
     e2e_value = total_tokens * args.steps / (e2e_ms / 1e3)
-    n_tiles = int(sum((int(L) + 63) // 64 for L in batch.lengths))
-    h2d_bytes = 4 * (batch.n_tokens + batch.n_seqs + 1) + 16 * n_tiles
-    d2h_bytes = 4 * batch.n_seqs * spec.out_dim + 4
+    n_tiles = int(sum((int(L) + 127) // 128 for L in batch.lengths))
+    # bytes copied per step by ALL ranks (ids, cu_seqlens and the query-tile list in; rows and the error word out)
+    h2d_bytes = int(sum_over_ranks(4 * (batch.n_tokens + batch.n_seqs + 1) + 16 * n_tiles))
+    d2h_bytes = int(sum_over_ranks(4 * batch.n_seqs * spec.out_dim + 4))
+
+    # One handle over all GPUs of the box (the design of the reference's replica fan-out seen from one
+    # backend object: select_model.py:80-83, batch_handler.py:111, 130-141): rank 0 alone drives devices
+    # 0..N-1 through b200emb_forward with host buffers, the other ranks wait on the host.
+    handle = None
+    if world > 1:
+        host_group = dist.new_group(backend="gloo")
+        gathered = [None] * world if rank == 0 else None
+        dist.gather_object((mine, h_out.numpy().copy()), gathered, dst=0, group=host_group)
+        if rank == 0:
+            handle = one_handle_run(spec, wpath, world, seqs, lens, gathered, args)
+        dist.barrier(group=host_group)
 
     cpu_base = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu_base, _, _ = cpu_reference_sample(budget_s=15.0, max_seqs=96)
+        cpu_base, _, _ = cpu_reference_sample(budget_s=15.0, max_batches=4)
+
+    gpu_base = None
+    if rank == 0 and world == 1 and not args.no_gpu_baseline:
+        try:
+            gpu_base = gpu_torch_sample()
+        except Exception as exc:  # a baseline that cannot run must not cost the bench line
+            gpu_base = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
 
     if rank == 0:
         achieved = gemm_flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else None
@@ -314,6 +464,11 @@ def run_ours(args):
             "clocks": clocks,
             "cpu_baseline": cpu_base,
         }
+        if handle is not None:
+            line["handle_e2e"] = handle["handle_e2e"]
+            line["strong"] = handle["strong"]
+        if gpu_base is not None:
+            line["gpu_torch_baseline"] = gpu_base
         print(json.dumps(line), flush=True)
     model.close()
     import shutil
@@ -335,6 +490,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -86,6 +86,42 @@ def load_weights(path: str | Path) -> Dict[str, torch.Tensor]:
     return out
 
 
+class WeightFileReader:
+    """Reads single tensors of a weight file on demand (the file is memory-mapped, nothing is read
+    until a tensor is asked for): for tools that walk a large file one layer at a time."""
+
+    def __init__(self, path: str | Path):
+        self.path = Path(path)
+        with open(self.path, "rb") as f:
+            head = f.read(24)
+            if head[:8] != MAGIC:
+                raise ValueError(f"{path}: not a b200emb weight file")
+            n, _, self._data_offset = struct.unpack_from("<IIQ", head, 8)
+            table = f.read(_ENTRY.size * n)
+        self.entries: Dict[str, tuple] = {}
+        for i in range(n):
+            name, dt, ndim, d0, d1, d2, d3, off, nbytes = _ENTRY.unpack_from(table, i * _ENTRY.size)
+            self.entries[name.split(b"\0", 1)[0].decode()] = (dt, [d0, d1, d2, d3][:ndim], off, nbytes)
+        self._map = np.memmap(self.path, dtype=np.uint8, mode="r")
+
+    def __contains__(self, name: str) -> bool:
+        return name in self.entries
+
+    def names(self):
+        return list(self.entries)
+
+    def read(self, name: str) -> torch.Tensor:
+        dt, shape, off, nbytes = self.entries[name]
+        raw = np.array(self._map[self._data_offset + off: self._data_offset + off + nbytes])
+        dtype = _DTYPES_INV[dt]
+        if dtype == torch.bfloat16:
+            t = torch.from_numpy(raw.view(np.int16)).view(torch.bfloat16)
+        else:
+            np_dt = {torch.float32: np.float32, torch.uint8: np.uint8, torch.int32: np.int32}[dtype]
+            t = torch.from_numpy(raw.view(np_dt))
+        return t.reshape(shape)
+
+
 def quantize_weight_file(in_path: str | Path, out_path: str | Path, weight_format: str, device_id: int = 0) -> None:
     """Block-quantises the layer matrices of a bf16 weight file on the GPU (``b200emb_quantize_weights``)."""
     from . import _lib

@@ -61,3 +61,53 @@ def build_model(tmp_path, spec, seed, perturb, device_ids=(0,)):
         wt.quantize_weight_file(path, qpath, spec.weight_format)
         return B200Model(spec, str(qpath), device_ids), quantized_oracle_tensors(spec, master, spec.weight_format)
     return B200Model(spec, str(path), device_ids), cf.oracle_tensors(spec, master)
+
+
+def _e2m1_pair_table() -> np.ndarray:
+    """byte -> the two e2m1 values it packs (low nibble = even element), as two fp16 in one uint32."""
+    e2m1 = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0], dtype=np.float16)
+    byte = np.arange(256)
+    return np.stack([e2m1[byte & 15], e2m1[byte >> 4]], axis=1).view(np.uint32).reshape(256)
+
+
+_E2M1_PAIRS = _e2m1_pair_table()
+
+
+def fast_dequantize_nvfp4(packed: torch.Tensor, scales: torch.Tensor, gs: float) -> torch.Tensor:
+    """oracle.quant.dequantize_nvfp4 for matrices of hundreds of millions of elements: one table
+    look-up per byte, then the same two fp32 operations in the same order (value * block scale, / tensor
+    scale), in place. The tests check it against the numpy statement before relying on it."""
+    rows = packed.shape[0]
+    halves = np.take(_E2M1_PAIRS, packed.numpy()).view(np.float16).reshape(rows, -1)
+    vals = torch.from_numpy(halves).float().reshape(rows, -1, 16)
+    vals.mul_(scales.view(torch.float8_e4m3fn).float()[..., None])
+    vals.div_(np.float32(gs))
+    return vals.reshape(rows, -1)
+
+
+class StreamedDecoderWeights:
+    """The oracle's weight mapping for a block-quantised decoder weight FILE, one tensor at a time:
+    ``W[name]`` reads the stored bytes of that tensor, dequantises them (NVFP4) and returns fp32, so
+    a 28-layer 7B model never sits in host memory in fp32. The file is what the runtime loads, so
+    the oracle and the kernels compute with the same stored weights."""
+
+    def __init__(self, path):
+        self.reader = wt.WeightFileReader(path)
+        self._gu = (None, None)
+
+    def _matrix(self, name: str) -> torch.Tensor:
+        r = self.reader
+        if name + ".q" in r:
+            gs = float(r.read(name + ".gs").reshape(-1)[0])
+            return fast_dequantize_nvfp4(r.read(name + ".q"), r.read(name + ".s"), gs)
+        return r.read(name).float()
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        if name.endswith("gate.w") or name.endswith("up.w"):
+            base = name[: name.rfind(".", 0, len(name) - 2) + 1]  # "layer.L."
+            if self._gu[0] != base:
+                self._gu = (base, deinterleave_gate_up(self._matrix(base + "gu.w")))
+            return self._gu[1][0 if name.endswith("gate.w") else 1]
+        if name.endswith(".w") or name == "emb.word":
+            return self._matrix(name)
+        return self.reader.read(name).float()

@@ -1,0 +1,83 @@
+"""Full-depth parity of the two large configurations against the fp32 CPU oracle.
+
+The other GPU tests check configurations 4 and 5 on two layers with the real matrix shapes; these
+run every layer of the named models (seeded random-init weights of the configuration, its real
+vocabulary) on a few sequences, with the weights the runtime loads, so that the accumulation of
+bf16 activation rounding over the full depth is measured and not extrapolated. The measured minimum
+cosine is printed; the tolerance is the one the configurations state for block formats (0.999)."""
+import os
+import time
+from dataclasses import replace
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import StreamedDecoderWeights, build_model, cosines, fast_dequantize_nvfp4
+from infinity_b200 import configs as cf
+from infinity_b200 import weights as wt
+from infinity_b200.engine import B200Model
+from oracle import decoder as dec
+from oracle import encoder as enc
+from oracle import quant as Q
+
+pytestmark = pytest.mark.gpu
+COS_TOL_BLOCK = 0.999
+
+
+def test_config4_moe_encoder_full_depth(tmp_path, capsys):
+    """12 layers, 250 048-row vocabulary, MXFP8 expert matrices, 16 sequences of the configuration's
+    length distribution (about 1 TFLOP for the CPU oracle)."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    spec = cf.MOE_ENCODER
+    assert spec.n_layers == 12 and spec.vocab == 250048 and spec.weight_format == "mxfp8"
+    model, W = build_model(tmp_path, spec, cf.SEEDS["c4"][2], perturb=False)
+    batch = cf.synth_batch("c4", 16)
+    got = model.forward(batch)
+    model.close()
+    ref = enc.forward_batch(spec, W, batch)
+    cos = cosines(got, ref)
+    with capsys.disabled():
+        print(f"\n[config 4, 12 layers, {batch.n_seqs} sequences, {batch.n_tokens} tokens] min cosine {cos.min():.6f}, "
+              f"mean {cos.mean():.6f}")
+    assert cos.min() >= COS_TOL_BLOCK, cos
+
+
+def test_fast_nvfp4_dequantiser_equals_the_numpy_statement():
+    rng = np.random.default_rng(11)
+    w = rng.normal(0, 0.02, size=(64, 256)).astype(np.float32)
+    w[3, :16] = 0.0
+    packed, scales, gs = Q.quantize_nvfp4(w)
+    want = Q.dequantize_nvfp4(packed, scales, gs)
+    got = fast_dequantize_nvfp4(torch.from_numpy(packed), torch.from_numpy(scales), float(gs)).numpy()
+    assert np.array_equal(got, want)
+
+
+def test_config5_qwen2_7b_shape_full_depth(tmp_path, capsys):
+    """All 28 layers of the Qwen2-7B shape with NVFP4 weights (7.07 G parameters, real vocabulary) on
+    four short sequences. The oracle streams the runtime's weight file one tensor at a time and runs
+    the fp32 forward on the dequantised values."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    spec = cf.QWEN2_7B
+    assert spec.n_layers == 28 and spec.weight_format == "nvfp4"
+    t0 = time.perf_counter()
+    path = tmp_path / "c5.b2ew"
+    tensors = cf.runtime_tensors(cf.init_weights(spec, cf.SEEDS["c5"][2]))
+    wt.save_weights(path, tensors)
+    del tensors
+    qpath = tmp_path / "c5.nvfp4.b2ew"
+    wt.quantize_weight_file(path, qpath, "nvfp4")
+    os.remove(path)
+    t_weights = time.perf_counter() - t0
+    batch = cf.random_batch(spec, [32, 100, 61, 48], 17)
+    model = B200Model(spec, str(qpath), (0,))
+    got = model.forward(batch)
+    model.close()
+    t1 = time.perf_counter()
+    ref = dec.forward_batch(spec, StreamedDecoderWeights(qpath), batch)
+    t_oracle = time.perf_counter() - t1
+    cos = cosines(got, ref)
+    with capsys.disabled():
+        print(f"\n[config 5, 28 layers, NVFP4, {batch.n_seqs} sequences, {batch.n_tokens} tokens] min cosine "
+              f"{cos.min():.6f}, all {np.round(cos, 6).tolist()} (weights {t_weights:.0f} s, oracle {t_oracle:.0f} s)")
+    assert cos.min() >= COS_TOL_BLOCK, cos
