@@ -13,13 +13,12 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import StreamedDecoderWeights, build_model, cosines, fast_dequantize_nvfp4
+from helpers import StreamedDecoderWeights, build_model, cosines
 from infinity_b200 import configs as cf
 from infinity_b200 import weights as wt
 from infinity_b200.engine import B200Model
 from oracle import decoder as dec
 from oracle import encoder as enc
-from oracle import quant as Q
 
 pytestmark = pytest.mark.gpu
 COS_TOL_BLOCK = 0.999
@@ -41,16 +40,6 @@ def test_config4_moe_encoder_full_depth(tmp_path, capsys):
         print(f"\n[config 4, 12 layers, {batch.n_seqs} sequences, {batch.n_tokens} tokens] min cosine {cos.min():.6f}, "
               f"mean {cos.mean():.6f}")
     assert cos.min() >= COS_TOL_BLOCK, cos
-
-
-def test_fast_nvfp4_dequantiser_equals_the_numpy_statement():
-    rng = np.random.default_rng(11)
-    w = rng.normal(0, 0.02, size=(64, 256)).astype(np.float32)
-    w[3, :16] = 0.0
-    packed, scales, gs = Q.quantize_nvfp4(w)
-    want = Q.dequantize_nvfp4(packed, scales, gs)
-    got = fast_dequantize_nvfp4(torch.from_numpy(packed), torch.from_numpy(scales), float(gs)).numpy()
-    assert np.array_equal(got, want)
 
 
 def test_config5_qwen2_7b_shape_full_depth(tmp_path, capsys):

@@ -223,3 +223,16 @@ def test_label_scores_match_the_text_classification_pipeline():
     assert np.allclose(enc.label_scores(single), tc.sigmoid(single), atol=1e-7)
     assert np.allclose(enc.label_scores(np.array([[0.0]], dtype=np.float32)), [[0.5]])
     assert np.allclose(enc.label_scores(np.array([[1000.0, 0.0]], dtype=np.float32)), [[1.0, 0.0]])
+
+
+def test_fast_nvfp4_dequantiser_equals_the_numpy_statement():
+    """The table look-up used by the full-depth GPU test to stream a 7 G-parameter NVFP4 file."""
+    from helpers import fast_dequantize_nvfp4
+    from oracle import quant as Q
+    rng = np.random.default_rng(11)
+    w = rng.normal(0, 0.02, size=(64, 256)).astype(np.float32)
+    w[3, :16] = 0.0
+    packed, scales, gs = Q.quantize_nvfp4(w)
+    want = Q.dequantize_nvfp4(packed, scales, gs)
+    got = fast_dequantize_nvfp4(torch.from_numpy(packed), torch.from_numpy(scales), float(gs)).numpy()
+    assert np.array_equal(got, want)
