@@ -6,6 +6,7 @@ CUDA device is usable, the callers raise. Nothing here falls back to torch or nu
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 from . import build as _build
@@ -84,7 +85,9 @@ _lib = None
 
 
 def lib_path() -> Path:
-    return _build.LIB_PATH
+    """The in-tree library, or the file named by B200EMB_LIBRARY (to compare two builds)."""
+    override = os.environ.get("B200EMB_LIBRARY")
+    return Path(override) if override else _build.LIB_PATH
 
 
 def load(build_if_missing: bool = True) -> C.CDLL:

@@ -48,21 +48,6 @@ static constexpr uint32_t TC_TMEM_COLS = 256;  // S 128 | P 64 | O 64
 static constexpr uint32_t TC_S_COL = 0, TC_P_COL = 128, TC_O_COL = 192;
 static constexpr float TC_LAZY_SUM = 65536.f;  // a tile's row sum of exp2(score - reference) above this moves the reference
 
-#ifdef B2_ATT_PROFILE
-// Phase timing of CTA 0 / thread 0 (development aid; not part of normal builds).
-__device__ long long g_att_prof[16];
-#define B2_PROF_DECL_T(tid) unsigned prof_acc[10] = {}; unsigned prof_t0 = (unsigned)clock(); const bool prof_on = (blockIdx.x == 0 && threadIdx.x == (tid));
-#define B2_PROF_DECL B2_PROF_DECL_T(0)
-#define B2_PROF(slot) do { if (prof_on) { const unsigned n__ = (unsigned)clock(); prof_acc[slot] += n__ - prof_t0; prof_t0 = n__; } } while (0)
-#define B2_PROF_FLUSH do { if (prof_on) { for (int i__ = 0; i__ < 10; ++i__) g_att_prof[i__] += prof_acc[i__]; } } while (0)
-#define B2_PROF_FLUSH_HI do { if (prof_on) { for (int i__ = 0; i__ < 6; ++i__) g_att_prof[10 + i__] += prof_acc[i__]; } } while (0)
-#else
-#define B2_PROF_DECL
-#define B2_PROF_DECL_T(tid)
-#define B2_PROF(slot) do { } while (0)
-#define B2_PROF_FLUSH do { } while (0)
-#define B2_PROF_FLUSH_HI do { } while (0)
-#endif
 
 __device__ __forceinline__ float max3f(float a, float b, float c) {
   float d;
@@ -213,7 +198,6 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
     int qslot = 0, kslot = 0, vslot = 0;
     uint32_t qphase = 0, kphase = 0, vphase = 0;
     bool ok = true;
-    B2_PROF_DECL_T(160)
     // every lane waits; the warp agrees on the outcome so that it never splits around elect.sync
     auto wait_all = [](uint64_t* bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbar_wait(bar, parity)); };
     auto issue_s = [&]() -> bool {  // false when a wait gave up
@@ -225,7 +209,6 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
       }
       if (!wait_all(&k_full[kslot], kphase)) return false;
       tc_fence_after_sync();
-      B2_PROF(3);  // Q / K waits
       const int nv = min(TC_BKV, s_len - s_it * TC_BKV);
       const uint32_t idesc = make_idesc_bf16_f32(128, (nv + 15) & ~15);
       const uint64_t a_desc = make_kmajor_sw128_desc(q_addr + qslot * TC_TILE_BYTES);
@@ -238,7 +221,6 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
         tc_commit(&k_empty[kslot]);
         if (s_it == s_nkv - 1) tc_commit(&q_empty[qslot]);  // last use of this Q tile
       }
-      B2_PROF(4);  // S issue
       if (++kslot == TC_KSLOTS) {
         kslot = 0;
         kphase ^= 1u;
@@ -265,7 +247,6 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
           ok = false;
           break;
         }
-        B2_PROF(0);  // wait for P
         // S of the next step first: it only needs the S columns, which bar_p has just released, and lets
         // the next softmax start while P V of this step executes. The softmax threads hold back their
         // first P store of the next step until bar_pv says that P V has read this step's P.
@@ -278,7 +259,6 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
           break;
         }
         tc_fence_after_sync();
-        B2_PROF(1);  // wait for V
         const uint64_t v_desc = make_mnmajor_sw128_desc(v_addr + vslot * TC_TILE_BYTES, 16);
         // 16 keys = two 8-row groups of the MN-major V tile = 2048 bytes (128 in descriptor units); 16 keys
         // of P = 8 columns
@@ -290,14 +270,12 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
           tc_commit(bar_pv);
           tc_commit(&v_empty[vslot]);
         }
-        B2_PROF(2);  // P V issue
         if (++vslot == TC_VSLOTS) {
           vslot = 0;
           vphase ^= 1u;
         }
       }
     }
-    B2_PROF_FLUSH_HI;
     if (!ok && lane == 0) atomicExch(err_flag, 7);
   } else {
     // ---------------- softmax warps ----------------
@@ -364,7 +342,6 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
       }
       out_pending = false;
     };
-    B2_PROF_DECL
     const float2 scale2 = make_float2(scale_log2, scale_log2);
     for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
       const AttnTile t = tiles[item / n_heads];
@@ -388,7 +365,6 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
         failed = __any_sync(0xffffffffu, failed);  // the warp leaves together
         if (failed) break;
         tc_fence_after_sync();
-        B2_PROF(2);  // wait for S
 
         if (warp_active) {
           uint32_t ra[32], rb[32];
@@ -472,7 +448,6 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
                 store_p(pb, 96);
               }
             }
-            B2_PROF(3);  // softmax pass
             float alpha = 1.f;
             const bool move_ref = !(l0 + (lsum.x + lsum.y) <= TC_LAZY_SUM);  // also true for inf / NaN
             if (__any_sync(0xffffffffu, move_ref)) {
@@ -523,12 +498,10 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
             tmem_st_wait();
           }
         }
-        B2_PROF(4);  // reference move + store wait
         if (failed) break;  // warp-uniform: set from __all_sync
         if (out_pending) {
           write_pending();  // previous item's rows; its O is overwritten only after the arrival below
           if (failed) break;
-          B2_PROF(9);  // output
         }
         tc_fence_before_sync();
         mbar_arrive(bar_p);  // this thread's P row is in tensor memory and its reads of S are done
@@ -540,8 +513,6 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
       out_dst = out + static_cast<size_t>(t.seq_start + t.q_start + warp * 32) * out_stride + h * TC_D;
     }
     if (!failed && out_pending) write_pending();
-    B2_PROF(8);  // tail
-    B2_PROF_FLUSH;
     if (failed && lane == 0) atomicExch(err_flag, 4);
   }
 
@@ -553,21 +524,6 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
   }
 }
 
-#ifdef B2_ATT_PROFILE
-extern "C" int b200emb_debug_att_prof(long long* out16, int reset) {
-  if (out16) {
-    cudaMemcpyFromSymbol(out16, g_att_prof, sizeof(long long) * 16);
-    int occ = -1;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, b2::attn_tc_d64_kernel, b2::TC_THREADS, b2::TC_SMEM_BYTES);
-    out16[15] = occ;
-  }
-  if (reset) {
-    long long z[16] = {};
-    cudaMemcpyToSymbol(g_att_prof, z, sizeof(z));
-  }
-  return 0;
-}
-#endif
 
 int attention_tc_init_device() {
   B2_CUDA_CHECK(cudaFuncSetAttribute(attn_tc_d64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));

@@ -42,17 +42,6 @@ static constexpr uint32_t T2_TMEM_COLS = 512;
 static constexpr uint32_t T2_S_COL = 0, T2_P_COL = 256, T2_O_COL = 320;
 static constexpr float T2_LAZY_SUM = 65536.f;  // a tile's row sum of exp2(score - reference) above this moves the reference
 
-#ifdef B2_ATT_PROFILE
-// Phase timing of CTA 0 (development aid; not part of normal builds).
-__device__ long long g_att2_prof[16];
-#define T2_PROF_DECL(tid) unsigned prof_acc[8] = {}; unsigned prof_t0 = (unsigned)clock(); const bool prof_on = (blockIdx.x == 0 && threadIdx.x == (tid));
-#define T2_PROF(slot) do { if (prof_on) { const unsigned n__ = (unsigned)clock(); prof_acc[slot] += n__ - prof_t0; prof_t0 = n__; } } while (0)
-#define T2_PROF_FLUSH(base) do { if (prof_on) { for (int i__ = 0; i__ < 8; ++i__) g_att2_prof[(base) + i__] += prof_acc[i__]; } } while (0)
-#else
-#define T2_PROF_DECL(tid)
-#define T2_PROF(slot) do { } while (0)
-#define T2_PROF_FLUSH(base) do { } while (0)
-#endif
 
 template <int D>
 struct T2Cfg {
@@ -294,7 +283,6 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __r
     };
     ok = issue_s() && issue_s();  // S of the first two steps
     uint32_t gi = 0;
-    T2_PROF_DECL(160)
     const uint32_t idesc_pv = make_idesc_bf16_f32_b_mn(128, D);
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       const AttnTile* tp = &tiles[item / n_heads];
@@ -307,13 +295,11 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __r
           ok = false;
           break;
         }
-        T2_PROF(0);  // wait for P
         if (!wait_all(&v_full[vslot], vphase)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        T2_PROF(1);  // wait for V
         // V tile: MN-major, head-dim blocks of 64 are T2_BOX_BYTES apart; 16 keys = two 8-row groups =
         // 2048 bytes (128 descriptor units); 16 keys of P = 8 columns
         const uint64_t v_desc = make_mnmajor_sw128_desc(v_addr + vslot * TILE, T2_BOX_BYTES);
@@ -325,7 +311,6 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __r
           tc_commit(bar_pv);
           tc_commit(&v_empty[vslot]);
         }
-        T2_PROF(2);  // P V issue
         if (++vslot == Cfg::VSLOTS) {
           vslot = 0;
           vphase ^= 1u;
@@ -335,10 +320,8 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __r
           ok = false;
           break;
         }
-        T2_PROF(3);  // S issue incl. waits for Q / K
       }
     }
-    T2_PROF_FLUSH(8);
     if (!ok && lane == 0) atomicExch(err_flag, 7);
   } else {
     // ---------------- softmax warps ----------------
@@ -409,7 +392,6 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __r
     };
     const float2 scale2 = make_float2(scale_log2, scale_log2);
     const int row_local = warp * 32 + lane;
-    T2_PROF_DECL(0)
     for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
       const AttnTile t = tiles[item / n_heads];
       const int h = item % n_heads;
@@ -442,7 +424,6 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __r
         failed = __any_sync(0xffffffffu, failed);  // the warp leaves together
         if (failed) break;
         tc_fence_after_sync();
-        T2_PROF(0);  // wait for S
 
         if (warp_active) {
           uint32_t ra[32], rb[32];
@@ -513,9 +494,7 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __r
             if (n_chunks > 2) tmem_ld_32x32b_x32(s_base + 64, ra);
             chunk(rb, pb, 32);
           }
-          T2_PROF(1);  // first two chunks
           if (gi > 0 && !__all_sync(0xffffffffu, mbar_wait(bar_pv, (gi - 1) & 1u))) failed = true;
-          T2_PROF(2);  // wait for the previous P V
           if (!failed) {
             store_p(pa, 0);
             if (n_chunks > 1) store_p(pb, 32);
@@ -577,16 +556,13 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __r
               }
             }
             l_run = l_run * alpha + (l0 + (lsum.x + lsum.y));
-            T2_PROF(3);  // last two chunks
             tmem_st_wait();
           }
         }
-        T2_PROF(4);  // store wait
         if (failed) break;  // warp-uniform: set from __all_sync
         if (out_pending) {
           write_pending();  // previous item's rows; its O is overwritten only after the arrival below
           if (failed) break;
-          T2_PROF(5);  // output
         }
         tc_fence_before_sync();
         mbar_arrive(bar_p);  // this thread's P row is in tensor memory and its reads of S are done
@@ -598,7 +574,6 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __r
       out_dst = out + static_cast<size_t>(t.seq_start + t.q_start + warp * 32) * out_stride + h * D;
     }
     if (!failed && out_pending) write_pending();
-    T2_PROF_FLUSH(0);
     if (failed && lane == 0) atomicExch(err_flag, 4);
   }
 
@@ -610,16 +585,6 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __r
   }
 }
 
-#ifdef B2_ATT_PROFILE
-extern "C" int b200emb_debug_att2_prof(long long* out16, int reset) {
-  if (out16) cudaMemcpyFromSymbol(out16, g_att2_prof, sizeof(long long) * 16);
-  if (reset) {
-    long long z[16] = {};
-    cudaMemcpyToSymbol(g_att2_prof, z, sizeof(z));
-  }
-  return 0;
-}
-#endif
 
 template <int D, bool CAUSAL>
 static int t2_init_one() {
