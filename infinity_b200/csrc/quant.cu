@@ -118,30 +118,32 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ w, size_t n_blocks, uint8_t
   scales[b] = static_cast<uint8_t>(ex + 127);
 }
 
-__device__ __forceinline__ float e2m1_value(uint32_t nib) {
-  const float mag[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
-  const float m = mag[nib & 7];
-  return (nib & 8) ? -m : m;
-}
-
-// q * float(s_q) in bf16 (exact: at most 5 significant bits); the tensor scale 1/gs is applied by the consumer
+// q * float(s_q) in bf16 (exact: at most 5 significant bits); the tensor scale 1/gs is applied by the consumer.
+// One thread expands two 16-element blocks: a 16-byte load, the hardware e2m1 pair -> half pair conversion,
+// the block scale applied in fp32, four 16-byte stores. (The first version looked the eight magnitudes up in a
+// per-thread array, which the compiler kept in local memory: 3.6 ms per Qwen2-7B layer, 3 % of the HBM rate.)
 __global__ void __launch_bounds__(256)
-dequant_nvfp4_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ scales, size_t n_blocks,
+dequant_nvfp4_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ scales, size_t n_pairs,
                      __nv_bfloat16* __restrict__ out) {
-  const size_t b = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
-  if (b >= n_blocks) return;
-  const uint2 packed = __ldg(reinterpret_cast<const uint2*>(q + b * 8));
-  const float s = __half2float(__half(__nv_cvt_fp8_to_halfraw(scales[b], __NV_E4M3)));
-  __nv_bfloat162 o[8];
+  const size_t t = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (t >= n_pairs) return;
+  const uint4 packed = __ldg(reinterpret_cast<const uint4*>(q) + t);
+  const uint16_t two_scales = __ldg(reinterpret_cast<const uint16_t*>(scales) + t);
+  const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+  uint4* dst = reinterpret_cast<uint4*>(out + t * 32);
 #pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    const uint32_t word = e < 4 ? packed.x : packed.y;
-    const uint32_t byte = (word >> (8 * (e & 3))) & 0xffu;
-    o[e] = __floats2bfloat162_rn(e2m1_value(byte & 15) * s, e2m1_value(byte >> 4) * s);
+  for (int blk = 0; blk < 2; ++blk) {
+    const float s = __half2float(__half(__nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>((two_scales >> (8 * blk)) & 0xffu), __NV_E4M3)));
+    __nv_bfloat162 o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const uint32_t byte = (words[blk * 2 + (e >> 2)] >> (8 * (e & 3))) & 0xffu;  // low nibble = even element
+      const float2 f = __half22float2(__half2(__nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>(byte), __NV_E2M1)));
+      o[e] = __floats2bfloat162_rn(f.x * s, f.y * s);
+    }
+    dst[blk * 2] = *reinterpret_cast<uint4*>(&o[0]);
+    dst[blk * 2 + 1] = *reinterpret_cast<uint4*>(&o[4]);
   }
-  uint4* dst = reinterpret_cast<uint4*>(out + b * 16);
-  dst[0] = *reinterpret_cast<uint4*>(&o[0]);
-  dst[1] = *reinterpret_cast<uint4*>(&o[4]);
 }
 
 __global__ void __launch_bounds__(256)
@@ -213,9 +215,12 @@ int launch_dequantize(const void* q, const void* scales, int64_t rows, int64_t c
   if (fmt == B200EMB_WFMT_NVFP4) {
     int rc = check_shape(rows, cols, 16);
     if (rc) return rc;
-    const size_t blocks = static_cast<size_t>(rows) * cols / 16;
-    dequant_nvfp4_kernel<<<static_cast<unsigned int>((blocks + 255) / 256), 256, 0, stream>>>(
-        reinterpret_cast<const uint8_t*>(q), reinterpret_cast<const uint8_t*>(scales), blocks,
+    // a thread expands two consecutive 16-element blocks (blocks are contiguous across rows)
+    if ((static_cast<size_t>(rows) * cols) % 32 != 0)
+      return set_error(B200EMB_ERR_INVALID, "dequantise: an NVFP4 tensor must hold a multiple of 32 elements");
+    const size_t pairs = static_cast<size_t>(rows) * cols / 32;
+    dequant_nvfp4_kernel<<<static_cast<unsigned int>((pairs + 255) / 256), 256, 0, stream>>>(
+        reinterpret_cast<const uint8_t*>(q), reinterpret_cast<const uint8_t*>(scales), pairs,
         reinterpret_cast<__nv_bfloat16*>(out));
   } else if (fmt == B200EMB_WFMT_MXFP8) {
     int rc = check_shape(rows, cols, 32);
