@@ -64,3 +64,70 @@ def token_budget_batches(lengths: Sequence[int], max_tokens: int, max_seqs: Opti
     if current:
         batches.append(current)
     return batches
+
+
+class TokenBudgetQueue:
+    """Drop-in for the reference's ``CustomFIFOQueue`` (infinity_emb/inference/queue.py:15-76: ``extend``,
+    ``pop_optimal_batches``, ``__len__``) that cuts batches by token budget.
+
+    A pop takes the first ``size * max_n_batches`` waiting items exactly as the reference does, sorts them
+    by priority when more than ``size`` were taken, drops items whose future is already done, and then cuts
+    the list where the running cost ``sum(L + quadratic_weight * L^2)`` would pass ``max_tokens`` (and at
+    ``size`` items at the latest). The priority of an item is its length: token count with
+    ``lengths_via_tokenize=True``, else characters (batch_handler.py:356-374), so give ``max_tokens`` in the
+    same unit. With ``max_tokens=None`` every pop yields the reference's batches, item for item.
+
+    Items are duck-typed like ``PrioritizedQueueItem`` (primitives.py): ``.priority`` and ``.item`` with
+    ``.item.future.done()``; this module does not import infinity_emb. To use it, assign an instance to
+    ``BatchHandler._queue_prio`` before ``spawn()`` (batch_handler.py:110 creates the queue, :327 fills it,
+    :401 pops it).
+    """
+
+    def __init__(self, max_tokens: Optional[int] = None, quadratic_weight: float = 0.0) -> None:
+        import threading
+        if max_tokens is not None and max_tokens <= 0:
+            raise ValueError("max_tokens must be positive")
+        self.max_tokens = max_tokens
+        self.quadratic_weight = float(quadratic_weight)
+        self._lock = threading.Lock()
+        self._queue: list = []
+        self._sync_event = threading.Event()
+
+    def __len__(self) -> int:
+        return len(self._queue)
+
+    def extend(self, items: list) -> None:
+        with self._lock:
+            self._queue.extend(items)
+        self._sync_event.set()
+
+    def pop_optimal_batches(self, size: int, max_n_batches: int = 4, timeout: float = 0.2, **kwargs):
+        """Generator of batches (lists of ``.item`` objects), none longer than ``size`` or, unless it is a
+        single item, dearer than ``max_tokens``. Yields nothing when the queue stays empty for ``timeout``."""
+        if not self._queue:
+            if not self._sync_event.wait(timeout):
+                return
+        take = size * max_n_batches
+        with self._lock:
+            taken, self._queue = self._queue[:take], self._queue[take:]
+            if not self._queue:
+                self._sync_event.clear()
+        if len(taken) > size:
+            taken.sort(key=lambda entry: entry.priority)  # stable, as the reference's sort on the items is
+        live = [entry for entry in taken if not entry.item.future.done()]
+        if self.max_tokens is None:
+            for i in range(0, len(live), size):
+                yield [entry.item for entry in live[i: i + size]]
+            return
+        current: list = []
+        cost = 0.0
+        for entry in live:
+            length = int(entry.priority)
+            c = length + self.quadratic_weight * length * length
+            if current and (cost + c > self.max_tokens or len(current) >= size):
+                yield current
+                current, cost = [], 0.0
+            current.append(entry.item)
+            cost += c
+        if current:
+            yield current

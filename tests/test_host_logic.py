@@ -201,6 +201,57 @@ def test_token_budget_batches():
         bt.token_budget_batches([1], 0)
 
 
+class _Future:
+    def __init__(self, done=False):
+        self._done = done
+
+    def done(self):
+        return self._done
+
+
+class _Inner:
+    def __init__(self, index, done=False):
+        self.index, self.future = index, _Future(done)
+
+
+class _Prio:
+    def __init__(self, priority, index, done=False):
+        self.priority, self.item = priority, _Inner(index, done)
+
+
+def test_token_budget_queue_matches_the_reference_orders_without_a_budget():
+    """TokenBudgetQueue with no budget pops exactly the batches the reference's CustomFIFOQueue popped
+    (orders generated by the reference itself: tests/golden/batching_golden.json)."""
+    import json
+    golden = json.loads((Path(__file__).parent / "golden" / "batching_golden.json").read_text())
+    for case in golden["cases"]:
+        q = bt.TokenBudgetQueue()
+        q.extend([_Prio(p, i) for i, p in enumerate(case["priorities"])])
+        assert len(q) == len(case["priorities"])
+        got = []
+        while len(q):
+            got.extend([[it.index for it in b] for b in q.pop_optimal_batches(case["size"], case["max_n_batches"])])
+        assert got == case["batches"]
+    assert list(bt.TokenBudgetQueue().pop_optimal_batches(4, timeout=0.01)) == []
+
+
+def test_token_budget_queue_cuts_by_tokens():
+    rng = np.random.default_rng(3)
+    lengths = rng.integers(1, 513, size=300).tolist()
+    q = bt.TokenBudgetQueue(max_tokens=4096)
+    q.extend([_Prio(L, i, done=(i % 50 == 7)) for i, L in enumerate(lengths)])
+    seen = []
+    while len(q):
+        for batch in q.pop_optimal_batches(32, max_n_batches=4):
+            idx = [it.index for it in batch]
+            assert 1 <= len(idx) <= 32 and (len(idx) == 1 or sum(lengths[i] for i in idx) <= 4096)
+            assert [lengths[i] for i in idx] == sorted(lengths[i] for i in idx)
+            seen.extend(idx)
+    assert sorted(seen) == [i for i in range(300) if i % 50 != 7]      # finished futures are dropped
+    with pytest.raises(ValueError):
+        bt.TokenBudgetQueue(max_tokens=0)
+
+
 def test_backend_warmup_contract():
     spec = cf.tiny_spec("bert")
     emb = B200Embedder(spec=spec, model=FakeDeviceModel(spec.hidden))
@@ -245,6 +296,41 @@ def test_embed_through_the_reference_batch_handler(reference):
         toks = [int(x) for x in s.split()]
         assert e.shape == (spec.hidden,) and e[0] == len(toks) and e[1] == float(sum(toks))
     assert max(backend.model.calls) <= 16
+
+
+def test_token_budget_queue_inside_the_reference_batch_handler(reference):
+    """The one-assignment swap: BatchHandler._queue_prio = TokenBudgetQueue(...). Every sentence still gets
+    its own row, and no encode_core call sees more tokens than the budget."""
+    from infinity_emb.inference.batch_handler import BatchHandler
+    spec = cf.tiny_spec("bert")
+    model = FakeDeviceModel(spec.hidden)
+    tokens_per_call = []
+    plain_forward = model.forward_arrays
+
+    def counting_forward(ids, cu, types=None, out=None, **kw):
+        tokens_per_call.append(int(cu[-1]))
+        return plain_forward(ids, cu, types, out=out, **kw)
+
+    model.forward_arrays = counting_forward
+    backend = B200Embedder(spec=spec, model=model)
+    rng = np.random.default_rng(4)
+    sentences = [" ".join(map(str, rng.integers(1, 900, size=int(L)))) for L in rng.integers(1, 120, size=300)]
+
+    async def run():
+        bh = BatchHandler(model_replicas=[backend], max_batch_size=32, lengths_via_tokenize=True)
+        bh._queue_prio = bt.TokenBudgetQueue(max_tokens=600)
+        await bh.spawn()
+        try:
+            return await bh.embed(sentences)
+        finally:
+            await bh.shutdown()
+
+    embeddings, usage = asyncio.run(run())
+    assert usage == sum(len(s.split()) for s in sentences)
+    for s, e in zip(sentences, embeddings):
+        toks = [int(x) for x in s.split()]
+        assert e[0] == len(toks) and e[1] == float(sum(toks))
+    assert max(tokens_per_call) <= 600 and max(model.calls) <= 32 and len(tokens_per_call) > 300 * 60 // 600 // 2
 
 
 def test_rerank_through_the_reference_batch_handler(reference):
