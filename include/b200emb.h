@@ -305,10 +305,14 @@ int b200emb_op_moe_router(const void* x, const float* router_w, const float* rou
  * (B200EMB_STATIC_ATTN_MAX_TILES tile records, about 256 KB, present on every GPU that loads
  * the library until the process exits) and the list is built by a kernel from d_cu_seqlens.
  * The call makes no cudaMalloc, cudaFree or other allocating call. A batch that needs more
- * query tiles (128 rows each for head_dim 64 bidirectional, else 64 rows) is rejected with
- * B200EMB_ERR_UNSUPPORTED. The first call on each device looks up the array's device address;
- * make that first call before any stream capture. All calls on a device share the array:
- * two calls whose kernels overlap on the GPU (different streams or threads) race on it. */
+ * query tiles (128 rows each for head_dim 64 and 128, 64 rows for other head dims; a sequence of
+ * L tokens takes ceil(L / rows) tiles) is rejected with B200EMB_ERR_UNSUPPORTED. Like
+ * b200emb_op_attention it waits for the stream before it returns (it reads the kernels' error
+ * word back). The first call on each device looks up the array's device address; make that
+ * first call before any stream capture. All calls on a device share the array: two calls whose
+ * kernels overlap on the GPU (different streams or threads) race on it. h_cu_seqlens and
+ * d_cu_seqlens must hold the same offsets: the tile count comes from the host copy, the tile
+ * records from the device copy. */
 #define B200EMB_STATIC_ATTN_MAX_TILES 16384
 int b200emb_op_attention_static(const void* qkv, void* out, const int32_t* d_cu_seqlens,
                                 const int32_t* h_cu_seqlens, int32_t n_seqs, int32_t n_tokens, int32_t n_heads,

@@ -44,6 +44,36 @@ def test_static_attention_matches_allocating_entry_point_twice(lib, d, nh, nkv, 
         assert torch.equal(got, want), f"call {k}: max abs diff {(got.float() - want.float()).abs().max().item()}"
 
 
+def test_static_attention_many_short_sequences_and_forced_kernel(lib):
+    """More sequences than the tile-building kernel has threads (each thread then scans several),
+    and the flag that forces the one-CTA-per-SM kernel for head_dim 64."""
+    rng = np.random.default_rng(5)
+    lens = rng.integers(1, 40, size=3000).tolist()
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    for d, nh, flags in ((64, 2, 0), (64, 2, 0x200), (64, 2, 0x201)):
+        g = torch.Generator(device="cuda").manual_seed(d + flags)
+        qkv = torch.randn(int(cu[-1]), 3 * nh * d, generator=g, device="cuda").to(torch.bfloat16)
+        want = _run(lib, lib.b200emb_op_attention, qkv, cu, nh, nh, d, flags)
+        got = _run(lib, lib.b200emb_op_attention_static, qkv, cu, nh, nh, d, flags)
+        assert torch.equal(got, want)
+
+
+def test_static_attention_allocates_no_device_memory(lib):
+    """Free device memory as the driver reports it is the same before and after a warmed call."""
+    lens = [300, 1, 128, 129, 64, 500, 17]
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    qkv = torch.randn(int(cu[-1]), 3 * 8 * 64, device="cuda").to(torch.bfloat16)
+    _run(lib, lib.b200emb_op_attention_static, qkv, cu, 8, 8, 64, 0)  # first call on the device: set-up
+    out = torch.empty(int(cu[-1]), 8 * 64, dtype=torch.bfloat16, device="cuda")
+    d_cu = torch.from_numpy(cu).cuda()
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(3):
+        _lib.check(lib.b200emb_op_attention_static(qkv.data_ptr(), out.data_ptr(), d_cu.data_ptr(), cu.ctypes.data,
+                                                   len(lens), int(cu[-1]), 8, 8, 64, 0, None))
+    assert torch.cuda.mem_get_info()[0] == free_before
+
+
 def test_static_attention_rejects_batches_beyond_its_scratch(lib):
     n = 16385  # one query tile each: one more than B200EMB_STATIC_ATTN_MAX_TILES
     cu = np.arange(n + 1, dtype=np.int32)
