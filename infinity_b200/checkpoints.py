@@ -80,7 +80,11 @@ def spec_from_hf_config(config: dict, *, name: str = "checkpoint", pooling: Opti
             n_kv_heads=nh, head_dim=H // nh, ffn=config["intermediate_size"], vocab=config["vocab_size"],
             max_pos=config["max_position_embeddings"], type_vocab=config.get("type_vocab_size", 2),
             pos_offset=pos_offset, norm_eps=config.get("layer_norm_eps", 1e-12),
-            pooling=pooling or "cls", normalize=(not classifier) if normalize is None else normalize,
+            # no sentence-transformers pooling files: SentenceTransformer builds Transformer + Pooling(mean) for a
+            # plain checkpoint directory, which is what the reference loads (sentence_transformer.py:57-78);
+            # a classification head reads the first token
+            pooling=pooling or ("cls" if classifier else "mean"),
+            normalize=(not classifier) if normalize is None else normalize,
             head="classifier" if classifier else "none", n_labels=n_labels,
             max_len=config["max_position_embeddings"] - pos_offset)
     if mt == "qwen2":

@@ -85,6 +85,17 @@ def _hf_embeddings(model, spec, batch):
     return OP.normalize(pooled) if spec.normalize else pooled
 
 
+def test_plain_checkpoint_without_pooling_files_gets_mean_pooling():
+    """A plain transformers directory (no modules.json / 1_Pooling): the reference loads it through
+    SentenceTransformer, which adds mean pooling; a classification checkpoint reads the first token."""
+    base = dict(model_type="bert", hidden_size=128, num_attention_heads=4, num_hidden_layers=2, intermediate_size=256,
+                vocab_size=1000, max_position_embeddings=96)
+    assert ck.spec_from_hf_config(dict(base, architectures=["BertModel"])).pooling == "mean"
+    clf = ck.spec_from_hf_config(dict(base, architectures=["BertForSequenceClassification"], num_labels=3))
+    assert clf.pooling == "cls" and clf.head == "classifier" and clf.n_labels == 3
+    assert ck.spec_from_hf_config(dict(base, architectures=["BertModel"]), pooling="cls").pooling == "cls"
+
+
 def test_spec_and_tensor_names_from_checkpoints(tmp_path):
     model, d = _bert(tmp_path, "mean")
     spec = ck.convert_checkpoint(d, tmp_path / "bert.b2ew")
