@@ -76,7 +76,24 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if proc.returncode != 0:
         raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
     (LIB_DIR / "source.sha256").write_text(_source_digest())
+    (LIB_DIR / "commit.txt").write_text(source_commit())
     return LIB_PATH
+
+
+def source_commit() -> str:
+    """Commit of the checkout the library was built from ("+" appended when files differ from it), or
+    "unknown" without git. Written next to the library so that measurement lines can name the build on
+    machines that only receive a copy of the tree."""
+    try:
+        root = str(PKG_DIR.parent)
+        head = subprocess.run(["git", "-C", root, "rev-parse", "--short", "HEAD"], capture_output=True, text=True, timeout=10)
+        if head.returncode != 0 or not head.stdout.strip():
+            return "unknown"
+        dirty = subprocess.run(["git", "-C", root, "status", "--porcelain", "--untracked-files=no"], capture_output=True,
+                               text=True, timeout=10).stdout.strip()
+        return head.stdout.strip() + ("+" if dirty else "")
+    except Exception:
+        return "unknown"
 
 
 if __name__ == "__main__":
