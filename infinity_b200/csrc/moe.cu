@@ -480,6 +480,10 @@ moe_scatter_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __r
   }
 }
 
+// out[t] = LayerNorm(x[t] + sum_k gate[t, k] * yperm[row_of[t, k]]). Persistent warps; the row indices and
+// gates of the next token are read, and its x row and (up to two) expert rows requested, before the current
+// token is reduced and stored, so a warp keeps two tokens of gathers in flight. (Without the look-ahead
+// every token paid the index load and the dependent gathers in sequence: 62 % of the HBM rate.)
 template <int NCH>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_combine_ln_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ yperm,
@@ -495,15 +499,53 @@ moe_combine_ln_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
   const int lane = threadIdx.x & 31;
   const int n_chunks = hidden >> 3;
   const int warps_total = gridDim.x * MOE_WARPS;
-  for (int t = blockIdx.x * MOE_WARPS + (threadIdx.x >> 5); t < n_tokens; t += warps_total) {
-    float v[NCH][8];
-    const __nv_bfloat16* xr = x + static_cast<size_t>(t) * hidden;
+  int t = blockIdx.x * MOE_WARPS + (threadIdx.x >> 5);
+  if (t >= n_tokens) return;
+  constexpr int PRE = 2;  // expert rows fetched ahead; further ones (top_k > 2) are read in the loop
+  uint4 xn[NCH], yn[PRE][NCH];
+  float gn[PRE];
+  auto load_token = [&](int tok) {
+    const __nv_bfloat16* xr = x + static_cast<size_t>(tok) * hidden;
+    const __nv_bfloat16* yr[PRE];
+#pragma unroll
+    for (int k = 0; k < PRE; ++k) {
+      yr[k] = nullptr;
+      gn[k] = 0.f;
+      if (k < top_k) {
+        gn[k] = __ldg(topk_w + static_cast<size_t>(tok) * top_k + k);
+        yr[k] = yperm + static_cast<size_t>(__ldg(row_of + static_cast<size_t>(tok) * top_k + k)) * hidden;
+      }
+    }
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
       const int c = lane + 32 * i;
-      if (c < n_chunks) unpack8m(*reinterpret_cast<const uint4*>(xr + c * 8), v[i]);
+      if (c < n_chunks) {
+        xn[i] = *reinterpret_cast<const uint4*>(xr + c * 8);
+#pragma unroll
+        for (int k = 0; k < PRE; ++k)
+          if (yr[k] != nullptr) yn[k][i] = *reinterpret_cast<const uint4*>(yr[k] + c * 8);
+      }
     }
-    for (int k = 0; k < top_k; ++k) {
+  };
+  load_token(t);
+  while (t < n_tokens) {
+    float v[NCH][8];
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const int c = lane + 32 * i;
+      if (c < n_chunks) {
+        unpack8m(xn[i], v[i]);
+#pragma unroll
+        for (int k = 0; k < PRE; ++k)
+          if (k < top_k) {  // experts are added in the order k = 0, 1, ... as before
+            float a[8];
+            unpack8m(yn[k][i], a);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[i][e] = fmaf(gn[k], a[e], v[i][e]);
+          }
+      }
+    }
+    for (int k = PRE; k < top_k; ++k) {
       const float g = topk_w[static_cast<size_t>(t) * top_k + k];
       const __nv_bfloat16* yr = yperm + static_cast<size_t>(row_of[static_cast<size_t>(t) * top_k + k]) * hidden;
 #pragma unroll
@@ -517,6 +559,8 @@ moe_combine_ln_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
         }
       }
     }
+    const int next = t + warps_total;
+    if (next < n_tokens) load_token(next);  // in flight while this token is reduced and stored
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < NCH; ++i)
@@ -547,6 +591,7 @@ moe_combine_ln_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
         *reinterpret_cast<uint4*>(dst + c * 8) = pack8m(o);
       }
     }
+    t = next;
   }
 }
 
