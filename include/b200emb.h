@@ -260,6 +260,17 @@ int b200emb_op_gemm_bf16(const void* A, const void* W, const float* bias, void* 
 int b200emb_op_gemm_mxfp8(const void* A_bf16, const void* W_q, const void* W_scales, const float* bias, void* C,
                           int32_t M, int32_t N, int32_t K, int32_t epilogue, void* stream);
 
+/* C[M,N] (bf16; [M, N/2] for the SwiGLU epilogue) = epilogue((A[M,K] (bf16) * dequant(W)^T) / tensor_scale + bias) with
+ * the NVFP4 weights expanded inside the kernel: W_q [N, K/2] packed e2m1, W_scales [N, K/16] e4m3, tensor_scale = gs,
+ * all three as b200emb_op_quantize writes them. The stored bytes are read once per tile straight from HBM; the
+ * result equals b200emb_op_dequantize followed by b200emb_op_gemm_bf16 (with 1 / gs applied to the accumulator)
+ * bit for bit. K % 64 == 0, N % 256 == 0, epilogue B200EMB_EPI_BIAS or B200EMB_EPI_BIAS_SWIGLU; otherwise
+ * B200EMB_ERR_UNSUPPORTED. The model forward uses it for batches of up to 512 tokens per device on matrices wide
+ * enough to fill the GPU with 256-column tiles, and expands the matrix once per GEMM otherwise (in the kernel a weight
+ * tile is re-expanded for every 256 rows of A: measured slower from about 1000 rows on). Synchronises the stream. */
+int b200emb_op_gemm_nvfp4(const void* A, const void* W_q, const void* W_scales, float tensor_scale, const float* bias,
+                          void* C, int32_t M, int32_t N, int32_t K, int32_t epilogue, void* stream);
+
 /* Variable-length attention over a packed qkv buffer [n_tokens, (n_heads + 2*n_kv_heads) * head_dim]
  * (all query heads, then all key heads, then all value heads), bf16.
  * out [n_tokens, n_heads * head_dim] bf16. h_cu_seqlens is the host copy used

@@ -68,6 +68,7 @@ SIGNATURES = {
     "b200emb_device_count": (C.c_int, []),
     "b200emb_selftest_bounded_wait": (C.c_int, [C.c_int32]),
     "b200emb_op_gemm_bf16": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P]),
+    "b200emb_op_gemm_nvfp4": (C.c_int, [_P, _P, _P, C.c_float, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P]),
     "b200emb_op_gemm_mxfp8": (C.c_int, [_P, _P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P]),
     "b200emb_op_attention": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P]),
     "b200emb_op_attention_static": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P]),

@@ -72,6 +72,14 @@ int gemm_init_device();
 // TMA descriptor of a bf16 row-major [rows, cols] matrix: box [box_rows x 64 columns], 128-byte swizzle.
 int make_tmap_bf16_2d(::CUtensorMap_st* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 
+// ---- GEMM against NVFP4 weights expanded inside the kernel (gemm_w4.cu) ----
+// Wq: packed e2m1 [N, K / 2], Ws: e4m3 block scales [N, K / 16], alpha = 1 / tensor scale. CTA-pair tiles of
+// 256 x 256; gemm_w4_supported says whether a shape qualifies (K % 64 == 0, N % 256 == 0, bias or SwiGLU epilogue).
+bool gemm_w4_supported(int M, int N, int K, int epi);
+int launch_gemm_w4(const void* A, const void* Wq, const void* Ws, const float* bias, void* C, int M, int N, int K, int epi,
+                   float alpha, int sm_count, int* err_flag, cudaStream_t stream);
+int gemm_w4_init_device();
+
 // ---- MXFP8 block-scaled GEMM (gemm_mxfp8.cu) ----
 // Aq / Wq: e4m3 [M, K] / [N (x n_experts), K]; sf*_atoms: e8m0 scales in 512-byte atoms (128 rows x 4 K-blocks).
 int launch_gemm_mxfp8(const void* Aq, const void* sfa_atoms, const void* Wq, const void* sfw_atoms, const float* bias,

@@ -188,6 +188,14 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// The same arrival with the default (CTA-scope release) semantics: for per-stage arrivals by threads that hold
+// global loads in flight. The cluster-scope release above makes the thread wait for every outstanding memory
+// operation first, which turns a register prefetch into a stall of a full memory latency per arrival; what the
+// consumer needs here (shared-memory writes visible to the tensor cores) is established by fence.proxy.async
+// in front of the arrival.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 // 2-D tiled load into this CTA's shared memory whose completion is signalled on an mbarrier given by
 // its shared::cluster address (the pair leader's barrier). No multicast: each CTA loads its own tile.
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* tmap, uint32_t bar_cluster_addr, int32_t x,

@@ -59,6 +59,7 @@ int kernels_init_device() {
   if (!rc) rc = attention_tc_init_device();
   if (!rc) rc = attention_tc2_init_device();
   if (!rc) rc = gemm_mxfp8_init_device();
+  if (!rc) rc = gemm_w4_init_device();
   if (!rc) rc = moe_init_device();
   if (rc) return rc;
   if (dev >= 0 && dev < 64) g_dev_inited[dev] = true;
@@ -596,6 +597,21 @@ static int gemm_grouped(DeviceCtx* c, int wfmt, const void* A, const Mat& W, con
                           W.alpha, c->tile_expert, n_experts);
 }
 
+// Up to this many rows (tokens on the device) an NVFP4 GEMM whose 256-column tiles fill the machine expands its
+// weights inside the kernel; otherwise the matrix is expanded once into the scratch and multiplied by the bf16
+// kernel. In-kernel expansion re-expands a weight tile for every 256-row tile of A that meets it, so its cost grows
+// with the rows, while the separate pass costs a fixed 2.6 bytes of traffic per weight. Measured on the Qwen2-7B
+// gate/up shape (37888 x 3584, SwiGLU): 0.125 against 0.156 ms at 32 rows, 0.130 against 0.159 ms at 256, 0.37
+// against 0.26 ms at 1024, 5.0 against 2.6 ms at 16384; the narrow matrices (14-18 column tiles) lose at every
+// row count because the kernel has no tiles narrower than 256. B200EMB_W4_FUSED_MAX_ROWS overrides the default.
+static int w4_fused_max_rows() {
+  static const int v = [] {
+    const char* e = getenv("B200EMB_W4_FUSED_MAX_ROWS");
+    return e != nullptr ? atoi(e) : 512;
+  }();
+  return v;
+}
+
 // GEMM against a model weight; a block-quantised weight is expanded into the scratch first.
 static int gemm(DeviceCtx* c, int wfmt, const void* A, const Mat& W, const float* bias, void* C, int M, int N, int K,
                 int epi) {
@@ -603,6 +619,13 @@ static int gemm(DeviceCtx* c, int wfmt, const void* A, const Mat& W, const float
   // every projection to fp8 as well costs more accuracy than the 0.999 cosine bar allows (0.9987 measured
   // on a two-layer decoder); the block-scaled fp8 x fp8 path is used for the expert GEMMs only.
   const void* w = W.w;
+  if (W.q != nullptr && wfmt == B200EMB_WFMT_NVFP4 && M <= w4_fused_max_rows() && N / 256 >= c->sm_count / 2 &&
+      gemm_w4_supported(M, N, K, epi)) {
+    // NVFP4 weights, few rows: expanded tile by tile inside the GEMM, straight from the stored bytes
+    KernelScope ks(c, B200EMB_KCLASS_GEMM);
+    c->gemm_flops += 2.0 * M * N * K;
+    return launch_gemm_w4(A, W.q, W.s, bias, C, M, N, K, epi, W.alpha, c->sm_count, c->d_err, c->stream);
+  }
   if (W.q != nullptr) {
     KernelScope ks(c, B200EMB_KCLASS_OTHER);
     int rc = launch_dequantize(W.q, W.s, W.rows, W.cols, wfmt, c->wscratch, c->stream);
@@ -1450,6 +1473,33 @@ int b200emb_op_gemm_bf16(const void* A, const void* W, const float* bias, void* 
   if (herr != 0) {
     cudaMemset(d_err, 0, sizeof(int));
     return set_error(B200EMB_ERR_DEVICE_WAIT, "gemm: a device-side wait gave up (role %d)", herr);
+  }
+  return B200EMB_OK;
+}
+
+int b200emb_op_gemm_nvfp4(const void* A, const void* W_q, const void* W_scales, float tensor_scale, const float* bias,
+                          void* C, int32_t M, int32_t N, int32_t K, int32_t epilogue, void* stream) {
+  if (A == nullptr || W_q == nullptr || W_scales == nullptr || C == nullptr)
+    return set_error(B200EMB_ERR_INVALID, "gemm_nvfp4: null pointer");
+  if (!(tensor_scale > 0.f)) return set_error(B200EMB_ERR_INVALID, "gemm_nvfp4: the tensor scale must be positive");
+  int rc = kernels_init_device();
+  if (rc) return rc;
+  int sms = 0;
+  rc = current_sm_count(&sms);
+  if (rc) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int* d_err = nullptr;
+  rc = op_error_word(&d_err);
+  if (rc) return rc;
+  rc = launch_gemm_w4(A, W_q, W_scales, bias, C, M, N, K, epilogue, 1.0f / tensor_scale, sms, d_err, s);
+  int herr = 0;
+  cudaError_t e = cudaMemcpyAsync(&herr, d_err, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (rc) return rc;
+  if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "gemm_nvfp4: %s", cudaGetErrorString(e));
+  if (herr != 0) {
+    cudaMemset(d_err, 0, sizeof(int));
+    return set_error(B200EMB_ERR_DEVICE_WAIT, "gemm_nvfp4: a device-side wait gave up (role %d)", herr);
   }
   return B200EMB_OK;
 }

@@ -3,6 +3,10 @@
     python -m infinity_b200.kernel_case gemm --m 32768 --n 3072 --k 1024 --epi bias --launches 3
     python -m infinity_b200.kernel_case attention --seqs 256 --len 384 --heads 16 --head-dim 64 --launches 3
     python -m infinity_b200.kernel_case add_ln --rows 65536 --hidden 1024 --launches 3
+    python -m infinity_b200.kernel_case nvfp4 --m 1024 --n 37888 --k 3584 --epi swiglu --launches 5
+
+The nvfp4 case also times its two ways of multiplying by NVFP4 weights (CUDA events, best of the launches):
+expansion inside the GEMM (b200emb_op_gemm_nvfp4) against the expansion kernel followed by the bf16 GEMM.
 
 Every case checks its result against a torch computation before exiting 0.
 """
@@ -19,7 +23,7 @@ from . import _lib
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attention", "add_ln"])
+    ap.add_argument("kernel", choices=["gemm", "attention", "add_ln", "nvfp4"])
     ap.add_argument("--m", type=int, default=32768)
     ap.add_argument("--n", type=int, default=3072)
     ap.add_argument("--k", type=int, default=1024)
@@ -56,6 +60,49 @@ def main() -> None:
         err = (Cm[rows].float() - ref).abs().max().item()
         assert err < 0.05, err
         print(f"gemm {a.m}x{a.n}x{a.k} ok, max abs err {err:.4f}")
+    elif a.kernel == "nvfp4":
+        NVFP4 = _lib.WFMT["nvfp4"]
+        w = (torch.randn(a.n, a.k, device="cuda") * 0.02).to(torch.bfloat16)
+        q = torch.zeros(a.n, a.k // 2, dtype=torch.uint8, device="cuda")
+        sc = torch.zeros(a.n, a.k // 16, dtype=torch.uint8, device="cuda")
+        gs = torch.zeros(1, dtype=torch.float32, device="cuda")
+        _lib.check(lib.b200emb_op_quantize(w.data_ptr(), a.n, a.k, NVFP4, q.data_ptr(), sc.data_ptr(), gs.data_ptr(), stream))
+        del w
+        A = torch.randn(a.m, a.k, device="cuda").to(torch.bfloat16)
+        n_out = a.n // 2 if a.epi == "swiglu" else a.n
+        c1 = torch.empty(a.m, n_out, dtype=torch.bfloat16, device="cuda")
+        c2 = torch.empty(a.m, n_out, dtype=torch.bfloat16, device="cuda")
+        wexp = torch.empty(a.n, a.k, dtype=torch.bfloat16, device="cuda")
+        torch.cuda.synchronize()
+
+        def timed(fn):
+            best = float("inf")
+            for _ in range(a.launches):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                best = min(best, e0.elapsed_time(e1))
+            return best
+
+        def fused():
+            _lib.check(lib.b200emb_op_gemm_nvfp4(A.data_ptr(), q.data_ptr(), sc.data_ptr(), float(gs.item()), None,
+                                                 c1.data_ptr(), a.m, a.n, a.k, _lib.EPI[a.epi], stream))
+
+        def expanded():
+            _lib.check(lib.b200emb_op_dequantize(q.data_ptr(), sc.data_ptr(), a.n, a.k, NVFP4, wexp.data_ptr(), stream))
+            _lib.check(lib.b200emb_op_gemm_bf16(A.data_ptr(), wexp.data_ptr(), None, c2.data_ptr(), a.m, a.n, a.k,
+                                                _lib.EPI[a.epi], stream))
+
+        t_fused, t_exp = timed(fused), timed(expanded)
+        assert torch.isfinite(c1.float()).all()
+        if a.epi == "bias":  # same B tiles; the tensor scale is applied to the accumulator in one and left out in the other
+            ratio = (c1.float().abs().mean() / c2.float().abs().mean()).item()
+            assert abs(ratio * float(gs.item()) - 1.0) < 2e-2, (ratio, float(gs.item()))
+        flops = 2.0 * a.m * a.n * a.k
+        print(f"nvfp4 gemm {a.m}x{a.n}x{a.k} {a.epi}: expansion in the kernel {t_fused:.3f} ms ({flops / t_fused / 1e9:.0f} TFLOP/s), "
+              f"expansion kernel + bf16 gemm {t_exp:.3f} ms ({flops / t_exp / 1e9:.0f} TFLOP/s)")
     elif a.kernel == "attention":
         nkv = a.kv_heads or a.heads
         cu = (np.arange(a.seqs + 1) * a.len).astype(np.int32)

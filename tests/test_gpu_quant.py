@@ -124,3 +124,80 @@ def test_gemm_mxfp8_block_scaled(lib, M, N, K, epi):
     err = (c.float() - ref).abs().max().item()
     tol = 2.0 ** -8 * max(1.0, ref.abs().max().item()) + 2e-3
     assert err <= tol, (err, tol)
+
+
+def _nvfp4_weights(N, K, seed, amax=None):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    w = (torch.randn(N, K, generator=g, device="cuda") * 0.02).clamp_(-0.04, 0.04)
+    if amax is not None:
+        w[0, 0] = amax
+    w = w.to(torch.bfloat16)
+    q = torch.zeros(N, K // 2, dtype=torch.uint8, device="cuda")
+    s = torch.zeros(N, K // 16, dtype=torch.uint8, device="cuda")
+    gs = torch.zeros(1, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    _lib.check(_lib.load().b200emb_op_quantize(w.data_ptr(), N, K, NVFP4, q.data_ptr(), s.data_ptr(), gs.data_ptr(), None))
+    return q, s, float(gs.item())
+
+
+@pytest.mark.parametrize("M,N,K", [(20000, 512, 256), (19000, 1024, 1024), (40001, 256, 3584), (1, 256, 64), (300, 768, 192)])
+def test_nvfp4_gemm_expands_weights_in_the_kernel(lib, M, N, K):
+    """b200emb_op_gemm_nvfp4 reads the stored e2m1 bytes and e4m3 scales itself: against the fp32 product with the
+    numpy-dequantised weights, and bit for bit against the expansion kernel followed by the bf16 GEMM (the tensor
+    scale is a power of two here, so that its factor commutes with the rounding to bf16)."""
+    amax = 2688.0 / 65536.0  # exactly representable in bf16: gs = 2688 / amax = 65536
+    q, s, gs = _nvfp4_weights(N, K, 11 + N, amax)
+    assert gs == 65536.0
+    g = torch.Generator(device="cuda").manual_seed(M)
+    a = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    bias = torch.randn(N, generator=g, device="cuda") * 0.5
+    c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()
+    _lib.check(lib.b200emb_op_gemm_nvfp4(a.data_ptr(), q.data_ptr(), s.data_ptr(), gs, bias.data_ptr(), c.data_ptr(), M, N, K,
+                                         _lib.EPI["bias"], None))
+    w_dq = torch.from_numpy(Q.dequantize_nvfp4(q.cpu().numpy(), s.cpu().numpy(), np.float32(gs))).cuda()
+    rows = slice(0, 2048)
+    ref = a[rows].float() @ w_dq.t() + bias
+    err = (c[rows].float() - ref).abs().max().item()
+    assert err <= 2.0 ** -8 * max(1.0, ref.abs().max().item()) + 1e-3, err
+    assert not torch.isnan(c.float()).any()
+    # the unfused path: expansion kernel, then the bf16 GEMM on q * block scale with the bias scaled by gs
+    w_exp = torch.empty(N, K, dtype=torch.bfloat16, device="cuda")
+    _lib.check(lib.b200emb_op_dequantize(q.data_ptr(), s.data_ptr(), N, K, NVFP4, w_exp.data_ptr(), None))
+    c2 = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    bias_scaled = (bias * gs).contiguous()
+    torch.cuda.synchronize()
+    _lib.check(lib.b200emb_op_gemm_bf16(a.data_ptr(), w_exp.data_ptr(), bias_scaled.data_ptr(), c2.data_ptr(), M, N, K,
+                                        _lib.EPI["bias"] | (257 << 8), None))
+    assert torch.equal((c2.float() / gs).to(torch.bfloat16), c)
+
+
+def test_nvfp4_gemm_swiglu_and_limits(lib):
+    from infinity_b200.configs import interleave_gate_up
+    M, F, K = 20000, 512, 512
+    g = torch.Generator(device="cuda").manual_seed(3)
+    wg = (torch.randn(F, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    wu = (torch.randn(F, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    w = interleave_gate_up(wg, wu).contiguous()
+    q = torch.zeros(2 * F, K // 2, dtype=torch.uint8, device="cuda")
+    s = torch.zeros(2 * F, K // 16, dtype=torch.uint8, device="cuda")
+    gs = torch.zeros(1, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    _lib.check(lib.b200emb_op_quantize(w.data_ptr(), 2 * F, K, NVFP4, q.data_ptr(), s.data_ptr(), gs.data_ptr(), None))
+    a = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    c = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()
+    _lib.check(lib.b200emb_op_gemm_nvfp4(a.data_ptr(), q.data_ptr(), s.data_ptr(), float(gs.item()), None, c.data_ptr(), M, 2 * F, K,
+                                         _lib.EPI["swiglu"], None))
+    w_dq = torch.from_numpy(Q.dequantize_nvfp4(q.cpu().numpy(), s.cpu().numpy(), np.float32(gs.item()))).cuda()
+    from helpers import deinterleave_gate_up
+    gd, ud = deinterleave_gate_up(w_dq)
+    rows = slice(0, 1024)
+    ref = torch.nn.functional.silu(a[rows].float() @ gd.t()) * (a[rows].float() @ ud.t())
+    err = (c[rows].float() - ref).abs().max().item()
+    assert err <= 2.0 ** -8 * max(1.0, ref.abs().max().item()) + 2e-3, err
+    # an unsupported epilogue or shape: a clean status, nothing launched
+    st = lib.b200emb_op_gemm_nvfp4(a.data_ptr(), q.data_ptr(), s.data_ptr(), 1.0, None, c.data_ptr(), M, 2 * F, K, _lib.EPI["gelu"], None)
+    assert st == -2 and "gemm_w4" in _lib.last_error()
+    st = lib.b200emb_op_gemm_nvfp4(a.data_ptr(), q.data_ptr(), s.data_ptr(), 1.0, None, c.data_ptr(), M, 2 * F - 128, K, _lib.EPI["bias"], None)
+    assert st == -2
