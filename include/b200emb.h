@@ -173,7 +173,10 @@ int b200emb_forward(b200emb_handle* h, const int32_t* input_ids, const int32_t* 
 
 /* Same computation with every buffer already resident on device 0 of the
  * handle (device pointers; out is device fp32). Used to measure the kernels
- * without host<->device copies. Single-device handles only. */
+ * without host<->device copies. Single-device handles only. Lengths are validated on the
+ * host from h_cu_seqlens; ids and token types, which only the device holds, are range-checked
+ * by the embedding kernel: an id outside its table is read as 0 (no out-of-bounds access) and
+ * the call returns B200EMB_ERR_INVALID when the forward has finished. */
 int b200emb_forward_device(b200emb_handle* h, const int32_t* d_input_ids, const int32_t* d_token_type_ids,
                            const int32_t* d_cu_seqlens, const int32_t* h_cu_seqlens, int32_t n_seqs,
                            int32_t n_tokens, float* d_out, int64_t out_row_stride, b200emb_timing* timing);

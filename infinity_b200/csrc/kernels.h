@@ -142,9 +142,11 @@ int launch_moe_combine_ln(const void* x, const void* yperm, const int32_t* row_o
 
 // ---- row kernels (rowops.cu) ----
 int launch_wait_selftest(unsigned long long limit_ns, int* err_flag, cudaStream_t stream);
+// vocab / type_vocab > 0: ids and types outside the tables are reported through err_flag (codes 32 / 33) and read as 0
 int launch_embed_ln(const int32_t* ids, const int32_t* types, const int32_t* d_cu, int n_seqs, int n_tokens,
                     const void* word, const void* pos, const void* type_table, const float* gamma, const float* beta,
-                    int hidden, int pos_offset, float eps, void* out, cudaStream_t stream);
+                    int hidden, int pos_offset, float eps, void* out, cudaStream_t stream, int vocab = 0,
+                    int type_vocab = 0, int* err_flag = nullptr);
 int launch_add_ln(const void* x, const void* y, const float* gamma, const float* beta, int n_rows, int hidden,
                   float eps, void* out, cudaStream_t stream);
 // h (fp32) += y (bf16, nullable); out = RMSNorm(h) * gamma (bf16)

@@ -104,16 +104,29 @@ __device__ __forceinline__ void layernorm_store(float (&v)[NCH][8], int lane, in
   }
 }
 
+// Index that is safe to use whatever the caller put on the device: an id outside [0, limit) is reported in the
+// error word (first writer wins; the host turns the code into an invalid-argument status when the forward ends)
+// and replaced by 0, so that no kernel reads outside its table. limit <= 0 switches the check off.
+static constexpr int ERR_BAD_TOKEN_ID = 32, ERR_BAD_TOKEN_TYPE = 33;
+__device__ __forceinline__ int checked_index(int v, int limit, int* err_flag, int code) {
+  if (limit > 0 && (v < 0 || v >= limit)) {
+    if (err_flag != nullptr) atomicCAS(err_flag, 0, code);
+    return 0;
+  }
+  return v;
+}
+
 // Plain row gather out[t,:] = table[ids[t],:] (decoder embedding lookup): persistent warps, four
 // 16-byte loads in flight per lane, nothing kept in registers.
 __global__ void __launch_bounds__(ROW_WARPS * 32)
 gather_rows_kernel(const int32_t* __restrict__ ids, int n_tokens, const __nv_bfloat16* __restrict__ table, int hidden,
-                   __nv_bfloat16* __restrict__ out) {
+                   __nv_bfloat16* __restrict__ out, int vocab, int* __restrict__ err_flag) {
   const int lane = threadIdx.x & 31;
   const int n_chunks = hidden >> 3;
   const int warps_total = gridDim.x * ROW_WARPS;
   for (int t = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5); t < n_tokens; t += warps_total) {
-    const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<size_t>(__ldg(ids + t)) * hidden);
+    const int id = checked_index(__ldg(ids + t), vocab, err_flag, ERR_BAD_TOKEN_ID);
+    const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<size_t>(id) * hidden);
     uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * hidden);
     for (int c = lane; c < n_chunks; c += 128) {
       uint4 u[4];
@@ -133,7 +146,7 @@ embed_ln_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ typ
                 int n_seqs, int n_tokens, const __nv_bfloat16* __restrict__ word,
                 const __nv_bfloat16* __restrict__ pos, const __nv_bfloat16* __restrict__ type_table,
                 const float* __restrict__ gamma, const float* __restrict__ beta, int hidden, int pos_offset,
-                float eps, __nv_bfloat16* __restrict__ out) {
+                float eps, __nv_bfloat16* __restrict__ out, int vocab, int type_vocab, int* __restrict__ err_flag) {
   const int t = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
   if (t >= n_tokens) return;
   const int lane = threadIdx.x & 31;
@@ -148,11 +161,14 @@ embed_ln_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ typ
     }
     p = pos_offset + t - __ldg(cu + lo);
   }
-  const int id = __ldg(ids + t);
+  const int id = checked_index(__ldg(ids + t), vocab, err_flag, ERR_BAD_TOKEN_ID);
   const __nv_bfloat16* wrow = word + static_cast<size_t>(id) * hidden;
   const __nv_bfloat16* prow = pos != nullptr ? pos + static_cast<size_t>(p) * hidden : nullptr;
   const __nv_bfloat16* trow = nullptr;
-  if (type_table != nullptr) trow = type_table + static_cast<size_t>(types != nullptr ? __ldg(types + t) : 0) * hidden;
+  if (type_table != nullptr) {
+    const int ty = types != nullptr ? checked_index(__ldg(types + t), type_vocab, err_flag, ERR_BAD_TOKEN_TYPE) : 0;
+    trow = type_table + static_cast<size_t>(ty) * hidden;
+  }
 
   float v[NCH][8];
 #pragma unroll
@@ -577,7 +593,8 @@ static int check_hidden(int hidden, int max_chunks_per_lane) {
 
 int launch_embed_ln(const int32_t* ids, const int32_t* types, const int32_t* d_cu, int n_seqs, int n_tokens,
                     const void* word, const void* pos, const void* type_table, const float* gamma, const float* beta,
-                    int hidden, int pos_offset, float eps, void* out, cudaStream_t stream) {
+                    int hidden, int pos_offset, float eps, void* out, cudaStream_t stream, int vocab, int type_vocab,
+                    int* err_flag) {
   if (n_tokens <= 0) return B200EMB_OK;
   int rc = check_hidden(hidden, 16);
   if (rc) return rc;
@@ -587,7 +604,7 @@ int launch_embed_ln(const int32_t* ids, const int32_t* types, const int32_t* d_c
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int full = (n_tokens + ROW_WARPS - 1) / ROW_WARPS;
     gather_rows_kernel<<<full < sms * 8 ? full : sms * 8, ROW_WARPS * 32, 0, stream>>>(
-        ids, n_tokens, reinterpret_cast<const __nv_bfloat16*>(word), hidden, reinterpret_cast<__nv_bfloat16*>(out));
+        ids, n_tokens, reinterpret_cast<const __nv_bfloat16*>(word), hidden, reinterpret_cast<__nv_bfloat16*>(out), vocab, err_flag);
     cudaError_t eg = cudaGetLastError();
     if (eg != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "gather launch: %s", cudaGetErrorString(eg));
     return B200EMB_OK;
@@ -598,7 +615,7 @@ int launch_embed_ln(const int32_t* ids, const int32_t* types, const int32_t* d_c
                            ids, types, d_cu, n_seqs, n_tokens, reinterpret_cast<const __nv_bfloat16*>(word),
                            reinterpret_cast<const __nv_bfloat16*>(pos),
                            reinterpret_cast<const __nv_bfloat16*>(type_table), gamma, beta, hidden, pos_offset, eps,
-                           reinterpret_cast<__nv_bfloat16*>(out))));
+                           reinterpret_cast<__nv_bfloat16*>(out), vocab, type_vocab, err_flag)));
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "embed_ln launch: %s", cudaGetErrorString(e));
   return B200EMB_OK;

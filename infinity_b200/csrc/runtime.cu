@@ -652,7 +652,7 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
     {
       KernelScope ks(c, B200EMB_KCLASS_EMBED);
       rc = launch_embed_ln(d_ids, nullptr, d_cu, n_seqs, T, w.word, nullptr, nullptr, nullptr, nullptr, H, 0, d.norm_eps,
-                           c->y, c->stream);
+                           c->y, c->stream, d.vocab, 0, c->d_err);
       if (rc) return rc;
     }
     {
@@ -707,7 +707,8 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
   {
     KernelScope ks(c, B200EMB_KCLASS_EMBED);
     rc = launch_embed_ln(d_ids, w.type != nullptr ? d_types : nullptr, d_cu, n_seqs, T, w.word, w.pos, w.type,
-                         w.emb_ln_g, w.emb_ln_b, H, d.pos_offset, d.norm_eps, c->x, c->stream);
+                         w.emb_ln_g, w.emb_ln_b, H, d.pos_offset, d.norm_eps, c->x, c->stream, d.vocab, d.type_vocab,
+                         c->d_err);
     if (rc) return rc;
   }
   for (int l = 0; l < d.n_layers; ++l) {
@@ -1408,6 +1409,9 @@ int b200emb_forward_device(b200emb_handle* h, const int32_t* d_input_ids, const 
     const int code = *c->h_err;
     cudaMemsetAsync(c->d_err, 0, sizeof(int), s);
     cudaStreamSynchronize(s);
+    if (code == 32 || code == 33)
+      return set_error(B200EMB_ERR_INVALID, "forward_device: %s outside its table (found by the embedding kernel, which read row 0 instead)",
+                       code == 32 ? "an input id" : "a token type id");
     return set_error(B200EMB_ERR_DEVICE_WAIT, "a device-side wait gave up (role %d)", code);
   }
   if (timing != nullptr) {

@@ -284,6 +284,44 @@ def test_multi_device_handle_equals_single_device(tmp_path):
     multi_t.close()
 
 
+def test_forward_device_range_checks_ids_on_the_device(tmp_path):
+    """b200emb_forward_device never sees the ids on the host: the embedding kernel checks them against the table,
+    reads row 0 for a bad one (no out-of-bounds access) and the call reports an invalid argument at its end;
+    the handle stays usable."""
+    from infinity_b200._lib import B200EmbError
+    spec = cf.tiny_spec("bert")
+    model, _ = build_model(tmp_path, spec, 16, perturb=True)
+    batch = cf.random_batch(spec, [40, 3, 77], 5, with_types=True)
+    want = model.forward(batch)
+    d_cu = torch.from_numpy(batch.cu_seqlens).cuda()
+    d_types = torch.from_numpy(batch.token_type_ids).cuda()
+    d_out = torch.empty(batch.n_seqs, spec.out_dim, dtype=torch.float32, device="cuda")
+
+    def run(ids, types):
+        d_ids = torch.from_numpy(ids).cuda()
+        d_ty = torch.from_numpy(types).cuda()
+        torch.cuda.synchronize()
+        model.forward_device(d_ids.data_ptr(), d_ty.data_ptr(), d_cu.data_ptr(), batch.cu_seqlens, batch.n_tokens, d_out.data_ptr())
+        torch.cuda.synchronize()
+        return d_out.cpu().numpy()
+
+    assert np.array_equal(run(batch.input_ids, batch.token_type_ids), want)
+    bad = batch.input_ids.copy()
+    bad[17] = spec.vocab + 5
+    with pytest.raises(B200EmbError, match="input id"):
+        run(bad, batch.token_type_ids)
+    bad = batch.input_ids.copy()
+    bad[2] = -1
+    with pytest.raises(B200EmbError, match="input id"):
+        run(bad, batch.token_type_ids)
+    bad_t = batch.token_type_ids.copy()
+    bad_t[5] = spec.type_vocab
+    with pytest.raises(B200EmbError, match="token type"):
+        run(batch.input_ids, bad_t)
+    assert np.array_equal(run(batch.input_ids, batch.token_type_ids), want)
+    model.close()
+
+
 def test_failed_workspace_growth_leaves_the_handle_usable(tmp_path):
     """A workspace allocation that fails part-way (the failure is injected on the host; the
     allocator is not called and no device fault is involved) must give a clean status, and the
