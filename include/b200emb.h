@@ -225,6 +225,21 @@ int b200emb_partition(const int32_t* lens, int32_t n_seqs, int32_t n_shards, dou
  * that passes them to b200emb_partition cuts a batch exactly as a multi-device handle does. */
 int b200emb_cost_model(const b200emb_model_desc* desc, double* cost_linear, double* cost_quadratic);
 
+/* 1 when the library is the checked build (compiled with -DB200EMB_BOUNDS=1,
+ * `python -m infinity_b200.build --checked` -> libb200emb_checked.so), else 0. In the checked build
+ * every index a kernel reads from device memory (expert choices, rows of the expert-contiguous
+ * layout, sequence boundaries and positions derived from the device copy of cu_seqlens, the expert
+ * of a GEMM row block) is range-checked by the kernel that uses it: a value outside its range is
+ * recorded, replaced by index 0 so that the access stays inside its buffer, and the forward returns
+ * B200EMB_ERR_INVALID ("device index check: ..."). Nothing traps. It stands in for a memory checker
+ * on machines where none may be run; the normal build contains none of it. No counterpart in the reference. */
+int b200emb_checked_build(void);
+
+/* TMA descriptors (tensor maps) of weights and workspace slices are encoded once per (address, shape)
+ * and kept for the life of the process; these are the counts of descriptor requests served from that
+ * table and of those that called the driver's encoder. No counterpart in the reference. */
+int b200emb_tensor_map_stats(uint64_t* hits, uint64_t* misses);
+
 /* Thread-local message of the last failure on the calling thread ("" if none). */
 const char* b200emb_last_error(void);
 
@@ -277,8 +292,8 @@ int b200emb_op_gemm_nvfp4(const void* A, const void* W_q, const void* W_scales, 
 /* Variable-length attention over a packed qkv buffer [n_tokens, (n_heads + 2*n_kv_heads) * head_dim]
  * (all query heads, then all key heads, then all value heads), bf16.
  * out [n_tokens, n_heads * head_dim] bf16. h_cu_seqlens is the host copy used
- * to build the tile list. causal: 0 = bidirectional, 1 = causal. head_dim 64 and 128 run on the
- * tensor-memory (tcgen05) kernels, other head dims on the mma.sync kernel; adding 0x100 forces the
+ * to build the tile list. causal: 0 = bidirectional, 1 = causal. head_dim 64 and 128, and
+ * bidirectional head_dim 32, run on the tensor-memory (tcgen05) kernels, the rest on the mma.sync kernel; adding 0x100 forces the
  * mma.sync kernel, adding 0x200 forces the one-CTA-per-SM tensor-memory kernel (which otherwise serves
  * head_dim 128 and causal batches) for head_dim 64 bidirectional too.
  * Synchronises the stream before returning. */
@@ -319,8 +334,8 @@ int b200emb_op_moe_router(const void* x, const float* router_w, const float* rou
  * (B200EMB_STATIC_ATTN_MAX_TILES tile records, about 256 KB, present on every GPU that loads
  * the library until the process exits) and the list is built by a kernel from d_cu_seqlens.
  * The call makes no cudaMalloc, cudaFree or other allocating call. A batch that needs more
- * query tiles (128 rows each for head_dim 64 and 128, 64 rows for other head dims; a sequence of
- * L tokens takes ceil(L / rows) tiles) is rejected with B200EMB_ERR_UNSUPPORTED. Like
+ * query tiles (128 rows each for head_dim 64 and 128 and for bidirectional head_dim 32, 64 rows
+ * otherwise; a sequence of L tokens takes ceil(L / rows) tiles) is rejected with B200EMB_ERR_UNSUPPORTED. Like
  * b200emb_op_attention it waits for the stream before it returns (it reads the kernels' error
  * word back). The first call on each device looks up the array's device address; make that
  * first call before any stream capture. All calls on a device share the array: two calls whose

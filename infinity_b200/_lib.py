@@ -64,6 +64,8 @@ SIGNATURES = {
     "b200emb_partition": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_double, C.c_double, _P]),
     "b200emb_cost_model": (C.c_int, [C.POINTER(ModelDesc), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "b200emb_test_fail_allocs": (C.c_int, [C.c_int32, C.c_int32]),
+    "b200emb_checked_build": (C.c_int, []),
+    "b200emb_tensor_map_stats": (C.c_int, [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "b200emb_last_error": (C.c_char_p, []),
     "b200emb_device_count": (C.c_int, []),
     "b200emb_selftest_bounded_wait": (C.c_int, [C.c_int32]),

@@ -18,6 +18,9 @@ CSRC = PKG_DIR / "csrc"
 LIB_DIR = PKG_DIR / "lib"
 LIB_PATH = LIB_DIR / "libb200emb.so"
 OBJ_DIR = PKG_DIR / "build"
+# The checked build: the same sources with -DB200EMB_BOUNDS=1 (device-side index range checks, csrc/bounds.cuh).
+CHECKED_LIB_PATH = LIB_DIR / "libb200emb_checked.so"
+CHECKED_OBJ_DIR = PKG_DIR / "build_checked"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -34,8 +37,9 @@ def _nvcc() -> str:
     return exe
 
 
-def _source_digest() -> str:
+def _source_digest(extra: str = "") -> str:
     h = hashlib.sha256()
+    h.update(extra.encode())
     files = sorted(CSRC.glob("*")) + [PKG_DIR.parent / "include" / "b200emb.h"]
     for f in files:
         h.update(f.name.encode())
@@ -44,25 +48,30 @@ def _source_digest() -> str:
     return h.hexdigest()
 
 
-def is_current() -> bool:
-    stamp = LIB_DIR / "source.sha256"
-    return LIB_PATH.exists() and stamp.exists() and stamp.read_text().strip() == _source_digest()
+def is_current(checked: bool = False) -> bool:
+    stamp = LIB_DIR / ("source_checked.sha256" if checked else "source.sha256")
+    lib = CHECKED_LIB_PATH if checked else LIB_PATH
+    return lib.exists() and stamp.exists() and stamp.read_text().strip() == _source_digest("checked" if checked else "")
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile and link the library; returns its path. A no-op when the sources are unchanged."""
-    if not force and is_current():
-        return LIB_PATH
+def build(force: bool = False, verbose: bool = False, checked: bool = False) -> Path:
+    """Compile and link the library; returns its path. A no-op when the sources are unchanged.
+    ``checked=True`` builds the variant with device-side index range checks beside the normal one."""
+    lib_path = CHECKED_LIB_PATH if checked else LIB_PATH
+    obj_dir = CHECKED_OBJ_DIR if checked else OBJ_DIR
+    if not force and is_current(checked):
+        return lib_path
     nvcc = _nvcc()
     LIB_DIR.mkdir(exist_ok=True)
-    OBJ_DIR.mkdir(exist_ok=True)
+    obj_dir.mkdir(exist_ok=True)
     sources = sorted(CSRC.glob("*.cu"))
+    flags = NVCC_FLAGS + (["-DB200EMB_BOUNDS=1"] if checked else [])
 
     def compile_one(src: Path) -> Path:
-        obj = OBJ_DIR / (src.stem + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        obj = obj_dir / (src.stem + ".o")
+        cmd = [nvcc, *flags, "-c", str(src), "-o", str(obj)]
         proc = subprocess.run(cmd, capture_output=True, text=True)
-        (OBJ_DIR / (src.stem + ".ptxas.log")).write_text(proc.stdout + proc.stderr)
+        (obj_dir / (src.stem + ".ptxas.log")).write_text(proc.stdout + proc.stderr)
         if proc.returncode != 0:
             raise RuntimeError(f"nvcc failed for {src.name}:\n{proc.stdout}\n{proc.stderr}")
         if verbose:
@@ -71,13 +80,16 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, len(sources))) as pool:
         objs = list(pool.map(compile_one, sources))
-    cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
+    cmd = [nvcc, "-shared", "-o", str(lib_path), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
+    if checked:
+        (LIB_DIR / "source_checked.sha256").write_text(_source_digest("checked"))
+        return lib_path
     (LIB_DIR / "source.sha256").write_text(_source_digest())
     (LIB_DIR / "commit.txt").write_text(source_commit())
-    return LIB_PATH
+    return lib_path
 
 
 def source_commit() -> str:
@@ -97,4 +109,5 @@ def source_commit() -> str:
 
 
 if __name__ == "__main__":
-    print(build(force=True, verbose=True))
+    import sys
+    print(build(force=True, verbose=True, checked="--checked" in sys.argv[1:]))

@@ -251,8 +251,7 @@ static constexpr int att_smem_bytes() {
 }
 
 int attention_tile_rows(int head_dim, int causal) {
-  (void)causal;
-  return (head_dim == 64 || head_dim == 128) ? 128 : ATT_BQ;
+  return (head_dim == 64 || head_dim == 128 || (head_dim == 32 && !causal)) ? 128 : ATT_BQ;
 }
 
 int attention_build_tiles_q(const int32_t* cu, int n_seqs, int bq, AttnTile* tiles) {

@@ -20,6 +20,9 @@
 // 90 cycles of operand moves, more than the 32-64 cycles these small MMAs take to execute.
 // The kernel is persistent, two CTAs per SM (256 of the 512 TMEM columns each), so one CTA's
 // softmax overlaps the other's MMAs.
+// head_dim 32 (template D = 32) runs the same pipeline on the same 128-row x 64-column, 128-byte-swizzled tiles: a tile
+// holds a PAIR of adjacent heads, and the operand descriptors of the odd head start 64 bytes into the swizzled
+// row (the way a K step advances them by 32), so S takes two K = 16 instructions and P V is 128 x 32 per 16 keys.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -34,8 +37,8 @@
 namespace b2 {
 
 static constexpr int TC_BKV = 128;
-static constexpr int TC_D = 64;
-static constexpr int TC_TILE_BYTES = 128 * TC_D * 2;  // 16 KB
+static constexpr int TC_TILE_COLS = 64;  // columns of a Q / K / V tile: one head of 64 or two heads of 32
+static constexpr int TC_TILE_BYTES = 128 * TC_TILE_COLS * 2;  // 16 KB
 static constexpr int TC_QSLOTS = 2;
 static constexpr int TC_KSLOTS = 2;
 static constexpr int TC_VSLOTS = 2;
@@ -44,7 +47,7 @@ static constexpr int TC_STAGE_BYTES = 4 * 16 * 128;  // output staging: 16 rows 
 static constexpr int TC_BAR_BYTES = 160;
 static constexpr int TC_SMEM_BYTES = TC_N_TILES * TC_TILE_BYTES + TC_STAGE_BYTES + TC_BAR_BYTES + 1024;
 static constexpr int TC_THREADS = 192;         // 4 softmax warps + TMA producer warp + MMA warp
-static constexpr uint32_t TC_TMEM_COLS = 256;  // S 128 | P 64 | O 64
+static constexpr uint32_t TC_TMEM_COLS = 256;  // S 128 | P 64 | O 64 (32 used for head_dim 32)
 static constexpr uint32_t TC_S_COL = 0, TC_P_COL = 128, TC_O_COL = 192;
 static constexpr float TC_LAZY_SUM = 65536.f;  // a tile's row sum of exp2(score - reference) above this moves the reference
 
@@ -62,8 +65,9 @@ __device__ __forceinline__ float ex2f(float x) {
 
 // Persistent: CTA b serves work items b, b + gridDim.x, ...; item i = (query tile i / n_heads,
 // head i % n_heads). Every role walks the same sequence of (item, key tile) steps.
+template <int D>
 __global__ void __launch_bounds__(TC_THREADS, 2)
-attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __restrict__ out,
+attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __restrict__ out,
                    const AttnTile* __restrict__ tiles, int n_items, int n_heads, int n_kv_heads, float scale_log2,
                    int* __restrict__ err_flag) {
   extern __shared__ uint8_t att_raw[];
@@ -135,12 +139,15 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
         const int h = item % n_heads;
         const int hk = h / (n_heads / n_kv_heads);
         const int n_kv = (t.seq_len + TC_BKV - 1) / TC_BKV;
+        // first column of the tile that holds head column block c (blocks of D columns): for D = 32 the
+        // even-aligned pair of blocks, so that the tile starts on a 128-byte boundary
+        auto tile_col = [](int c) { return D == 64 ? c * 64 : (c >> 1) * 64; };
         if (!mbar_wait(&q_empty[qslot], qphase ^ 1u)) {
           ok = false;
           break;
         }
         mbar_arrive_expect_tx(&q_full[qslot], TC_TILE_BYTES);
-        tma_load_2d(q_s + qslot * TC_TILE_BYTES, &tmap_qkv, &q_full[qslot], h * TC_D, t.seq_start + t.q_start);
+        tma_load_2d(q_s + qslot * TC_TILE_BYTES, &tmap_qkv, &q_full[qslot], tile_col(h), t.seq_start + t.q_start);
         ++q_fills;
         if (++qslot == TC_QSLOTS) {
           qslot = 0;
@@ -152,7 +159,7 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
             break;
           }
           mbar_arrive_expect_tx(&k_full[kslot], TC_TILE_BYTES);
-          tma_load_2d(k_s + kslot * TC_TILE_BYTES, &tmap_qkv, &k_full[kslot], (n_heads + hk) * TC_D,
+          tma_load_2d(k_s + kslot * TC_TILE_BYTES, &tmap_qkv, &k_full[kslot], tile_col(n_heads + hk),
                       t.seq_start + it * TC_BKV);
           ++k_fills;
           if (++kslot == TC_KSLOTS) {
@@ -164,7 +171,7 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
             break;
           }
           mbar_arrive_expect_tx(&v_full[vslot], TC_TILE_BYTES);
-          tma_load_2d(v_s + vslot * TC_TILE_BYTES, &tmap_qkv, &v_full[vslot], (n_heads + n_kv_heads + hk) * TC_D,
+          tma_load_2d(v_s + vslot * TC_TILE_BYTES, &tmap_qkv, &v_full[vslot], tile_col(n_heads + n_kv_heads + hk),
                       t.seq_start + it * TC_BKV);
           ++v_fills;
           if (++vslot == TC_VSLOTS) {
@@ -211,10 +218,14 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
       tc_fence_after_sync();
       const int nv = min(TC_BKV, s_len - s_it * TC_BKV);
       const uint32_t idesc = make_idesc_bf16_f32(128, (nv + 15) & ~15);
-      const uint64_t a_desc = make_kmajor_sw128_desc(q_addr + qslot * TC_TILE_BYTES);
-      const uint64_t b_desc = make_kmajor_sw128_desc(k_addr + kslot * TC_TILE_BYTES);
+      // head_dim 32: the odd column block of a tile starts 64 bytes (4 descriptor units) into the swizzled row
+      const int s_h = s_item % n_heads;
+      const int q_odd = D == 32 ? (s_h & 1) : 0;
+      const int k_odd = D == 32 ? ((n_heads + s_h / (n_heads / n_kv_heads)) & 1) : 0;
+      const uint64_t a_desc = make_kmajor_sw128_desc(q_addr + qslot * TC_TILE_BYTES) + 4 * q_odd;
+      const uint64_t b_desc = make_kmajor_sw128_desc(k_addr + kslot * TC_TILE_BYTES) + 4 * k_odd;
 #pragma unroll
-      for (int k = 0; k < TC_D / 16; ++k)
+      for (int k = 0; k < D / 16; ++k)
         if (elect_one()) tc_mma_f16(tmem_u + TC_S_COL, a_desc + 2 * k, b_desc + 2 * k, idesc, k != 0);
       if (elect_one()) {
         tc_commit(bar_s);
@@ -237,10 +248,11 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
     };
     ok = issue_s();
     uint32_t gi = 0;
-    const uint32_t idesc_pv = make_idesc_bf16_f32_b_mn(128, TC_D);
+    const uint32_t idesc_pv = make_idesc_bf16_f32_b_mn(128, D);
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       const int L = __shfl_sync(0xffffffffu, tiles[item / n_heads].seq_len, 0);
       const int n_kv = (L + TC_BKV - 1) / TC_BKV;
+      const int v_odd = D == 32 ? ((n_heads + n_kv_heads + (item % n_heads) / (n_heads / n_kv_heads)) & 1) : 0;
       for (int it = 0; it < n_kv; ++it, ++gi) {
         const int n_eff = (min(TC_BKV, L - it * TC_BKV) + 15) & ~15;
         if (!wait_all(bar_p, gi & 1u)) {
@@ -259,7 +271,7 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
           break;
         }
         tc_fence_after_sync();
-        const uint64_t v_desc = make_mnmajor_sw128_desc(v_addr + vslot * TC_TILE_BYTES, 16);
+        const uint64_t v_desc = make_mnmajor_sw128_desc(v_addr + vslot * TC_TILE_BYTES, 16) + 4 * v_odd;
         // 16 keys = two 8-row groups of the MN-major V tile = 2048 bytes (128 in descriptor units); 16 keys
         // of P = 8 columns
 #pragma unroll
@@ -290,7 +302,7 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
     float out_inv = 0.f;
     int out_rows = 0;
     __nv_bfloat16* out_dst = nullptr;
-    const size_t out_stride = static_cast<size_t>(n_heads) * TC_D;
+    const size_t out_stride = static_cast<size_t>(n_heads) * D;
     // O of the pending item -> bf16 rows in global memory. Each warp stages 16 rows at a time in shared
     // memory (128 bytes per row, 16-byte chunks XOR-swizzled by row so that neither pass has bank
     // conflicts) and writes them out as whole 128-byte lines, four rows per instruction.
@@ -299,6 +311,33 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
       failed = __any_sync(0xffffffffu, failed);
       if (failed) return;
       tc_fence_after_sync();
+      if (D == 32) {
+        // 64 bytes per row: every lane writes its own row (two whole sectors)
+        if (out_rows > 0) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(lane_base + TC_O_COL, r);
+          tmem_ld_wait_for(r);
+          if (lane < out_rows) {
+            const float inv = out_inv;
+            uint4* dst = reinterpret_cast<uint4*>(out_dst + static_cast<size_t>(lane) * out_stride);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint4 u;
+              __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[c * 8 + 0]) * inv, __uint_as_float(r[c * 8 + 1]) * inv);
+              __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[c * 8 + 2]) * inv, __uint_as_float(r[c * 8 + 3]) * inv);
+              __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[c * 8 + 4]) * inv, __uint_as_float(r[c * 8 + 5]) * inv);
+              __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[c * 8 + 6]) * inv, __uint_as_float(r[c * 8 + 7]) * inv);
+              u.x = *reinterpret_cast<uint32_t*>(&p0);
+              u.y = *reinterpret_cast<uint32_t*>(&p1);
+              u.z = *reinterpret_cast<uint32_t*>(&p2);
+              u.w = *reinterpret_cast<uint32_t*>(&p3);
+              dst[c] = u;
+            }
+          }
+        }
+        out_pending = false;
+        return;
+      }
       if (out_rows > 0) {
         uint32_t ra[32], rb[32];
         tmem_ld_32x32b_x32(lane_base + TC_O_COL, ra);
@@ -476,7 +515,7 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
                 // P V of the previous step has finished (waited for above)
                 const float2 alpha2 = make_float2(alpha, alpha);
 #pragma unroll
-                for (int c = 0; c < TC_D; c += 32) {
+                for (int c = 0; c < D; c += 32) {
                   tmem_ld_32x32b_x32(lane_base + TC_O_COL + c, ra);
                   tmem_ld_wait_for(ra);
 #pragma unroll
@@ -510,7 +549,7 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
       out_pending = true;
       out_inv = 1.f / l_run;
       out_rows = warp_active ? min(32, L - (t.q_start + warp * 32)) : 0;
-      out_dst = out + static_cast<size_t>(t.seq_start + t.q_start + warp * 32) * out_stride + h * TC_D;
+      out_dst = out + static_cast<size_t>(t.seq_start + t.q_start + warp * 32) * out_stride + h * D;
     }
     if (!failed && out_pending) write_pending();
     if (failed && lane == 0) atomicExch(err_flag, 4);
@@ -526,30 +565,35 @@ attn_tc_d64_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* 
 
 
 int attention_tc_init_device() {
-  B2_CUDA_CHECK(cudaFuncSetAttribute(attn_tc_d64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
+  B2_CUDA_CHECK(cudaFuncSetAttribute(attn_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
+  B2_CUDA_CHECK(cudaFuncSetAttribute(attn_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES));
   return B200EMB_OK;
 }
 
 int launch_attention_tc(const void* qkv, void* out, const AttnTile* d_tiles, int n_tiles, int n_tokens, int n_heads,
                         int n_kv_heads, int head_dim, int causal, int variant, int sm_count, int* err_flag,
                         cudaStream_t stream) {
-  if (head_dim != TC_D || causal || variant == 1)
+  if ((head_dim != 64 && head_dim != 32) || causal || (variant == 1 && head_dim != 32))
     return launch_attention_tc2(qkv, out, d_tiles, n_tiles, n_tokens, n_heads, n_kv_heads, head_dim, causal, sm_count,
                                 err_flag, stream);
   if (n_tiles <= 0) return B200EMB_OK;
   if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_heads > 65535)
     return set_error(B200EMB_ERR_INVALID, "attention: bad head counts %d / %d", n_heads, n_kv_heads);
   CUtensorMap tm;
-  const uint64_t width = static_cast<uint64_t>(n_heads + 2 * n_kv_heads) * TC_D;
+  const uint64_t width = static_cast<uint64_t>(n_heads + 2 * n_kv_heads) * head_dim;
   int rc = make_tmap_bf16_2d(&tm, qkv, static_cast<uint64_t>(n_tokens), width, 128);
   if (rc) return rc;
-  const float scale_log2 = 1.4426950408889634f / 8.0f;  // log2(e) / sqrt(64)
+  const float scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(head_dim));  // log2(e) / sqrt(head_dim)
   const long long n_items = static_cast<long long>(n_tiles) * n_heads;
   if (n_items > 0x7fffffffLL) return set_error(B200EMB_ERR_UNSUPPORTED, "attention: too many tiles");
   const int grid = static_cast<int>(n_items < 2LL * sm_count ? n_items : 2LL * sm_count);
-  cudaError_t e = launch_pdl(attn_tc_d64_kernel, dim3(grid), dim3(TC_THREADS), TC_SMEM_BYTES, stream, tm,
-                             reinterpret_cast<__nv_bfloat16*>(out), d_tiles, static_cast<int>(n_items), n_heads,
-                             n_kv_heads, scale_log2, err_flag);
+  cudaError_t e = head_dim == 64
+                      ? launch_pdl(attn_tc_kernel<64>, dim3(grid), dim3(TC_THREADS), TC_SMEM_BYTES, stream, tm,
+                                   reinterpret_cast<__nv_bfloat16*>(out), d_tiles, static_cast<int>(n_items), n_heads,
+                                   n_kv_heads, scale_log2, err_flag)
+                      : launch_pdl(attn_tc_kernel<32>, dim3(grid), dim3(TC_THREADS), TC_SMEM_BYTES, stream, tm,
+                                   reinterpret_cast<__nv_bfloat16*>(out), d_tiles, static_cast<int>(n_items), n_heads,
+                                   n_kv_heads, scale_log2, err_flag);
   if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "attention launch: %s", cudaGetErrorString(e));
   return B200EMB_OK;
 }

@@ -25,9 +25,18 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include <string.h>
 
+#include <mutex>
+#include <unordered_map>
+
+#include "bounds.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
+
+// expert of a row block as read from tile_expert[]: -1 (unused block) or [0, n_experts); the checked build
+// turns anything else into -1 and records it
+#define B2_EXPERT(x) (static_cast<int>(B2_IDX(static_cast<long long>(x) + 1, 0, BOUNDS_GEMM_EXPERT)) - 1)
 #include "gemm_tiles.cuh"
 
 namespace b2 {
@@ -109,7 +118,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         const int n0 = nt * BN;
         // grouped mode: row block m0/BM belongs to expert e (its weights are rows [e*N, e*N + N) of W);
         // e < 0 marks an unused row block, skipped by every role alike
-        const int expert = tile_expert != nullptr ? __ldg(tile_expert + mt) : 0;
+        const int expert = tile_expert != nullptr ? B2_EXPERT(__ldg(tile_expert + mt)) : 0;
         if (expert < 0) continue;
         const int w_row0 = expert * N + n0 + static_cast<int>(cta_rank) * Cfg::B_ROWS * (PAIR ? 1 : 0);
         for (int kb = 0; kb < k_blocks; ++kb) {
@@ -170,7 +179,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         if (tile_expert != nullptr) {
           int mt, nt;
           tile_coords(tile, m_tiles, n_tiles, group_m, mt, nt);
-          if (__shfl_sync(0xffffffffu, __ldg(tile_expert + mt), 0) < 0) continue;
+          if (__shfl_sync(0xffffffffu, B2_EXPERT(__ldg(tile_expert + mt)), 0) < 0) continue;
         }
         const int lt = local_tile++;
         const int acc = lt & 1;
@@ -250,7 +259,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     for (int tile = first_tile; tile < total_tiles; tile += tile_step) {
       int mt, nt;
       tile_coords(tile, m_tiles, n_tiles, group_m, mt, nt);
-      const int expert = tile_expert != nullptr ? __ldg(tile_expert + mt) : 0;
+      const int expert = tile_expert != nullptr ? B2_EXPERT(__ldg(tile_expert + mt)) : 0;
       if (expert < 0) continue;
       const int lt = local_tile++;
       const int m0 = mt * TILE_M + static_cast<int>(cta_rank) * BM;
@@ -405,9 +414,57 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+namespace {
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+    h ^= (k.rows + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= (k.cols + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= ((static_cast<uint64_t>(k.box_rows) << 40 | static_cast<uint64_t>(k.box_cols) << 16 | k.kind) + (h << 6) + (h >> 2));
+    return static_cast<size_t>(h);
+  }
+};
+struct TmapKeyEq {
+  bool operator()(const TmapKey& a, const TmapKey& b) const {
+    return a.base == b.base && a.rows == b.rows && a.cols == b.cols && a.box_rows == b.box_rows && a.box_cols == b.box_cols &&
+           a.kind == b.kind;
+  }
+};
+std::mutex g_tmap_mu;
+std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash, TmapKeyEq> g_tmaps;
+uint64_t g_tmap_hits = 0, g_tmap_misses = 0;
+constexpr size_t TMAP_CACHE_LIMIT = 16384;
+}  // namespace
+
+bool tmap_cache_get(const TmapKey& key, CUtensorMap_st* out) {
+  std::lock_guard<std::mutex> lock(g_tmap_mu);
+  auto it = g_tmaps.find(key);
+  if (it == g_tmaps.end()) {
+    ++g_tmap_misses;
+    return false;
+  }
+  ++g_tmap_hits;
+  memcpy(out, &it->second, sizeof(CUtensorMap));
+  return true;
+}
+
+void tmap_cache_put(const TmapKey& key, const CUtensorMap_st* tm) {
+  std::lock_guard<std::mutex> lock(g_tmap_mu);
+  if (g_tmaps.size() >= TMAP_CACHE_LIMIT) g_tmaps.clear();
+  memcpy(&g_tmaps[key], tm, sizeof(CUtensorMap));
+}
+
+void tmap_cache_stats(uint64_t* hits, uint64_t* misses) {
+  std::lock_guard<std::mutex> lock(g_tmap_mu);
+  *hits = g_tmap_hits;
+  *misses = g_tmap_misses;
+}
+
 // bf16 row-major [rows, cols] matrix, box = [box_rows, 64 columns], 128-byte swizzle; loads zero-fill
 // outside the matrix, stores are clipped.
 int make_tmap_bf16_2d(CUtensorMap_st* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  const TmapKey key{base, rows, cols, box_rows, static_cast<uint32_t>(BK), 0u};
+  if (tmap_cache_get(key, out)) return B200EMB_OK;
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return set_error(B200EMB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
   cuuint64_t dims[2] = {cols, rows};
@@ -418,6 +475,7 @@ int make_tmap_bf16_2d(CUtensorMap_st* out, const void* base, uint64_t rows, uint
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return set_error(B200EMB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  tmap_cache_put(key, out);
   return B200EMB_OK;
 }
 
@@ -554,6 +612,7 @@ int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, i
       ((M + 255) / 256) * ((N + 255) / 256) >= sm_count / 2)
     pair = true;
   if (pair && tile_expert != nullptr) return set_error(B200EMB_ERR_INVALID, "gemm: the CTA-pair kernel has no grouped mode");
+  if (tile_expert != nullptr) B2_SET_LIMIT(0, static_cast<long long>(n_experts) + 1, stream);  // values are expert + 1
   CUtensorMap ta, tw, tc;
   int rc = make_tmap_bf16_2d(&ta, A, (uint64_t)M, (uint64_t)K, BM);
   if (rc) return rc;
@@ -570,6 +629,11 @@ int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, i
     case 64: return launch_epi<64>(epi, ta, tw, tc, bias, alpha, M, N, K, tile_expert, sm_count, err_flag, stream);
   }
   return set_error(B200EMB_ERR_INVALID, "gemm: unsupported tile width %d", bn);
+}
+
+int gemm_bf16_bounds_status(cudaStream_t stream) {
+  (void)stream;
+  return B2_TAKE_STATUS(stream);
 }
 
 }  // namespace b2

@@ -15,8 +15,13 @@
 #include <math.h>
 #include <stdint.h>
 
+#include "bounds.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
+
+// expert of a row block as read from tile_expert[]: -1 (unused block) or [0, n_experts); the checked build
+// turns anything else into -1 and records it
+#define B2_EXPERT(x) (static_cast<int>(B2_IDX(static_cast<long long>(x) + 1, 0, BOUNDS_GEMM_EXPERT)) - 1)
 
 namespace b2 {
 
@@ -162,7 +167,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const int mb = tile / n_tiles;
         const int m0 = mb * F8_BM;
         const int n0 = (tile % n_tiles) * F8_BN;
-        const int expert = tile_expert != nullptr ? __ldg(tile_expert + mb) : 0;
+        const int expert = tile_expert != nullptr ? B2_EXPERT(__ldg(tile_expert + mb)) : 0;
         if (expert < 0) continue;
         const int w_row0 = expert * N + n0;
         for (int kb = 0; kb < k_blocks; ++kb) {
@@ -209,7 +214,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        if (tile_expert != nullptr && __shfl_sync(0xffffffffu, __ldg(tile_expert + tile / n_tiles), 0) < 0) continue;
+        if (tile_expert != nullptr && __shfl_sync(0xffffffffu, B2_EXPERT(__ldg(tile_expert + tile / n_tiles)), 0) < 0) continue;
         const int lt = local_tile++;
         const int acc = lt & 1;
         if (!wait_all(&acc_empty_bar[acc], ((lt >> 1) & 1u) ^ 1u)) {
@@ -265,7 +270,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     bool ok = true;
     int local_tile = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-      const int expert = tile_expert != nullptr ? __ldg(tile_expert + tile / n_tiles) : 0;
+      const int expert = tile_expert != nullptr ? B2_EXPERT(__ldg(tile_expert + tile / n_tiles)) : 0;
       if (expert < 0) continue;
       const int lt = local_tile++;
       const int m0 = (tile / n_tiles) * F8_BM;
@@ -454,6 +459,8 @@ typedef CUresult (*EncodeTiledFn8)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 
 static int make_tmap_u8_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols = 128,
                            bool swizzle = true) {
+  const TmapKey key{base, rows, cols, 128u, box_cols, swizzle ? 1u : 2u};
+  if (tmap_cache_get(key, out)) return B200EMB_OK;
   static EncodeTiledFn8 fn = nullptr;
   if (fn == nullptr) {
     void* p = nullptr;
@@ -472,6 +479,7 @@ static int make_tmap_u8_2d(CUtensorMap* out, const void* base, uint64_t rows, ui
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return set_error(B200EMB_ERR_CUDA, "cuTensorMapEncodeTiled (u8) failed (%d)", (int)r);
+  tmap_cache_put(key, out);
   return B200EMB_OK;
 }
 
@@ -497,6 +505,7 @@ int launch_gemm_mxfp8(const void* Aq, const void* sfa_atoms, const void* Wq, con
   CUtensorMap ta, tw, tc;
   int rc = make_tmap_u8_2d(&ta, Aq, (uint64_t)M, (uint64_t)K);
   if (rc) return rc;
+  if (tile_expert != nullptr) B2_SET_LIMIT(0, static_cast<long long>(n_experts) + 1, stream);  // values are expert + 1
   rc = make_tmap_u8_2d(&tw, Wq, (uint64_t)N * (tile_expert != nullptr ? n_experts : 1), (uint64_t)K);
   if (rc) return rc;
   const bool out_fp8 = out_sf_atoms != nullptr;
@@ -519,6 +528,11 @@ int launch_gemm_mxfp8(const void* Aq, const void* sfa_atoms, const void* Wq, con
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "mxfp8 gemm launch: %s", cudaGetErrorString(e));
   return B200EMB_OK;
+}
+
+int gemm_mxfp8_bounds_status(cudaStream_t stream) {
+  (void)stream;
+  return B2_TAKE_STATUS(stream);
 }
 
 }  // namespace b2

@@ -71,6 +71,19 @@ int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, i
 int gemm_init_device();
 // TMA descriptor of a bf16 row-major [rows, cols] matrix: box [box_rows x 64 columns], 128-byte swizzle.
 int make_tmap_bf16_2d(::CUtensorMap_st* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+// Descriptors depend on (address, shape, box, element kind) only, never on the memory's contents, and a forward
+// asks for the same few hundred of them every time (weights, workspace slices): the builders keep the encoded
+// 128 bytes per key and skip the driver call on a repeat. `kind` separates element types / swizzle modes.
+// Process-wide, guarded by a mutex, emptied when it reaches 16 384 entries.
+struct TmapKey {
+  const void* base;
+  uint64_t rows, cols;
+  uint32_t box_rows, box_cols, kind;
+};
+bool tmap_cache_get(const TmapKey& key, ::CUtensorMap_st* out);
+void tmap_cache_put(const TmapKey& key, const ::CUtensorMap_st* tm);
+// {hits, misses} since the library was loaded.
+void tmap_cache_stats(uint64_t* hits, uint64_t* misses);
 
 // ---- GEMM against NVFP4 weights expanded inside the kernel (gemm_w4.cu) ----
 // Wq: packed e2m1 [N, K / 2], Ws: e4m3 block scales [N, K / 16], alpha = 1 / tensor scale. CTA-pair tiles of
@@ -102,13 +115,13 @@ struct AttnTile {
 // Returns the number of tiles; `tiles` may be null to only count.
 int attention_build_tiles_q(const int32_t* h_cu_seqlens, int n_seqs, int bq, AttnTile* tiles);
 // Query-tile height of the kernel that serves (head_dim, causal): 128 for the tensor-memory
-// kernels (head_dim 64 and 128), 64 for the mma.sync kernel.
+// kernels (head_dim 64 and 128, head_dim 32 bidirectional), 64 for the mma.sync kernel.
 int attention_tile_rows(int head_dim, int causal);
 int launch_attention(const void* qkv, void* out, const AttnTile* d_tiles, int n_tiles, int n_heads, int n_kv_heads,
                      int head_dim, int causal, cudaStream_t stream);
 int attention_init_device();
 // Tensor-memory (tcgen05) kernels, 128-row query tiles. launch_attention_tc picks the kernel:
-// head_dim 64 bidirectional -> two CTAs per SM (attention_tc.cu); head_dim 128, or causal -> one CTA per
+// head_dim 64 or 32 bidirectional -> two CTAs per SM (attention_tc.cu); head_dim 128, or causal -> one CTA per
 // SM with double-buffered S (attention_tc2.cu). variant 1 forces the latter for every supported shape.
 int launch_attention_tc(const void* qkv, void* out, const AttnTile* d_tiles, int n_tiles, int n_tokens, int n_heads,
                         int n_kv_heads, int head_dim, int causal, int variant, int sm_count, int* err_flag,
@@ -146,7 +159,7 @@ int launch_wait_selftest(unsigned long long limit_ns, int* err_flag, cudaStream_
 int launch_embed_ln(const int32_t* ids, const int32_t* types, const int32_t* d_cu, int n_seqs, int n_tokens,
                     const void* word, const void* pos, const void* type_table, const float* gamma, const float* beta,
                     int hidden, int pos_offset, float eps, void* out, cudaStream_t stream, int vocab = 0,
-                    int type_vocab = 0, int* err_flag = nullptr);
+                    int type_vocab = 0, int* err_flag = nullptr, int n_positions = -1);
 int launch_add_ln(const void* x, const void* y, const float* gamma, const float* beta, int n_rows, int hidden,
                   float eps, void* out, cudaStream_t stream);
 // h (fp32) += y (bf16, nullable); out = RMSNorm(h) * gamma (bf16)
@@ -155,7 +168,7 @@ int launch_add_rmsnorm(float* h, const void* y, const float* gamma, int n_rows, 
 int launch_widen(const void* x, float* out, size_t n_elems, cudaStream_t stream);
 // rotates the first n_rot_heads heads (queries then keys) of every qkv row in place; cos_sin = [max_pos, head_dim/2] (cos, sin) pairs
 int launch_rope(void* qkv, const int32_t* d_cu, int n_seqs, int n_tokens, int n_rot_heads, int row_width,
-                int head_dim, const float* cos_sin, cudaStream_t stream);
+                int head_dim, const float* cos_sin, cudaStream_t stream, int n_positions = -1);
 // output embedding quantisation (int8 / uint8 with calibration ranges, binary / ubinary bit packing)
 int launch_quantize_embeddings(const float* x, int n_rows, int dim, int64_t x_row_stride, int precision,
                                const double* d_ranges, void* out, int64_t out_row_stride_bytes, cudaStream_t stream);
@@ -163,7 +176,14 @@ int launch_quantize_embeddings(const float* x, int n_rows, int dim, int64_t x_ro
 int launch_token_rows(const void* x, int n_tokens, int hidden, int normalize, float* out, int64_t out_row_stride,
                       cudaStream_t stream);
 int launch_pool(const void* x, const int32_t* d_cu, int n_seqs, int hidden, int pooling, int normalize, void* out,
-                int64_t out_row_stride, int out_bf16, cudaStream_t stream);
+                int64_t out_row_stride, int out_bf16, cudaStream_t stream, int n_tokens = -1);
+// The trailing n_positions / n_tokens of launch_embed_ln, launch_rope and launch_pool are the limits of the checked
+// build (-DB200EMB_BOUNDS=1, see bounds.cuh) for the indices those kernels derive from cu_seqlens on the device;
+// negative = not checked, ignored by the normal build. Each unit with checks reports and clears its status word:
+int rowops_bounds_status(cudaStream_t stream);
+int moe_bounds_status(cudaStream_t stream);
+int gemm_bf16_bounds_status(cudaStream_t stream);
+int gemm_mxfp8_bounds_status(cudaStream_t stream);
 // logits[i, l] = dot(x[i, :], W[l, :]) + b[l]; x bf16 [n, hidden], W bf16 [n_labels, hidden], out fp32.
 int launch_small_proj(const void* x, const void* W, const float* bias, int n_rows, int hidden, int n_labels,
                       float* out, int64_t out_row_stride, cudaStream_t stream);

@@ -13,6 +13,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "bounds.cuh"
 #include "kernels.h"
 
 namespace b2 {
@@ -376,14 +377,14 @@ moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restric
   // with ONE atomic (the lowest such lane adds the group size), then the warp copies the 32 rows
   for (int s0 = (blockIdx.x * MOE_WARPS + (threadIdx.x >> 5)) * 32; s0 < n_slots; s0 += warps_total * 32) {
     const int s = s0 + lane;
-    const int e = s < n_slots ? topk_idx[s] : -1 - lane;  // distinct dummies for lanes past the end
+    const int e = s < n_slots ? static_cast<int>(B2_IDX(topk_idx[s], 0, BOUNDS_MOE_EXPERT)) : -1 - lane;  // distinct dummies for lanes past the end
     const uint32_t peers = __match_any_sync(0xffffffffu, e);
     const int leader = __ffs(peers) - 1;
     const int rank = __popc(peers & ((1u << lane) - 1u));
     int base = 0;
     if (lane == leader && e >= 0) base = atomicAdd(cursor + e, __popc(peers));
     base = __shfl_sync(0xffffffffu, base, leader);
-    const int my_row = base + rank;
+    const int my_row = s < n_slots ? static_cast<int>(B2_IDX(base + rank, 1, BOUNDS_MOE_ROW)) : 0;
     if (s < n_slots) row_of[s] = my_row;
     const int n_here = min(32, n_slots - s0);
     for (int j = 0; j < n_here; ++j) {
@@ -407,14 +408,14 @@ moe_scatter_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __r
   const int kblocks = hidden >> 5, kgroups = hidden >> 7;
   for (int s0 = (blockIdx.x * MOE_WARPS + (threadIdx.x >> 5)) * 32; s0 < n_slots; s0 += warps_total * 32) {
     const int s = s0 + lane;
-    const int e = s < n_slots ? topk_idx[s] : -1 - lane;
+    const int e = s < n_slots ? static_cast<int>(B2_IDX(topk_idx[s], 0, BOUNDS_MOE_EXPERT)) : -1 - lane;
     const uint32_t peers = __match_any_sync(0xffffffffu, e);
     const int leader = __ffs(peers) - 1;
     const int rank = __popc(peers & ((1u << lane) - 1u));
     int base = 0;
     if (lane == leader && e >= 0) base = atomicAdd(cursor + e, __popc(peers));
     base = __shfl_sync(0xffffffffu, base, leader);
-    const int my_row = base + rank;
+    const int my_row = s < n_slots ? static_cast<int>(B2_IDX(base + rank, 1, BOUNDS_MOE_ROW)) : 0;
     if (s < n_slots) row_of[s] = my_row;
     const int n_here = min(32, n_slots - s0);
     // The top_k slots of a token are consecutive: its row is loaded and quantised once and written to
@@ -513,7 +514,7 @@ moe_combine_ln_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
       gn[k] = 0.f;
       if (k < top_k) {
         gn[k] = __ldg(topk_w + static_cast<size_t>(tok) * top_k + k);
-        yr[k] = yperm + static_cast<size_t>(__ldg(row_of + static_cast<size_t>(tok) * top_k + k)) * hidden;
+        yr[k] = yperm + static_cast<size_t>(B2_IDX(__ldg(row_of + static_cast<size_t>(tok) * top_k + k), 1, BOUNDS_MOE_ROW)) * hidden;
       }
     }
 #pragma unroll
@@ -547,7 +548,7 @@ moe_combine_ln_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
     }
     for (int k = PRE; k < top_k; ++k) {
       const float g = topk_w[static_cast<size_t>(t) * top_k + k];
-      const __nv_bfloat16* yr = yperm + static_cast<size_t>(row_of[static_cast<size_t>(t) * top_k + k]) * hidden;
+      const __nv_bfloat16* yr = yperm + static_cast<size_t>(B2_IDX(row_of[static_cast<size_t>(t) * top_k + k], 1, BOUNDS_MOE_ROW)) * hidden;
 #pragma unroll
       for (int i = 0; i < NCH; ++i) {
         const int c = lane + 32 * i;
@@ -652,6 +653,8 @@ int launch_moe_scatter(const void* x, const int32_t* topk_idx, const int32_t* co
                        cudaStream_t stream, void* xq, void* sf_atoms) {
   if (n_tokens <= 0) return B200EMB_OK;
   const int max_blocks = moe_max_row_blocks(n_tokens, top_k, n_experts);
+  B2_SET_LIMIT(0, n_experts, stream);
+  B2_SET_LIMIT(1, static_cast<long long>(max_blocks) * 128, stream);  // also the limit of the combine that follows
   moe_offsets_kernel<<<1, 256, 0, stream>>>(counts, n_experts, max_blocks, cursor, tile_expert);
   if (xq != nullptr) {
     if (hidden % 128) return set_error(B200EMB_ERR_INVALID, "moe scatter (mxfp8): hidden %d not a multiple of 128", hidden);
@@ -688,6 +691,11 @@ int launch_moe_combine_ln(const void* x, const void* yperm, const int32_t* row_o
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "moe combine launch: %s", cudaGetErrorString(e));
   return B200EMB_OK;
+}
+
+int moe_bounds_status(cudaStream_t stream) {
+  (void)stream;
+  return B2_TAKE_STATUS(stream);
 }
 
 }  // namespace b2

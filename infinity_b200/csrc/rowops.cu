@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "bounds.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
 
@@ -159,7 +160,7 @@ embed_ln_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ typ
       const int mid = (lo + hi) >> 1;
       if (__ldg(cu + mid) <= t) lo = mid; else hi = mid;
     }
-    p = pos_offset + t - __ldg(cu + lo);
+    p = static_cast<int>(B2_IDX(pos_offset + t - __ldg(cu + lo), 2, BOUNDS_EMBED_POSITION));
   }
   const int id = checked_index(__ldg(ids + t), vocab, err_flag, ERR_BAD_TOKEN_ID);
   const __nv_bfloat16* wrow = word + static_cast<size_t>(id) * hidden;
@@ -402,7 +403,7 @@ rope_kernel(__nv_bfloat16* __restrict__ qkv, const int32_t* __restrict__ cu, int
     const int mid = (lo + hi) >> 1;
     if (__ldg(cu + mid) <= t) lo = mid; else hi = mid;
   }
-  const int pos = t - __ldg(cu + lo);
+  const int pos = static_cast<int>(B2_IDX(t - __ldg(cu + lo), 1, BOUNDS_ROPE_POSITION));
   const int half = head_dim >> 1;
   const int per_head = half >> 3;  // 16-byte groups of 8 pairs
   const float2* cst = cs + static_cast<size_t>(pos) * half;
@@ -440,7 +441,8 @@ pool_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ cu,
             int normalize, void* __restrict__ out, int64_t out_row_stride, int out_bf16) {
   extern __shared__ float pool_smem[];  // [row_groups][hidden] partial sums + 32 reduction slots
   const int seq = blockIdx.x;
-  const int start = __ldg(cu + seq), end = __ldg(cu + seq + 1);
+  int start = __ldg(cu + seq), end = __ldg(cu + seq + 1);
+  if (!B2_RANGE_OK(start, end, 0, BOUNDS_POOL_RANGE)) start = end = 0;  // checked build: an empty sequence instead
   const int n_chunks = hidden >> 3;
   const int cols = n_chunks < POOL_THREADS ? n_chunks : POOL_THREADS;  // threads across the hidden dim
   const int row_groups = POOL_THREADS / cols;
@@ -594,8 +596,9 @@ static int check_hidden(int hidden, int max_chunks_per_lane) {
 int launch_embed_ln(const int32_t* ids, const int32_t* types, const int32_t* d_cu, int n_seqs, int n_tokens,
                     const void* word, const void* pos, const void* type_table, const float* gamma, const float* beta,
                     int hidden, int pos_offset, float eps, void* out, cudaStream_t stream, int vocab, int type_vocab,
-                    int* err_flag) {
+                    int* err_flag, int n_positions) {
   if (n_tokens <= 0) return B200EMB_OK;
+  B2_SET_LIMIT(2, n_positions, stream);
   int rc = check_hidden(hidden, 16);
   if (rc) return rc;
   if (gamma == nullptr && pos == nullptr && type_table == nullptr) {
@@ -681,8 +684,9 @@ int launch_widen(const void* x, float* out, size_t n_elems, cudaStream_t stream)
 }
 
 int launch_rope(void* qkv, const int32_t* d_cu, int n_seqs, int n_tokens, int n_rot_heads, int row_width,
-                int head_dim, const float* cos_sin, cudaStream_t stream) {
+                int head_dim, const float* cos_sin, cudaStream_t stream, int n_positions) {
   if (n_tokens <= 0) return B200EMB_OK;
+  B2_SET_LIMIT(1, n_positions, stream);
   if (head_dim % 16 != 0) return set_error(B200EMB_ERR_UNSUPPORTED, "rope: head_dim %d not a multiple of 16", head_dim);
   rope_kernel<<<n_tokens, 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(qkv), d_cu, n_seqs, n_tokens, n_rot_heads,
                                            row_width, head_dim, reinterpret_cast<const float2*>(cos_sin));
@@ -747,8 +751,9 @@ int launch_token_rows(const void* x, int n_tokens, int hidden, int normalize, fl
 }
 
 int launch_pool(const void* x, const int32_t* d_cu, int n_seqs, int hidden, int pooling, int normalize, void* out,
-                int64_t out_row_stride, int out_bf16, cudaStream_t stream) {
+                int64_t out_row_stride, int out_bf16, cudaStream_t stream, int n_tokens) {
   if (n_seqs <= 0) return B200EMB_OK;
+  B2_SET_LIMIT(0, n_tokens, stream);
   if (hidden <= 0 || (hidden % 8) != 0 || (hidden >> 3) > POOL_THREADS * POOL_MAXC)
     return set_error(B200EMB_ERR_UNSUPPORTED, "pool: hidden size %d unsupported", hidden);
   if (pooling < B200EMB_POOL_CLS || pooling > B200EMB_POOL_LAST)
@@ -840,6 +845,11 @@ int launch_label_scores(float* logits, int n_rows, int n_labels, int64_t row_str
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(B200EMB_ERR_CUDA, "label_scores launch: %s", cudaGetErrorString(e));
   return B200EMB_OK;
+}
+
+int rowops_bounds_status(cudaStream_t stream) {
+  (void)stream;
+  return B2_TAKE_STATUS(stream);
 }
 
 }  // namespace b2

@@ -17,6 +17,7 @@
 #include <thread>
 #include <vector>
 
+#include "bounds.cuh"
 #include "kernels.h"
 
 namespace b2 {
@@ -671,7 +672,7 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
       if (rc) return rc;
       {
         KernelScope ks(c, B200EMB_KCLASS_OTHER);
-        rc = launch_rope(c->qkv, d_cu, n_seqs, T, d.n_heads + d.n_kv_heads, QKV, d.head_dim, c->rope_cs, c->stream);
+        rc = launch_rope(c->qkv, d_cu, n_seqs, T, d.n_heads + d.n_kv_heads, QKV, d.head_dim, c->rope_cs, c->stream, d.max_pos);
         if (rc) return rc;
       }
       {
@@ -702,13 +703,13 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
     }
     KernelScope ks(c, B200EMB_KCLASS_POOL);
     if (d.pooling == B200EMB_POOL_TOKENS) return launch_token_rows(c->x, T, H, d.normalize, d_out, out_row_stride, c->stream);
-    return launch_pool(c->x, d_cu, n_seqs, H, d.pooling, d.normalize, d_out, out_row_stride, 0, c->stream);
+    return launch_pool(c->x, d_cu, n_seqs, H, d.pooling, d.normalize, d_out, out_row_stride, 0, c->stream, T);
   }
   {
     KernelScope ks(c, B200EMB_KCLASS_EMBED);
     rc = launch_embed_ln(d_ids, w.type != nullptr ? d_types : nullptr, d_cu, n_seqs, T, w.word, w.pos, w.type,
                          w.emb_ln_g, w.emb_ln_b, H, d.pos_offset, d.norm_eps, c->x, c->stream, d.vocab, d.type_vocab,
-                         c->d_err);
+                         c->d_err, d.max_pos);
     if (rc) return rc;
   }
   for (int l = 0; l < d.n_layers; ++l) {
@@ -813,12 +814,12 @@ static int enqueue_forward(b200emb_handle* h, DeviceCtx* c, const int32_t* d_ids
     if (d.pooling == B200EMB_POOL_TOKENS)
       rc = launch_token_rows(c->x, T, H, d.normalize, d_out, out_row_stride, c->stream);
     else
-      rc = launch_pool(c->x, d_cu, n_seqs, H, d.pooling, d.normalize, d_out, out_row_stride, 0, c->stream);
+      rc = launch_pool(c->x, d_cu, n_seqs, H, d.pooling, d.normalize, d_out, out_row_stride, 0, c->stream, T);
     if (rc) return rc;
   } else {
     {
       KernelScope ks(c, B200EMB_KCLASS_POOL);
-      rc = launch_pool(c->x, d_cu, n_seqs, H, d.pooling, 0, c->pooled, H, 1, c->stream);
+      rc = launch_pool(c->x, d_cu, n_seqs, H, d.pooling, 0, c->pooled, H, 1, c->stream, T);
       if (rc) return rc;
     }
     rc = gemm(c, c->pooled, w.head_dense_w, w.head_dense_b, c->head_h, n_seqs, H, H, EPI_BIAS_TANH);
@@ -888,6 +889,45 @@ static size_t out_row_bytes(const b200emb_handle* h, int precision) {
     case B200EMB_EMB_UBINARY: return (size_t)h->out_dim / 8;
   }
   return sizeof(float) * (size_t)h->out_dim;
+}
+
+// Checked build (-DB200EMB_BOUNDS=1): reads and clears the status words of the units whose kernels check the
+// indices they read from device memory; a recorded code becomes B200EMB_ERR_INVALID. Nothing in the normal build.
+static int bounds_after_forward(cudaStream_t s) {
+#if B200EMB_BOUNDS
+  struct Unit {
+    const char* name;
+    int (*take)(cudaStream_t);
+  };
+  const Unit units[] = {{"row kernels", rowops_bounds_status},
+                        {"mixture-of-experts kernels", moe_bounds_status},
+                        {"bf16 GEMM", gemm_bf16_bounds_status},
+                        {"MXFP8 GEMM", gemm_mxfp8_bounds_status}};
+  int first = 0;
+  const char* where = "";
+  for (const Unit& u : units) {
+    const int v = u.take(s);  // every unit is read, so all words are clear afterwards
+    if (v < 0) return set_error(B200EMB_ERR_CUDA, "device index check: could not read the status of the %s", u.name);
+    if (v > 0 && first == 0) {
+      first = v;
+      where = u.name;
+    }
+  }
+  if (first != 0) {
+    const char* what = first == BOUNDS_POOL_RANGE        ? "a sequence's token range leaves the token stream"
+                       : first == BOUNDS_ROPE_POSITION   ? "a position beyond the rotary table"
+                       : first == BOUNDS_EMBED_POSITION  ? "a position beyond the position table"
+                       : first == BOUNDS_MOE_EXPERT      ? "an expert choice outside [0, n_experts)"
+                       : first == BOUNDS_MOE_ROW         ? "a row beyond the padded expert-contiguous layout"
+                       : first == BOUNDS_GEMM_EXPERT     ? "a row block's expert outside [0, n_experts)"
+                                                         : "unknown code";
+    return set_error(B200EMB_ERR_INVALID, "device index check: code %d (%s) in the %s; the access read index 0 instead", first,
+                     what, where);
+  }
+#else
+  (void)s;
+#endif
+  return B200EMB_OK;
 }
 
 // Runs one shard (host inputs, shard-local cu_seqlens) on device context c and leaves the
@@ -967,6 +1007,7 @@ static void run_shard(b200emb_handle* h, DeviceCtx* c, const int32_t* ids, const
     cudaStreamSynchronize(s);
     return fail(set_error(B200EMB_ERR_DEVICE_WAIT, "a device-side wait gave up (role %d) on device %d", code, c->dev));
   }
+  if (int brc = bounds_after_forward(s)) return fail(brc);
 }
 
 // Cost of a sequence of length L on one device, up to a common factor: a * L + b * L * L.
@@ -1036,6 +1077,14 @@ int b200emb_cost_model(const b200emb_model_desc* desc, double* cost_linear, doub
   if (desc == nullptr || cost_linear == nullptr || cost_quadratic == nullptr)
     return set_error(B200EMB_ERR_INVALID, "cost_model: null argument");
   cost_model(*desc, cost_linear, cost_quadratic);
+  return B200EMB_OK;
+}
+
+int b200emb_checked_build(void) { return B200EMB_BOUNDS; }
+
+int b200emb_tensor_map_stats(uint64_t* hits, uint64_t* misses) {
+  if (hits == nullptr || misses == nullptr) return set_error(B200EMB_ERR_INVALID, "tensor_map_stats: null argument");
+  tmap_cache_stats(hits, misses);
   return B200EMB_OK;
 }
 
@@ -1414,6 +1463,7 @@ int b200emb_forward_device(b200emb_handle* h, const int32_t* d_input_ids, const 
                        code == 32 ? "an input id" : "a token type id");
     return set_error(B200EMB_ERR_DEVICE_WAIT, "a device-side wait gave up (role %d)", code);
   }
+  if (int brc = bounds_after_forward(s)) return brc;
   if (timing != nullptr) {
     const int pk = timing->per_kernel;
     memset(timing, 0, sizeof(*timing));

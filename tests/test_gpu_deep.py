@@ -74,3 +74,50 @@ def test_config5_qwen2_7b_shape_full_depth(tmp_path, capsys):
         print(f"\n[config 5, 28 layers, NVFP4, {batch.n_seqs} sequences, {batch.n_tokens} tokens] min cosine "
               f"{cos.min():.6f}, all {np.round(cos, 6).tolist()} (weights {t_weights:.0f} s, oracle {t_oracle:.0f} s)")
     assert cos.min() >= COS_TOL_BLOCK, cos
+
+
+def test_router_at_configuration4_scale(capsys):
+    """The router is an index computation, and a token whose second and third probabilities are closer than
+    the summation-order noise of a 768-term fp32 dot product may legitimately choose differently from the
+    numpy router. At the configuration's size (2 187 858 tokens, hidden 768, 8 experts, top 2) this counts
+    how many do, prints the count and the widest gap among them, and requires every other token to agree
+    in set and order; counts[] must add up to the slots."""
+    from infinity_b200 import _lib
+    from oracle.encoder import moe_route
+    lib = _lib.load()
+    spec = cf.MOE_ENCODER
+    T, H, E, k = cf.synth_batch("c4").n_tokens, spec.hidden, spec.n_experts, spec.top_k
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(T, H, generator=g, device="cuda").to(torch.bfloat16)       # LayerNorm-like rows
+    wr = torch.empty(E, H, device="cuda").normal_(0.0, 0.02, generator=g)       # the configuration's init
+    br = torch.zeros(E, device="cuda")
+    idx = torch.full((T, k), -1, dtype=torch.int32, device="cuda")
+    gate = torch.zeros(T, k, dtype=torch.float32, device="cuda")
+    counts = torch.zeros(E, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    _lib.check(lib.b200emb_op_moe_router(x.data_ptr(), wr.data_ptr(), br.data_ptr(), T, H, E, k, idx.data_ptr(),
+                                         gate.data_ptr(), counts.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    got = idx.cpu().numpy()
+    wr_h, br_h = wr.cpu().numpy(), br.cpu().numpy()
+    n_set = n_order = 0
+    widest = 0.0
+    step = 1 << 18
+    for lo in range(0, T, step):
+        xs = x[lo:lo + step].float().cpu().numpy()
+        ref_idx, _, probs = moe_route(xs, wr_h, br_h, k)
+        srt = -np.sort(-probs, axis=1)
+        gap = (srt[:, :k] - srt[:, 1:k + 1]).min(axis=1)      # smallest gap at or above the selection cut
+        mine = got[lo:lo + step]
+        differs = (mine != ref_idx).any(axis=1)
+        set_differs = (np.sort(mine, axis=1) != np.sort(ref_idx, axis=1)).any(axis=1)
+        n_set += int(set_differs.sum())
+        n_order += int((differs & ~set_differs).sum())
+        if differs.any():
+            widest = max(widest, float(gap[differs].max()))
+        assert not (differs & (gap > 1e-6)).any(), "a token with a clear gap was routed differently"
+    with capsys.disabled():
+        print(f"\n[router, {T} tokens x {H}, {E} experts, top {k}] top-{k} set differs from the fp32 numpy router for {n_set} "
+              f"tokens, order only for {n_order}; widest probability gap among them {widest:.2e}")
+    assert counts.sum().item() == T * k
+    assert np.array_equal(np.bincount(got.ravel(), minlength=E), counts.cpu().numpy())

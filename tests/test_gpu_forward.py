@@ -348,6 +348,34 @@ def test_failed_workspace_growth_leaves_the_handle_usable(tmp_path):
     model.close()
 
 
+def test_tensor_maps_are_encoded_once_per_buffer_and_shape(tmp_path):
+    """The second forward of a batch shape asks the driver for no descriptor: every request is
+    served from the table; a new token count encodes the activation-side maps again and still
+    finds the weight-side ones."""
+    import ctypes as C
+    from infinity_b200 import _lib
+    lib = _lib.load()
+
+    def stats():
+        h, m = C.c_uint64(), C.c_uint64()
+        assert lib.b200emb_tensor_map_stats(C.byref(h), C.byref(m)) == 0
+        return h.value, m.value
+
+    spec = cf.tiny_spec("bert")
+    model, _ = build_model(tmp_path, spec, 21, perturb=True)
+    a = cf.random_batch(spec, [40, 3, 77], 5)
+    first = model.forward(a)
+    h0, m0 = stats()
+    again = model.forward(a)
+    h1, m1 = stats()
+    assert m1 == m0 and h1 > h0
+    assert np.array_equal(first, again)
+    model.forward(cf.random_batch(spec, [33, 9], 6))      # other token count: new activation maps, same weight maps
+    h2, m2 = stats()
+    assert m2 > m1 and h2 > h1
+    model.close()
+
+
 def test_invalid_inputs_are_rejected(tmp_path):
     from infinity_b200._lib import B200EmbError
     spec = cf.tiny_spec("bert")

@@ -137,7 +137,9 @@ def _attention_ref(qkv, cu, nh, nkv, d, causal):
     return out
 
 
-@pytest.mark.parametrize("d,nh,nkv", [(32, 12, 12), (64, 16, 16), (64, 4, 4), (128, 8, 2), (128, 4, 4)])
+# head_dim 32 shares a 64-column tile between two adjacent heads: odd head counts and grouped keys put queries, keys
+# and values at every combination of even and odd column blocks
+@pytest.mark.parametrize("d,nh,nkv", [(32, 12, 12), (32, 5, 5), (32, 6, 2), (32, 3, 1), (64, 16, 16), (64, 4, 4), (128, 8, 2), (128, 4, 4)])
 # 0x100: on the mma.sync kernel; 0x200: on the one-CTA-per-SM tensor-memory kernel
 @pytest.mark.parametrize("causal", [0, 1, 0x100, 0x101, 0x200])
 def test_attention_varlen(lib, d, nh, nkv, causal):
@@ -158,7 +160,7 @@ def test_attention_varlen(lib, d, nh, nkv, causal):
 
 
 @pytest.mark.parametrize("kind", ["wide", "rising", "extreme"])
-@pytest.mark.parametrize("d,flags", [(64, 0), (64, 0x200), (64, 1), (128, 0), (128, 1)])
+@pytest.mark.parametrize("d,flags", [(32, 0), (64, 0), (64, 0x200), (64, 1), (128, 0), (128, 1)])
 def test_attention_wide_score_range(lib, kind, d, flags):
     """Scores far above a row's first keys: the head_dim-64 kernel keeps a per-row reference point
     (maximum of the first 32 keys) and must move it, redo P and rescale O when a later score exceeds
