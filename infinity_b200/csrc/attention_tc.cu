@@ -303,83 +303,65 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __re
     int out_rows = 0;
     __nv_bfloat16* out_dst = nullptr;
     const size_t out_stride = static_cast<size_t>(n_heads) * D;
-    // O of the pending item -> bf16 rows in global memory. Each warp stages 16 rows at a time in shared
-    // memory (128 bytes per row, 16-byte chunks XOR-swizzled by row so that neither pass has bank
-    // conflicts) and writes them out as whole 128-byte lines, four rows per instruction.
-    auto write_pending = [&]() {
+    // O of the pending item -> bf16 rows in global memory, in two parts. load_pending brings the warp's O rows
+    // into registers (scaled and packed to bf16 pairs); it has to come before the warp's arrival on bar_p, because the P V that arrival releases
+    // overwrites O. store_pending writes them; it runs after the arrival, in the time the
+    // warp would otherwise spend waiting for the next S, so only the tensor-memory read is on the chain
+    // softmax -> MMA -> softmax. For head_dim 64 each warp stages 16 rows at a time in shared memory (128 bytes
+    // per row, 16-byte chunks XOR-swizzled by row so that neither pass has bank conflicts) and writes them out
+    // as whole 128-byte lines, four rows per instruction; for head_dim 32 every lane writes its own 64-byte row.
+    auto load_pending = [&](uint32_t (&po)[D / 2]) {
       if (!mbar_wait(bar_pv, (gi - 1) & 1u)) failed = true;  // the item's last P V (normally long done)
       failed = __any_sync(0xffffffffu, failed);
       if (failed) return;
       tc_fence_after_sync();
-      if (D == 32) {
-        // 64 bytes per row: every lane writes its own row (two whole sectors)
-        if (out_rows > 0) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(lane_base + TC_O_COL, r);
-          tmem_ld_wait_for(r);
-          if (lane < out_rows) {
-            const float inv = out_inv;
-            uint4* dst = reinterpret_cast<uint4*>(out_dst + static_cast<size_t>(lane) * out_stride);
+      if (out_rows > 0) {
+        const float inv = out_inv;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              uint4 u;
-              __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[c * 8 + 0]) * inv, __uint_as_float(r[c * 8 + 1]) * inv);
-              __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[c * 8 + 2]) * inv, __uint_as_float(r[c * 8 + 3]) * inv);
-              __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[c * 8 + 4]) * inv, __uint_as_float(r[c * 8 + 5]) * inv);
-              __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[c * 8 + 6]) * inv, __uint_as_float(r[c * 8 + 7]) * inv);
-              u.x = *reinterpret_cast<uint32_t*>(&p0);
-              u.y = *reinterpret_cast<uint32_t*>(&p1);
-              u.z = *reinterpret_cast<uint32_t*>(&p2);
-              u.w = *reinterpret_cast<uint32_t*>(&p3);
-              dst[c] = u;
-            }
+        for (int c = 0; c < D; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(lane_base + TC_O_COL + c, r);
+          tmem_ld_wait_for(r);
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[j]) * inv, __uint_as_float(r[j + 1]) * inv);
+            po[(c + j) >> 1] = *reinterpret_cast<uint32_t*>(&b);
           }
         }
-        out_pending = false;
+      }
+    };
+    auto store_pending = [&](const uint32_t (&po)[D / 2]) {
+      out_pending = false;
+      if (out_rows <= 0) return;
+      if (D == 32) {
+        if (lane < out_rows) {
+          uint4* dst = reinterpret_cast<uint4*>(out_dst + static_cast<size_t>(lane) * out_stride);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) dst[c] = make_uint4(po[c * 4], po[c * 4 + 1], po[c * 4 + 2], po[c * 4 + 3]);
+        }
         return;
       }
-      if (out_rows > 0) {
-        uint32_t ra[32], rb[32];
-        tmem_ld_32x32b_x32(lane_base + TC_O_COL, ra);
-        tmem_ld_32x32b_x32(lane_base + TC_O_COL + 32, rb);
-        tmem_ld_wait_for(ra);
-        tmem_ld_wait_for(rb);
-        const float inv = out_inv;
-        auto stage8 = [&](const uint32_t* r, int chunk) {
-          uint4 u;
-          __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
-          __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
-          __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
-          __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
-          u.x = *reinterpret_cast<uint32_t*>(&p0);
-          u.y = *reinterpret_cast<uint32_t*>(&p1);
-          u.z = *reinterpret_cast<uint32_t*>(&p2);
-          u.w = *reinterpret_cast<uint32_t*>(&p3);
-          *reinterpret_cast<uint4*>(stage + (lane & 15) * 128 + ((chunk ^ (lane & 7)) << 4)) = u;
-        };
-        const int sub = lane >> 3, chunk = lane & 7;
+      const int sub = lane >> 3, chunk = lane & 7;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          if ((lane >> 4) == half) {
+      for (int half = 0; half < 2; ++half) {
+        if ((lane >> 4) == half) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) stage8(&ra[c * 8], c);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) stage8(&rb[c * 8], 4 + c);
-          }
-          __syncwarp();
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int rl = i * 4 + sub;  // row within this half
-            const int r = half * 16 + rl;
-            if (r < out_rows) {
-              const uint4 u = *reinterpret_cast<const uint4*>(stage + rl * 128 + ((chunk ^ (rl & 7)) << 4));
-              *reinterpret_cast<uint4*>(out_dst + static_cast<size_t>(r) * out_stride + chunk * 8) = u;
-            }
-          }
-          __syncwarp();
+          for (int c = 0; c < D / 8; ++c)
+            *reinterpret_cast<uint4*>(stage + (lane & 15) * 128 + ((c ^ (lane & 7)) << 4)) =
+                make_uint4(po[c * 4], po[c * 4 + 1], po[c * 4 + 2], po[c * 4 + 3]);
         }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int rl = i * 4 + sub;  // row within this half
+          const int r = half * 16 + rl;
+          if (r < out_rows) {
+            const uint4 u = *reinterpret_cast<const uint4*>(stage + rl * 128 + ((chunk ^ (rl & 7)) << 4));
+            *reinterpret_cast<uint4*>(out_dst + static_cast<size_t>(r) * out_stride + chunk * 8) = u;
+          }
+        }
+        __syncwarp();
       }
-      out_pending = false;
     };
     const float2 scale2 = make_float2(scale_log2, scale_log2);
     for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
@@ -538,12 +520,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __re
           }
         }
         if (failed) break;  // warp-uniform: set from __all_sync
-        if (out_pending) {
-          write_pending();  // previous item's rows; its O is overwritten only after the arrival below
+        if (out_pending) {  // first step of an item that follows another
+          uint32_t po[D / 2];
+          load_pending(po);  // previous item's rows; its O is overwritten only after the arrival below
           if (failed) break;
+          tc_fence_before_sync();
+          mbar_arrive(bar_p);
+          store_pending(po);
+        } else {
+          tc_fence_before_sync();
+          mbar_arrive(bar_p);  // this thread's P row is in tensor memory and its reads of S are done
         }
-        tc_fence_before_sync();
-        mbar_arrive(bar_p);  // this thread's P row is in tensor memory and its reads of S are done
       }
       if (failed) break;
       out_pending = true;
@@ -551,7 +538,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __re
       out_rows = warp_active ? min(32, L - (t.q_start + warp * 32)) : 0;
       out_dst = out + static_cast<size_t>(t.seq_start + t.q_start + warp * 32) * out_stride + h * D;
     }
-    if (!failed && out_pending) write_pending();
+    if (!failed && out_pending) {
+      uint32_t po[D / 2];
+      load_pending(po);
+      if (!failed) store_pending(po);
+    }
     if (failed && lane == 0) atomicExch(err_flag, 4);
   }
 
