@@ -111,7 +111,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __re
       mbar_init(&v_empty[i], 1);
     }
     mbar_init(bar_s, 1);
-    mbar_init(bar_p, 128);
+    mbar_init(bar_p, 4);  // one arrival per softmax warp
     mbar_init(bar_pv, 1);
     fence_mbar_init();
   }
@@ -207,7 +207,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __re
     bool ok = true;
     // every lane waits; the warp agrees on the outcome so that it never splits around elect.sync
     auto wait_all = [](uint64_t* bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbar_wait(bar, parity)); };
-    auto issue_s = [&]() -> bool {  // false when a wait gave up
+    // S of a step in two parts: prepare_s waits for its operands and builds the descriptors, fire_s issues the
+    // instructions. Between a softmax arrival and the next S only fire_s runs: the waits and the descriptor
+    // arithmetic of prepare_s are done before the issuer starts waiting for that arrival.
+    uint64_t s_a_desc = 0, s_b_desc = 0;
+    uint32_t s_idesc = 0;
+    bool s_prepared = false;
+    auto prepare_s = [&]() -> bool {  // false when a wait gave up
       if (s_item >= n_items) return true;
       if (s_it == 0) {
         s_len = __shfl_sync(0xffffffffu, tiles[s_item / n_heads].seq_len, 0);
@@ -215,18 +221,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __re
         if (!wait_all(&q_full[qslot], qphase)) return false;
       }
       if (!wait_all(&k_full[kslot], kphase)) return false;
-      tc_fence_after_sync();
       const int nv = min(TC_BKV, s_len - s_it * TC_BKV);
-      const uint32_t idesc = make_idesc_bf16_f32(128, (nv + 15) & ~15);
+      s_idesc = make_idesc_bf16_f32(128, (nv + 15) & ~15);
       // head_dim 32: the odd column block of a tile starts 64 bytes (4 descriptor units) into the swizzled row
       const int s_h = s_item % n_heads;
       const int q_odd = D == 32 ? (s_h & 1) : 0;
       const int k_odd = D == 32 ? ((n_heads + s_h / (n_heads / n_kv_heads)) & 1) : 0;
-      const uint64_t a_desc = make_kmajor_sw128_desc(q_addr + qslot * TC_TILE_BYTES) + 4 * q_odd;
-      const uint64_t b_desc = make_kmajor_sw128_desc(k_addr + kslot * TC_TILE_BYTES) + 4 * k_odd;
+      s_a_desc = make_kmajor_sw128_desc(q_addr + qslot * TC_TILE_BYTES) + 4 * q_odd;
+      s_b_desc = make_kmajor_sw128_desc(k_addr + kslot * TC_TILE_BYTES) + 4 * k_odd;
+      s_prepared = true;
+      return true;
+    };
+    auto fire_s = [&]() {
+      if (!s_prepared) return;
+      s_prepared = false;
+      tc_fence_after_sync();
 #pragma unroll
       for (int k = 0; k < D / 16; ++k)
-        if (elect_one()) tc_mma_f16(tmem_u + TC_S_COL, a_desc + 2 * k, b_desc + 2 * k, idesc, k != 0);
+        if (elect_one()) tc_mma_f16(tmem_u + TC_S_COL, s_a_desc + 2 * k, s_b_desc + 2 * k, s_idesc, k != 0);
       if (elect_one()) {
         tc_commit(bar_s);
         tc_commit(&k_empty[kslot]);
@@ -244,9 +256,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __re
           qphase ^= 1u;
         }
       }
-      return true;
     };
-    ok = issue_s();
+    ok = prepare_s();
+    if (ok) fire_s();
     uint32_t gi = 0;
     const uint32_t idesc_pv = make_idesc_bf16_f32_b_mn(128, D);
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
@@ -255,6 +267,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __re
       const int v_odd = D == 32 ? ((n_heads + n_kv_heads + (item % n_heads) / (n_heads / n_kv_heads)) & 1) : 0;
       for (int it = 0; it < n_kv; ++it, ++gi) {
         const int n_eff = (min(TC_BKV, L - it * TC_BKV) + 15) & ~15;
+        // operands and descriptors of the next S first, so that only the instructions themselves follow the arrival
+        if (!prepare_s()) {
+          ok = false;
+          break;
+        }
         if (!wait_all(bar_p, gi & 1u)) {
           ok = false;
           break;
@@ -262,10 +279,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __re
         // S of the next step first: it only needs the S columns, which bar_p has just released, and lets
         // the next softmax start while P V of this step executes. The softmax threads hold back their
         // first P store of the next step until bar_pv says that P V has read this step's P.
-        if (!issue_s()) {
-          ok = false;
-          break;
-        }
+        fire_s();
         if (!wait_all(&v_full[vslot], vphase)) {
           ok = false;
           break;
@@ -525,11 +539,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_qkv, __nv_bfloat16* __re
           load_pending(po);  // previous item's rows; its O is overwritten only after the arrival below
           if (failed) break;
           tc_fence_before_sync();
-          mbar_arrive(bar_p);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_p);
           store_pending(po);
         } else {
+          // every lane's P row is in tensor memory and its reads of S are done: the warp meets and arrives once
+          // (128 separate arrivals on one mbarrier serialise)
           tc_fence_before_sync();
-          mbar_arrive(bar_p);  // this thread's P row is in tensor memory and its reads of S are done
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_p);
         }
       }
       if (failed) break;
