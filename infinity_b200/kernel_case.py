@@ -19,6 +19,7 @@ import numpy as np
 import torch
 
 from . import _lib
+from . import configs as cf
 
 
 def main() -> None:
@@ -38,6 +39,8 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=65536)
     ap.add_argument("--hidden", type=int, default=1024)
     ap.add_argument("--launches", type=int, default=3)
+    ap.add_argument("--lengths-of", default=None, choices=sorted(cf.SPECS),
+                    help="attention: take the sequence lengths of this configuration's synthetic batch instead of --seqs x --len")
     a = ap.parse_args()
     lib = _lib.load()
     torch.manual_seed(0)
@@ -105,7 +108,12 @@ def main() -> None:
               f"expansion kernel + bf16 gemm {t_exp:.3f} ms ({flops / t_exp / 1e9:.0f} TFLOP/s)")
     elif a.kernel == "attention":
         nkv = a.kv_heads or a.heads
-        cu = (np.arange(a.seqs + 1) * a.len).astype(np.int32)
+        if a.lengths_of:
+            lengths = cf.synth_batch(a.lengths_of).lengths
+            a.seqs, a.len = len(lengths), int(lengths[0])
+            cu = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+        else:
+            cu = (np.arange(a.seqs + 1) * a.len).astype(np.int32)
         T = int(cu[-1])
         qkv = torch.randn(T, (a.heads + 2 * nkv) * a.head_dim, device="cuda").to(torch.bfloat16)
         out = torch.empty(T, a.heads * a.head_dim, dtype=torch.bfloat16, device="cuda")
@@ -125,7 +133,8 @@ def main() -> None:
         ref = (torch.softmax(s, -1) @ vh).transpose(0, 1).reshape(a.len, -1)
         err = (out[: a.len].float() - ref).abs().max().item()
         assert err < 2e-2, err
-        print(f"attention {a.seqs}x{a.len} ok, max abs err {err:.4f}")
+        flop = 4.0 * float((np.diff(cu).astype(np.float64) ** 2).sum()) * a.heads * a.head_dim * (0.5 if a.causal & 1 else 1.0)
+        print(f"attention {a.seqs} sequences, {T} tokens ok, max abs err {err:.4f}, {flop / 1e9:.1f} GFLOP algorithmic")
     else:
         x = torch.randn(a.rows, a.hidden, device="cuda").to(torch.bfloat16)
         y = torch.randn(a.rows, a.hidden, device="cuda").to(torch.bfloat16)
