@@ -25,6 +25,8 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -580,12 +582,40 @@ int gemm_init_device() {
   return rc;
 }
 
-int gemm_pick_bn(int M, int N, int sm_count) {
-  // Widest tile whose grid still fills the machine at least once; small problems take narrower tiles.
-  const int m_tiles = (M + BM - 1) / BM;
-  if (m_tiles * ((N + 255) / 256) >= sm_count) return 256;
-  if (m_tiles * ((N + 127) / 128) >= sm_count) return 128;
-  return 64;
+// Tile width. The rule: the widest tile whose grid still fills the machine at least once; small problems take
+// narrower tiles. For short reductions (K <= 512: the hidden-384 / 512 encoders) a 256-wide tile has six to eight K
+// blocks, fill and epilogue weigh as much as the MMAs, and the count of rounds of the persistent grid decides: there a
+// small cost model chooses, rounds x (fixed part + K / 16 steps), with the fixed part growing with the width
+// (300 + 5 cycles per column: the epilogue of the last round is not overlapped) and 128, 76 and 55 cycles per step for
+// 256, 128 and 64 columns; the 256-wide tile is counted with CTA pairs when the launcher would use them. Measured on the
+// bge-small shapes at 7.7 k tokens (N = 1152 and 1536, K = 384: three rounds of pair tiles against four and five of
+// tiles half as wide): 128 takes 7 % off the forward. For K >= 1024 the same model was measured wrong (narrow tiles
+// stream twice the operand bytes per flop and lose 3-19 % from 5 k tokens on), so it is not consulted there.
+int gemm_pick_bn(int M, int N, int K, int sm_count, bool grouped) {
+  // Diagnostic override for tuning runs: B200EMB_GEMM_BN_MAP="N:K:width,N:K:width,..." (width 64, 128 or 256).
+  for (const char* e = getenv("B200EMB_GEMM_BN_MAP"); e != nullptr && *e != 0;) {
+    int n = 0, k = 0, b = 0;
+    if (sscanf(e, "%d:%d:%d", &n, &k, &b) == 3 && n == N && k == K && (b == 64 || b == 128 || b == 256)) return b;
+    e = strchr(e, ',');
+    if (e != nullptr) ++e;
+  }
+  const long long m_tiles = (M + BM - 1) / BM;
+  if (K > 512 || grouped) {
+    if (m_tiles * ((N + 255) / 256) >= sm_count) return 256;
+    if (m_tiles * ((N + 127) / 128) >= sm_count) return 128;
+    return 64;
+  }
+  const long long k_steps = (K + 15) / 16;
+  auto rounds = [&](long long tiles, long long units) { return (tiles + units - 1) / units; };
+  const long long pair_tiles = ((M + 255) / 256) * static_cast<long long>((N + 255) / 256);
+  const bool pairs = pair_tiles >= sm_count / 2;
+  const long long r256 = pairs ? rounds(pair_tiles, sm_count / 2) : rounds(m_tiles * ((N + 255) / 256), sm_count);
+  if (r256 >= 8) return 256;  // many rounds: the waves no longer matter
+  const long long c256 = r256 * (300 + 5 * 256 + k_steps * 128);
+  const long long c128 = rounds(m_tiles * ((N + 127) / 128), sm_count) * (300 + 5 * 128 + k_steps * 76);
+  const long long c64 = rounds(m_tiles * ((N + 63) / 64), sm_count) * (300 + 5 * 64 + k_steps * 55);
+  if (c256 <= c128 && c256 <= c64) return 256;
+  return c128 <= c64 ? 128 : 64;
 }
 
 int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int epi,
@@ -600,7 +630,7 @@ int launch_gemm_bf16(const void* A, const void* W, const float* bias, void* C, i
   // force_bn 257 = CTA-pair kernel (256-wide tiles); otherwise pairs are used whenever the widest tile is
   // chosen, the problem is not grouped, and there is at least one 256 x 256 tile per pair of SMs
   bool pair = force_bn == 257;
-  int bn = pair ? 256 : (force_bn > 0 ? force_bn : gemm_pick_bn(M, N, sm_count));
+  int bn = pair ? 256 : (force_bn > 0 ? force_bn : gemm_pick_bn(M, N, K, sm_count, tile_expert != nullptr));
   int n_out = N;
   if (epi == EPI_BIAS_SWIGLU) {
     // W holds 128-row blocks [gate rows | up rows]; a 256-wide tile yields 128 output columns
