@@ -169,6 +169,12 @@ def gpu_torch_sample(passes: int = 2):
                     "host ids in, host fp32 rows out; a baseline on the same GPU, not part of this library's path"}
 
 
+# the workload both arms name in config.workload
+WORKLOAD = ("bert-large-shape embedder (24 layers, hidden 1024, 16 heads, FFN 4096), "
+            f"{SEQS_PER_GPU} sequences per GPU, log-normal lengths (median 128, sigma 0.8) in [8, 512], "
+            "mean pooling + L2 normalise")
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -187,8 +193,8 @@ def run_reference(args):
         "impl": "reference", "metric": "embedded tokens/sec", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * secs / len(per_step),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "bert-large-shape embedder, 1024 sequences log-normal(128, 0.8) in [8, 512], "
-                               "mean pooling + L2 normalise; each step a bounded sample of it on the host cores"},
+        "config": {"workload": WORKLOAD,
+                   "sample": "each step is a bounded sample of the workload on the host cores (see cpu_baseline.sample)"},
         "cpu_baseline": base,
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -391,9 +397,7 @@ def run_ours(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {
-                "workload": "bert-large-shape embedder (24 layers, hidden 1024, 16 heads, FFN 4096), "
-                            f"{SEQS_PER_GPU} sequences per GPU, log-normal lengths (median 128, sigma 0.8) in [8, 512], "
-                            "mean pooling + L2 normalise",
+                "workload": WORKLOAD,
                 "tokens_per_step": total_tokens, "sequences_per_step": len(seqs),
                 "sharding": "token-balanced whole sequences, replicated weights, no collective" if world > 1 else "single GPU",
                 "l2": "working set (668 MB of weights + GBs of activations per step) exceeds the 126 MB L2; no flush needed",
