@@ -141,6 +141,8 @@ gather_rows_kernel(const int32_t* __restrict__ ids, int n_tokens, const __nv_bfl
   }
 }
 
+static constexpr int EMB_TOK = 4;  // tokens per warp of embed_ln_kernel
+
 template <int NCH>
 __global__ void __launch_bounds__(ROW_WARPS * 32)
 embed_ln_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ types, const int32_t* __restrict__ cu,
@@ -148,59 +150,79 @@ embed_ln_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ typ
                 const __nv_bfloat16* __restrict__ pos, const __nv_bfloat16* __restrict__ type_table,
                 const float* __restrict__ gamma, const float* __restrict__ beta, int hidden, int pos_offset,
                 float eps, __nv_bfloat16* __restrict__ out, int vocab, int type_vocab, int* __restrict__ err_flag) {
-  const int t = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
-  if (t >= n_tokens) return;
+  // A warp takes EMB_TOK consecutive tokens, one after the other (a CTA of one token per warp lives about two
+  // microseconds, too short for the block scheduler to keep the SMs full). Lane k reads the id and the type of token
+  // k; the sequence of the first token is found by bisection, the following tokens walk on from it.
+  const int t0 = (blockIdx.x * ROW_WARPS + (threadIdx.x >> 5)) * EMB_TOK;
+  if (t0 >= n_tokens) return;
   const int lane = threadIdx.x & 31;
   const int n_chunks = hidden >> 3;
-  // sequence of token t: largest i with cu[i] <= t (only needed for the position row)
-  int p = 0;
+  int my_id = 0, my_ty = 0;
+  if (lane < EMB_TOK && t0 + lane < n_tokens) {
+    my_id = checked_index(__ldg(ids + t0 + lane), vocab, err_flag, ERR_BAD_TOKEN_ID);
+    if (type_table != nullptr && types != nullptr)
+      my_ty = checked_index(__ldg(types + t0 + lane), type_vocab, err_flag, ERR_BAD_TOKEN_TYPE);
+  }
+  int seq = 0, seq_end = 0;
   if (pos != nullptr) {
+    // sequence of token t0: largest i with cu[i] <= t0 (only needed for the position rows)
     int lo = 0, hi = n_seqs;
     while (hi - lo > 1) {
       const int mid = (lo + hi) >> 1;
-      if (__ldg(cu + mid) <= t) lo = mid; else hi = mid;
+      if (__ldg(cu + mid) <= t0) lo = mid; else hi = mid;
     }
-    p = static_cast<int>(B2_IDX(pos_offset + t - __ldg(cu + lo), 2, BOUNDS_EMBED_POSITION));
+    seq = lo;
+    seq_end = __ldg(cu + seq + 1);
   }
-  const int id = checked_index(__ldg(ids + t), vocab, err_flag, ERR_BAD_TOKEN_ID);
-  const __nv_bfloat16* wrow = word + static_cast<size_t>(id) * hidden;
-  const __nv_bfloat16* prow = pos != nullptr ? pos + static_cast<size_t>(p) * hidden : nullptr;
-  const __nv_bfloat16* trow = nullptr;
-  if (type_table != nullptr) {
-    const int ty = types != nullptr ? checked_index(__ldg(types + t), type_vocab, err_flag, ERR_BAD_TOKEN_TYPE) : 0;
-    trow = type_table + static_cast<size_t>(ty) * hidden;
-  }
+#pragma unroll 1
+  for (int k = 0; k < EMB_TOK; ++k) {
+    const int t = t0 + k;
+    if (t >= n_tokens) break;
+    int p = 0;
+    if (pos != nullptr) {
+      while (t >= seq_end && seq + 1 < n_seqs) {  // sequences are not empty: at most EMB_TOK steps in all
+        ++seq;
+        seq_end = __ldg(cu + seq + 1);
+      }
+      p = static_cast<int>(B2_IDX(pos_offset + t - __ldg(cu + seq), 2, BOUNDS_EMBED_POSITION));
+    }
+    const int id = __shfl_sync(0xffffffffu, my_id, k);
+    const __nv_bfloat16* wrow = word + static_cast<size_t>(id) * hidden;
+    const __nv_bfloat16* prow = pos != nullptr ? pos + static_cast<size_t>(p) * hidden : nullptr;
+    const __nv_bfloat16* trow = nullptr;
+    if (type_table != nullptr) trow = type_table + static_cast<size_t>(__shfl_sync(0xffffffffu, my_ty, k)) * hidden;
 
-  float v[NCH][8];
-#pragma unroll
-  for (int i = 0; i < NCH; ++i) {
-    const int c = lane + 32 * i;
-    if (c < n_chunks) {
-      unpack8(__ldg(reinterpret_cast<const uint4*>(wrow + c * 8)), v[i]);
-      if (trow != nullptr) {
-        float a[8];
-        unpack8(__ldg(reinterpret_cast<const uint4*>(trow + c * 8)), a);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) v[i][e] += a[e];
-      }
-      if (prow != nullptr) {
-        float a[8];
-        unpack8(__ldg(reinterpret_cast<const uint4*>(prow + c * 8)), a);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) v[i][e] += a[e];
-      }
-    }
-  }
-  __nv_bfloat16* dst = out + static_cast<size_t>(t) * hidden;
-  if (gamma == nullptr) {
+    float v[NCH][8];
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
       const int c = lane + 32 * i;
-      if (c < n_chunks) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(v[i]);
+      if (c < n_chunks) {
+        unpack8(__ldg(reinterpret_cast<const uint4*>(wrow + c * 8)), v[i]);
+        if (trow != nullptr) {
+          float a[8];
+          unpack8(__ldg(reinterpret_cast<const uint4*>(trow + c * 8)), a);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[i][e] += a[e];
+        }
+        if (prow != nullptr) {
+          float a[8];
+          unpack8(__ldg(reinterpret_cast<const uint4*>(prow + c * 8)), a);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[i][e] += a[e];
+        }
+      }
     }
-    return;
+    __nv_bfloat16* dst = out + static_cast<size_t>(t) * hidden;
+    if (gamma == nullptr) {
+#pragma unroll
+      for (int i = 0; i < NCH; ++i) {
+        const int c = lane + 32 * i;
+        if (c < n_chunks) *reinterpret_cast<uint4*>(dst + c * 8) = pack8(v[i]);
+      }
+      continue;
+    }
+    layernorm_store<NCH>(v, lane, n_chunks, hidden, gamma, beta, eps, dst);
   }
-  layernorm_store<NCH>(v, lane, n_chunks, hidden, gamma, beta, eps, dst);
 }
 
 // Persistent: every warp walks rows warp_id, warp_id + n_warps, ...; gamma and beta are staged once
@@ -613,7 +635,7 @@ int launch_embed_ln(const int32_t* ids, const int32_t* types, const int32_t* d_c
     return B200EMB_OK;
   }
   const int nch = ((hidden >> 3) + 31) / 32;
-  const int grid = (n_tokens + ROW_WARPS - 1) / ROW_WARPS;
+  const int grid = (n_tokens + ROW_WARPS * EMB_TOK - 1) / (ROW_WARPS * EMB_TOK);
   B2_DISPATCH_NCH(nch, (embed_ln_kernel<NCH><<<grid, ROW_WARPS * 32, 0, stream>>>(
                            ids, types, d_cu, n_seqs, n_tokens, reinterpret_cast<const __nv_bfloat16*>(word),
                            reinterpret_cast<const __nv_bfloat16*>(pos),
