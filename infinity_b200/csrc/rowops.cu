@@ -362,22 +362,37 @@ add_rmsnorm_wide_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__
   __shared__ float red[RMS_BLOCK / 32];
   const int n_chunks = hidden >> 3;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // The loads of the CTA's next row are issued before the current row is reduced (two block barriers and a dependent
+  // store pass per row), so each CTA keeps two rows of loads in flight.
+  float4 ha[2][2];
+  uint4 ya[2];
+  auto load_row = [&](int r) {
+    const float* hr = h + static_cast<size_t>(r) * hidden;
+    const __nv_bfloat16* yr = y != nullptr ? y + static_cast<size_t>(r) * hidden : nullptr;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = threadIdx.x + RMS_BLOCK * i;
+      if (c < n_chunks) {
+        ha[i][0] = *reinterpret_cast<const float4*>(hr + c * 8);
+        ha[i][1] = *reinterpret_cast<const float4*>(hr + c * 8 + 4);
+        if (yr != nullptr) ya[i] = *reinterpret_cast<const uint4*>(yr + c * 8);
+      }
+    }
+  };
+  if (static_cast<int>(blockIdx.x) < n_rows) load_row(blockIdx.x);
   for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {
     float* hr = h + static_cast<size_t>(row) * hidden;
-    const __nv_bfloat16* yr = y != nullptr ? y + static_cast<size_t>(row) * hidden : nullptr;
     float v[2][8];
     float sq = 0.f;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       const int c = threadIdx.x + RMS_BLOCK * i;
       if (c < n_chunks) {
-        const float4 a0 = *reinterpret_cast<const float4*>(hr + c * 8);
-        const float4 a1 = *reinterpret_cast<const float4*>(hr + c * 8 + 4);
-        v[i][0] = a0.x; v[i][1] = a0.y; v[i][2] = a0.z; v[i][3] = a0.w;
-        v[i][4] = a1.x; v[i][5] = a1.y; v[i][6] = a1.z; v[i][7] = a1.w;
-        if (yr != nullptr) {
+        v[i][0] = ha[i][0].x; v[i][1] = ha[i][0].y; v[i][2] = ha[i][0].z; v[i][3] = ha[i][0].w;
+        v[i][4] = ha[i][1].x; v[i][5] = ha[i][1].y; v[i][6] = ha[i][1].z; v[i][7] = ha[i][1].w;
+        if (y != nullptr) {
           float b[8];
-          unpack8(*reinterpret_cast<const uint4*>(yr + c * 8), b);
+          unpack8(ya[i], b);
 #pragma unroll
           for (int e = 0; e < 8; ++e) v[i][e] += b[e];
           *reinterpret_cast<float4*>(hr + c * 8) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
@@ -387,6 +402,7 @@ add_rmsnorm_wide_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__
         for (int e = 0; e < 8; ++e) sq += v[i][e] * v[i][e];
       }
     }
+    if (row + static_cast<int>(gridDim.x) < n_rows) load_row(row + gridDim.x);
     sq = warp_sum(sq);
     __syncthreads();  // the previous row's readers of red[] are done
     if (lane == 0) red[warp] = sq;
