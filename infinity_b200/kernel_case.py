@@ -24,7 +24,7 @@ from . import configs as cf
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attention", "add_ln", "nvfp4"])
+    ap.add_argument("kernel", choices=["gemm", "attention", "add_ln", "nvfp4", "mxfp8"])
     ap.add_argument("--m", type=int, default=32768)
     ap.add_argument("--n", type=int, default=3072)
     ap.add_argument("--k", type=int, default=1024)
@@ -63,6 +63,29 @@ def main() -> None:
         err = (Cm[rows].float() - ref).abs().max().item()
         assert err < 0.05, err
         print(f"gemm {a.m}x{a.n}x{a.k} ok, max abs err {err:.4f}")
+    elif a.kernel == "mxfp8":
+        # the block-scaled fp8 GEMM and the bf16 GEMM on the same shape, one after the other (dense, not grouped)
+        MXFP8 = _lib.WFMT["mxfp8"]
+        A = torch.randn(a.m, a.k, device="cuda").to(torch.bfloat16)
+        W = (torch.randn(a.n, a.k, device="cuda") / math.sqrt(a.k)).to(torch.bfloat16)
+        bias = torch.randn(a.n, device="cuda") * 0.1
+        wq = torch.zeros(a.n, a.k, dtype=torch.uint8, device="cuda")
+        ws = torch.zeros(a.n, a.k // 32, dtype=torch.uint8, device="cuda")
+        _lib.check(lib.b200emb_op_quantize(W.data_ptr(), a.n, a.k, MXFP8, wq.data_ptr(), ws.data_ptr(), None, stream))
+        c8 = torch.empty(a.m, a.n, dtype=torch.bfloat16, device="cuda")
+        c16 = torch.empty(a.m, a.n, dtype=torch.bfloat16, device="cuda")
+        torch.cuda.synchronize()
+        for _ in range(a.launches):
+            _lib.check(lib.b200emb_op_gemm_mxfp8(A.data_ptr(), wq.data_ptr(), ws.data_ptr(), bias.data_ptr(), c8.data_ptr(), a.m, a.n,
+                                                 a.k, _lib.EPI[a.epi], stream))
+            _lib.check(lib.b200emb_op_gemm_bf16(A.data_ptr(), W.data_ptr(), bias.data_ptr(), c16.data_ptr(), a.m, a.n, a.k,
+                                                _lib.EPI[a.epi] | (a.bn << 8), stream))
+        torch.cuda.synchronize()
+        rows = slice(0, min(a.m, 2048))
+        err = (c8[rows].float() - c16[rows].float()).abs().max().item()
+        scale = c16[rows].float().abs().max().item()
+        assert err < 0.1 * max(1.0, scale), (err, scale)
+        print(f"mxfp8 and bf16 gemm {a.m}x{a.n}x{a.k} {a.epi} ok, max abs difference {err:.4f} (largest output {scale:.2f})")
     elif a.kernel == "nvfp4":
         NVFP4 = _lib.WFMT["nvfp4"]
         w = (torch.randn(a.n, a.k, device="cuda") * 0.02).to(torch.bfloat16)
